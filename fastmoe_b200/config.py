@@ -1,0 +1,112 @@
+r"""
+One place for every environment switch of the framework.
+
+The reference scatters its switches over several modules
+(``fmoe/fastermoe/config.py:4-13``, ``fmoe/layers.py:81-84``,
+``fmoe/fastermoe/shadow_policy.py:19-22,69-71``, ``fmoe/gates/faster_gate.py:26-41``,
+``cuda/fastermoe/smart_schedule.cpp:78-86``).  The names and defaults are kept; the
+performance-model defaults are re-based to a B200 box (NVLink 5 instead of
+InfiniBand, tcgen05 bf16 instead of V100 fp32).  New switches control the fused
+sm_100a paths.
+"""
+import os
+
+_TRUE = ("1", "ON", "on", "true", "True", "TRUE")
+
+
+def float_from_env(key, default=-1):
+    r"""Float value of ``$key``, ``default`` when unset."""
+    if key in os.environ:
+        return float(os.environ[key])
+    return default
+
+
+def int_from_env(key, default=0):
+    r"""Integer value of ``$key``, ``default`` when unset."""
+    if key in os.environ:
+        return int(os.environ[key])
+    return default
+
+
+def switch_from_env(key, default=False):
+    r"""Boolean switch: the reference accepts ``'1'`` and ``'ON'``; a few more spellings are tolerated."""
+    if key in os.environ:
+        return os.environ[key] in _TRUE
+    return default
+
+
+# ---------------------------------------------------------------------------------
+# Reference-compatible switches
+# ---------------------------------------------------------------------------------
+def faster_schedule_enabled():
+    return switch_from_env("FMOE_FASTER_SCHEDULE_ENABLE", False)
+
+
+def faster_shadow_enabled():
+    return switch_from_env("FMOE_FASTER_SHADOW_ENABLE", False)
+
+
+def faster_group_size(default=4):
+    return max(1, int_from_env("FMOE_FASTER_GROUP_SIZE", default))
+
+
+def topo_gpus_per_node(default=8):
+    try:
+        return int(os.environ["FMOE_TOPO_GPUS_PER_NODE"])
+    except (KeyError, ValueError):
+        return default
+
+
+def topo_outgoing_fraction(default=0.14):
+    try:
+        return float(os.environ["FMOE_TOPO_OUTGOING_FRACTION"])
+    except (KeyError, ValueError):
+        return default
+
+
+# B200 defaults of the shadow-expert performance model: one direction of NVLink 5
+# through NVSwitch, and a conservative sustained bf16 tcgen05 GEMM rate.
+B200_NVLINK_BYTES_PER_S = 900e9
+B200_GEMM_FLOPS = 1.3e15
+
+
+# ---------------------------------------------------------------------------------
+# New switches (fused sm_100a paths)
+# ---------------------------------------------------------------------------------
+def fused_enabled():
+    r"""``FMOE_FUSED=0`` forces the collective-library comparison path for dispatch/combine."""
+    return switch_from_env("FMOE_FUSED", True)
+
+
+def deterministic():
+    r"""Slot assignment is always scan-based (deterministic); kept as a switch for API stability."""
+    return switch_from_env("FMOE_DETERMINISTIC", True)
+
+
+def wait_timeout_ms():
+    r"""Upper bound of every device-side wait on a peer, in milliseconds."""
+    return int_from_env("FMOE_WAIT_TIMEOUT_MS", 2000)
+
+
+def debug_bounds():
+    return switch_from_env("FMOE_DEBUG_BOUNDS", False)
+
+
+def use_nvls():
+    r"""``FMOE_USE_NVLS``: ``auto`` (default) tries NVSwitch multimem and falls back to peer loads."""
+    v = os.environ.get("FMOE_USE_NVLS", "auto")
+    if v in _TRUE:
+        return True
+    if v in ("0", "OFF", "off", "false", "False"):
+        return False
+    return None
+
+
+def recv_capacity_factor():
+    r"""Rows reserved in the expert receive buffer, as a multiple of the balanced load.
+
+    ``0`` (default) reserves the worst case (every token of every rank lands on one rank),
+    which is what 180 GB of HBM per GPU is for; a positive factor bounds the buffer and turns
+    overflow into a reported error.
+    """
+    return float_from_env("FMOE_RECV_CAPACITY_FACTOR", 0.0)

@@ -1,0 +1,98 @@
+r"""
+Data parallelism with a different all-reduce group per parameter.
+
+Parity: ``fmoe/distributed.py:10-114``.  A parameter's attribute ``dp_comm`` names the
+group that averages its gradient: ``'dp'`` (default), ``'gate'``, ``'world'``, ``'moe'`` or
+any ``<name>`` passed as ``<name>_group=`` to the constructor; parameters tagged with a name
+that has no group (``'none'`` — the experts under expert parallelism) are left alone.
+
+Differences from the reference: gradients of one ``(dp_comm, dtype)`` bucket live in one
+flat buffer that is reduced in place — on B200s by the peer-to-peer/NVSwitch kernel of
+:mod:`fastmoe_b200.ops.allreduce`, which also applies the ``1/size`` scale and the optional
+fp32 accumulation in the same pass — instead of flatten → all-reduce → unflatten → copy
+(``fmoe/distributed.py:63-75``).
+"""
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .parallel.comm import get_rank_0_in_comm, get_torch_default_comm
+
+
+def _bucket_params(params, need_grad):
+    buckets = {}
+    for p in params:
+        if need_grad and (not p.requires_grad or p.grad is None):
+            continue
+        key = (getattr(p, "dp_comm", "dp"), p.dtype)
+        buckets.setdefault(key, []).append(p)
+    return buckets
+
+
+class DistributedGroupedDataParallel(nn.Module):
+    r"""Wraps ``module``; call :meth:`allreduce_params` after backward.
+
+    ``auto_allreduce`` is not implemented in the reference either.  ``need_sync`` broadcasts
+    every bucket from the first member of its group at construction.
+    """
+
+    def __init__(self, module, auto_allreduce=False, need_sync=True, **kwargs):
+        assert not auto_allreduce, "Automatic all-reduce is not implemented yet"
+        super().__init__()
+        self.module = module
+        self.comms = {}
+        for name, group in kwargs.items():
+            if name.endswith("_group"):
+                self.comms[name[:-len("_group")]] = group
+        for name in ("dp", "gate", "moe", "world"):
+            if name not in self.comms:
+                self.comms[name] = get_torch_default_comm()
+        if need_sync:
+            self._sync_params()
+
+    # -------------------------------------------------------------- gradient reduction
+    def allreduce_gradients(self, no_scale=False, reduce_after=False, fp32_allreduce=False):
+        r"""Average (or sum, with ``no_scale``) gradients inside each parameter's group."""
+        from .ops import allreduce as _ar
+        for (dp_comm, dtype), group_params in _bucket_params(self.module.parameters(), True).items():
+            if dp_comm not in self.comms:
+                continue
+            comm = self.comms[dp_comm]
+            size = dist.get_world_size(comm)
+            scale = 1.0 if no_scale else 1.0 / size
+            grads = [p.grad.data for p in group_params]
+            if _ar.try_fused_allreduce(grads, comm, scale, fp32_accumulate=fp32_allreduce):
+                continue
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            if fp32_allreduce and dtype != torch.float32:
+                flat = flat.float()
+            if not no_scale and not reduce_after:
+                flat /= size
+            dist.all_reduce(flat, group=comm)
+            if not no_scale and reduce_after:
+                flat /= size
+            offset = 0
+            for g in grads:
+                g.copy_(flat[offset:offset + g.numel()].view_as(g))
+                offset += g.numel()
+
+    def allreduce_params(self, *args, **kwargs):
+        r"""Alias kept because Megatron versions call one name or the other."""
+        return self.allreduce_gradients(*args, **kwargs)
+
+    # -------------------------------------------------------------- initial sync
+    def _sync_params(self):
+        for (dp_comm, _dtype), group_params in _bucket_params(self.module.parameters(), False).items():
+            if dp_comm not in self.comms:
+                continue
+            comm = self.comms[dp_comm]
+            datas = [p.data for p in group_params]
+            flat = torch.cat([d.reshape(-1) for d in datas])
+            dist.broadcast(flat, get_rank_0_in_comm(comm), group=comm)
+            offset = 0
+            for d in datas:
+                d.copy_(flat[offset:offset + d.numel()].view_as(d))
+                offset += d.numel()
+
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)

@@ -1,0 +1,28 @@
+r"""Plain learned top-k gate (parity: ``fmoe/gates/naive_gate.py:11-45``)."""
+import torch
+import torch.nn as nn
+
+from .base_gate import BaseGate
+from ..ops import gating
+
+
+class NaiveGate(BaseGate):
+    r"""``Linear(d_model → tot_expert)``, top-k of the logits, softmax over the k selected logits.
+
+    State-dict keys: ``gate.weight [tot_expert, d_model]``, ``gate.bias [tot_expert]``.
+    On a GPU the top-k + softmax (and their backward) are one kernel.
+    """
+
+    def __init__(self, d_model, num_expert, world_size, top_k=2, gate_bias=True):
+        super().__init__(num_expert, world_size)
+        self.gate = nn.Linear(d_model, self.tot_expert, bias=gate_bias)
+        self.top_k = top_k
+
+    def forward(self, inp, return_all_scores=False):
+        logits = self.gate(inp)
+        idx, score = gating.topk_softmax(logits.view(-1, self.tot_expert), self.top_k)
+        # The reference installs a zero "dummy" loss so that callers can always add it.
+        self.set_loss(torch.zeros(1, requires_grad=True, device=inp.device))
+        if return_all_scores:
+            return idx, score, logits
+        return idx, score

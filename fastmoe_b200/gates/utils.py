@@ -1,0 +1,24 @@
+r"""Capacity helper shared by the balanced gates (parity: ``fmoe/gates/utils.py:9-26``)."""
+import torch
+
+from ..functions import count_by_gate
+from ..ops import api as _ops
+
+
+def limit_by_capacity(topk_idx, num_expert, world_size, capacity):
+    r"""Enforce a per-local-expert ``capacity`` across all ranks.
+
+    Every expert owner grants its capacity to the requesting ranks in rank order; ranks then
+    drop the slots beyond their grant (slot order).  Returns ``(new_lec, new_gec, topk_idx)``.
+    """
+    with torch.no_grad():
+        cap = torch.full((num_expert,), int(capacity), dtype=torch.int32, device=topk_idx.device)
+        _, _lec, gec = count_by_gate(topk_idx, num_expert, world_size, require_pos=False)
+        new_gec = _ops.limit_by_capacity(gec, cap, num_expert, world_size)
+        if world_size > 1:
+            new_lec = _ops.expert_exchange(new_gec, num_expert, world_size)
+        else:
+            new_lec = new_gec
+        topk_idx = _ops.prune_gate_by_capacity(
+            topk_idx, new_lec.to(torch.int32), num_expert, world_size)
+    return new_lec, new_gec, topk_idx
