@@ -1,0 +1,640 @@
+// Routing bookkeeping, row scatter / combine, gate top-k and balancing kernels.
+//
+// Replaces cuda/local_exchange.cuh (expert_count, assign_pos), cuda/balancing.cuh
+// (limit_by_capacity, prune_gate_by_capacity), cuda/parallel_linear.cuh:8-53 (column_reduce)
+// and the ATen index_select / index_copy_ / bmm / topk / softmax calls of the reference's layer.
+// All kernels are deterministic: no result depends on the order in which atomics land.
+#include "routing.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace fmoe {
+namespace {
+
+constexpr int kRouteThreads = 1024;
+constexpr int kRouteSmemLimit = 200 * 1024;
+
+__device__ __forceinline__ unsigned lanemask_lt() {
+  unsigned m;
+  asm volatile("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+  return m;
+}
+
+// One CTA.  Warp w owns the contiguous slot range [w * chunk, (w + 1) * chunk): pass 1 builds
+// per-warp histograms, the CTA turns them into exclusive prefixes over warps, pass 2 hands
+// every slot its rank.  Within a warp slots are visited in order, 32 at a time.
+__global__ void __launch_bounds__(kRouteThreads, 1)
+route_kernel(const int64_t* __restrict__ idx, int n_slots, int tot, int nw, int* __restrict__ counts,
+             int* __restrict__ rank, int* __restrict__ offs) {
+  extern __shared__ int hist[];  // [nw][tot]
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < nw * tot; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+
+  int chunk = (n_slots + nw - 1) / nw;
+  chunk = (chunk + 31) & ~31;
+  const int begin = warp * chunk;
+  const int end = min(n_slots, begin + chunk);
+
+  if (warp < nw) {
+    int* h = hist + warp * tot;
+    for (int s0 = begin; s0 < end; s0 += 32) {
+      const int s = s0 + lane;
+      long e = (s < end) ? idx[s] : -1;
+      const bool valid = e >= 0 && e < tot;
+      const int key = valid ? static_cast<int>(e) : tot + lane;
+      const unsigned peers = __match_any_sync(0xffffffffu, key);
+      if (valid && (peers & lanemask_lt()) == 0) h[key] += __popc(peers);
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < tot; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < nw; ++w) {
+      const int t = hist[w * tot + e];
+      hist[w * tot + e] = run;
+      run += t;
+    }
+    counts[e] = run;
+  }
+  __syncthreads();
+  if (warp < nw) {
+    int* h = hist + warp * tot;
+    for (int s0 = begin; s0 < end; s0 += 32) {
+      const int s = s0 + lane;
+      long e = (s < end) ? idx[s] : -1;
+      const bool valid = e >= 0 && e < tot;
+      const int key = valid ? static_cast<int>(e) : tot + lane;
+      const unsigned peers = __match_any_sync(0xffffffffu, key);
+      const int before = __popc(peers & lanemask_lt());
+      int r = -1;
+      if (valid) r = h[key] + before;
+      __syncwarp();
+      if (valid && before == 0) h[key] += __popc(peers);
+      __syncwarp();
+      if (s < end) rank[s] = r;
+    }
+  }
+  if (offs != nullptr) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int run = 0;
+      for (int e = 0; e < tot; ++e) {
+        offs[e] = run;
+        run += counts[e];
+      }
+      offs[tot] = run;
+    }
+  }
+}
+
+__global__ void prune_kernel(const int64_t* __restrict__ idx, const int* __restrict__ rank,
+                             const int* __restrict__ cap, int n_slots, int tot,
+                             int64_t* __restrict__ out) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n_slots) return;
+  const long e = idx[s];
+  out[s] = (e >= 0 && e < tot && rank[s] < cap[e]) ? e : -1;
+}
+
+__global__ void limit_kernel(const int64_t* __restrict__ ec, int* __restrict__ cap,
+                             int64_t* __restrict__ eca, int n_expert, int n_worker) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n_expert) return;
+  long left = cap[e];
+  for (int w = 0; w < n_worker; ++w) {
+    const long want = ec[w * n_expert + e];
+    const long room = left > 0 ? left : 0;
+    eca[w * n_expert + e] = want < room ? want : room;
+    left -= want;
+  }
+  cap[e] = static_cast<int>(left);
+}
+
+__global__ void fill_pos_kernel(const int64_t* __restrict__ idx, const int* __restrict__ rank,
+                                const int* __restrict__ cum_incl, int n_slots, int tot,
+                                int64_t* __restrict__ pos) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n_slots) return;
+  const long e = idx[s];
+  if (e < 0 || e >= tot) return;
+  const int base = e == 0 ? 0 : cum_incl[e - 1];
+  pos[base + rank[s]] = s;
+}
+
+// ------------------------------------------------------------------------------ row movement
+template <typename T> struct V2;
+template <> struct V2<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ float2 to_f2(type v) { return __bfloat1622float2(v); }
+  static __device__ __forceinline__ type from_f2(float a, float b) { return __floats2bfloat162_rn(a, b); }
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16(v); }
+};
+template <> struct V2<__half> {
+  using type = __half2;
+  static __device__ __forceinline__ float2 to_f2(type v) { return __half22float2(v); }
+  static __device__ __forceinline__ type from_f2(float a, float b) { return __floats2half2_rn(a, b); }
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half(v); }
+};
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
+  using P = typename V2<T>::type;
+  const P* p = reinterpret_cast<const P*>(&w);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 v = V2<T>::to_f2(p[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  using P = typename V2<T>::type;
+  uint4 w;
+  P* p = reinterpret_cast<P*>(&w);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = V2<T>::from_f2(f[2 * i], f[2 * i + 1]);
+  return w;
+}
+
+// One warp per slot; d % 8 == 0.
+template <typename T>
+__global__ void scatter_rows_kernel(const T* __restrict__ src, const int64_t* __restrict__ idx,
+                                    const int* __restrict__ rank, const int* __restrict__ base,
+                                    const T* __restrict__ scale, int n_slots, int k, int d,
+                                    T* __restrict__ dst, int* __restrict__ row_slot) {
+  const int s = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (s >= n_slots) return;
+  const long e = idx[s];
+  if (e < 0) return;
+  const long row = static_cast<long>(base[e]) + rank[s];
+  const uint4* in = reinterpret_cast<const uint4*>(src + static_cast<long>(s / k) * d);
+  uint4* out = reinterpret_cast<uint4*>(dst + row * d);
+  const int nv = d >> 3;
+  if (scale == nullptr) {
+    for (int i = lane; i < nv; i += 32) out[i] = __ldg(in + i);
+  } else {
+    const float sc = V2<T>::to_f(scale[s]);
+    for (int i = lane; i < nv; i += 32) {
+      float f[8];
+      unpack8<T>(__ldg(in + i), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] *= sc;
+      out[i] = pack8<T>(f);
+    }
+  }
+  if (row_slot != nullptr && lane == 0) row_slot[row] = s;
+}
+
+// One warp per token; d % 8 == 0.
+template <typename T>
+__global__ void gather_combine_kernel(const T* __restrict__ rows, const int64_t* __restrict__ idx,
+                                      const int* __restrict__ rank, const int* __restrict__ base,
+                                      const T* __restrict__ weight, int n_tokens, int k, int d,
+                                      T* __restrict__ out) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= n_tokens) return;
+  const int nv = d >> 3;
+  uint4* o = reinterpret_cast<uint4*>(out + static_cast<long>(t) * d);
+  for (int i = lane; i < nv; i += 32) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      const int s = t * k + j;
+      const long e = idx[s];
+      if (e < 0) continue;
+      const long row = static_cast<long>(base[e]) + rank[s];
+      const float w = weight != nullptr ? V2<T>::to_f(weight[s]) : 1.f;
+      float f[8];
+      unpack8<T>(__ldg(reinterpret_cast<const uint4*>(rows + row * d) + i), f);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] += w * f[q];
+    }
+    o[i] = pack8<T>(acc);
+  }
+}
+
+// One warp per slot.
+template <typename T>
+__global__ void combine_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ rows,
+                                   const int64_t* __restrict__ idx, const int* __restrict__ rank,
+                                   const int* __restrict__ base, const T* __restrict__ weight,
+                                   int n_slots, int k, int d, T* __restrict__ drows,
+                                   T* __restrict__ dscore) {
+  const int s = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (s >= n_slots) return;
+  const long e = idx[s];
+  if (e < 0) {
+    if (lane == 0 && dscore != nullptr) dscore[s] = V2<T>::from_f(0.f);
+    return;
+  }
+  const long row = static_cast<long>(base[e]) + rank[s];
+  const uint4* g = reinterpret_cast<const uint4*>(dout + static_cast<long>(s / k) * d);
+  const uint4* y = reinterpret_cast<const uint4*>(rows + row * d);
+  uint4* dy = reinterpret_cast<uint4*>(drows + row * d);
+  const float w = V2<T>::to_f(weight[s]);
+  const int nv = d >> 3;
+  float dot = 0.f;
+  for (int i = lane; i < nv; i += 32) {
+    float gf[8], yf[8];
+    unpack8<T>(__ldg(g + i), gf);
+    unpack8<T>(__ldg(y + i), yf);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      dot += gf[q] * yf[q];
+      gf[q] *= w;
+    }
+    dy[i] = pack8<T>(gf);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (lane == 0 && dscore != nullptr) dscore[s] = V2<T>::from_f(dot);
+}
+
+// Column sums per group.  A block takes 128 rows x 256 columns; blockIdx.y enumerates the
+// (group, 128-row chunk) pieces, found by scanning the offsets.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_kernel(const T* __restrict__ x, const int* __restrict__ offs, int num_groups, int n,
+              float* __restrict__ out) {
+  __shared__ float red[8][256 + 8];
+  int piece = blockIdx.y;
+  int g = 0, r0 = 0, r1 = 0;
+  bool found = false;
+  for (; g < num_groups; ++g) {
+    const int b = offs[g], e = offs[g + 1];
+    const int pieces = (e - b + 127) >> 7;
+    if (piece < pieces) {
+      r0 = b + piece * 128;
+      r1 = min(e, r0 + 128);
+      found = true;
+      break;
+    }
+    piece -= pieces;
+  }
+  if (!found) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 256 + lane * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col < n) {
+    for (int r = r0 + warp; r < r1; r += 8) {
+      float f[8];
+      unpack8<T>(__ldg(reinterpret_cast<const uint4*>(x + static_cast<long>(r) * n + col)), f);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] += f[q];
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 8; ++q) red[warp][lane * 8 + q] = acc[q];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < n) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += red[w][threadIdx.x];
+    atomicAdd(out + static_cast<long>(g) * n + c, s);
+  }
+}
+
+// ------------------------------------------------------------------------------ gate
+template <typename T> struct Ld;
+template <> struct Ld<float> {
+  static __device__ __forceinline__ float get(const float* p, long i) { return p[i]; }
+  static __device__ __forceinline__ void put(float* p, long i, float v) { p[i] = v; }
+};
+template <> struct Ld<__nv_bfloat16> {
+  static __device__ __forceinline__ float get(const __nv_bfloat16* p, long i) { return __bfloat162float(p[i]); }
+  static __device__ __forceinline__ void put(__nv_bfloat16* p, long i, float v) { p[i] = __float2bfloat16(v); }
+};
+template <> struct Ld<__half> {
+  static __device__ __forceinline__ float get(const __half* p, long i) { return __half2float(p[i]); }
+  static __device__ __forceinline__ void put(__half* p, long i, float v) { p[i] = __float2half(v); }
+};
+
+constexpr int kMaxK = 8;
+
+// One warp per row.  k rounds of warp arg-max; ties go to the lower expert id.
+template <typename T>
+__global__ void gate_topk_softmax_kernel(const T* __restrict__ logits, int n_rows, int n_experts,
+                                         int k, int64_t* __restrict__ idx, T* __restrict__ prob) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  const T* in = logits + static_cast<long>(row) * n_experts;
+  float sel_v[kMaxK];
+  int sel_i[kMaxK];
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int e = lane; e < n_experts; e += 32) {
+      bool taken = false;
+      for (int q = 0; q < j; ++q) taken |= (sel_i[q] == e);
+      if (taken) continue;
+      const float v = Ld<T>::get(in, e);
+      if (v > best || (v == best && e < best_i) || best_i == 0x7fffffff) {
+        best = v;
+        best_i = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (oi != 0x7fffffff && (best_i == 0x7fffffff || ov > best || (ov == best && oi < best_i))) {
+        best = ov;
+        best_i = oi;
+      }
+    }
+    sel_v[j] = best;
+    sel_i[j] = best_i;
+  }
+  if (lane == 0) {
+    const float mx = sel_v[0];
+    float den = 0.f;
+    float ex[kMaxK];
+    for (int j = 0; j < k; ++j) {
+      ex[j] = __expf(sel_v[j] - mx);
+      den += ex[j];
+    }
+    for (int j = 0; j < k; ++j) {
+      idx[static_cast<long>(row) * k + j] = sel_i[j];
+      Ld<T>::put(prob, static_cast<long>(row) * k + j, ex[j] / den);
+    }
+  }
+}
+
+// dlogits[row, idx_j] = p_j * (g_j - sum_i g_i p_i), zero elsewhere.  One warp per row.
+template <typename T>
+__global__ void gate_topk_softmax_bwd_kernel(const T* __restrict__ dprob,
+                                             const int64_t* __restrict__ idx,
+                                             const T* __restrict__ prob, int n_rows, int n_experts,
+                                             int k, T* __restrict__ dlogits) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  float g[kMaxK], p[kMaxK];
+  int id[kMaxK];
+  float dotp = 0.f;
+  for (int j = 0; j < k; ++j) {
+    g[j] = Ld<T>::get(dprob, static_cast<long>(row) * k + j);
+    p[j] = Ld<T>::get(prob, static_cast<long>(row) * k + j);
+    id[j] = static_cast<int>(idx[static_cast<long>(row) * k + j]);
+    dotp += g[j] * p[j];
+  }
+  T* out = dlogits + static_cast<long>(row) * n_experts;
+  for (int e = lane; e < n_experts; e += 32) {
+    float v = 0.f;
+    for (int j = 0; j < k; ++j) {
+      if (id[j] == e) v = p[j] * (g[j] - dotp);
+    }
+    Ld<T>::put(out, e, v);
+  }
+}
+
+// ------------------------------------------------------------------------------ SIMT GEMM
+template <typename T> struct Acc { using type = float; };
+template <> struct Acc<double> { using type = double; };
+
+template <typename T> __device__ __forceinline__ typename Acc<T>::type ldv(const T* p, long i) {
+  return static_cast<typename Acc<T>::type>(p[i]);
+}
+template <> __device__ __forceinline__ float ldv<__nv_bfloat16>(const __nv_bfloat16* p, long i) {
+  return __bfloat162float(p[i]);
+}
+template <> __device__ __forceinline__ float ldv<__half>(const __half* p, long i) {
+  return __half2float(p[i]);
+}
+template <typename T> __device__ __forceinline__ void stv(T* p, long i, typename Acc<T>::type v) {
+  p[i] = static_cast<T>(v);
+}
+template <> __device__ __forceinline__ void stv<__nv_bfloat16>(__nv_bfloat16* p, long i, float v) {
+  p[i] = __float2bfloat16(v);
+}
+template <> __device__ __forceinline__ void stv<__half>(__half* p, long i, float v) {
+  p[i] = __float2half(v);
+}
+
+__device__ __forceinline__ int group_of_row(const int* offs, int num_groups, int row) {
+  int lo = 0, hi = num_groups;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (offs[mid] <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// One thread per output element; mode 0: NT, mode 1: NN (row modes).
+template <typename T>
+__global__ void simt_rows_kernel(int mode, int num_groups, int n, int k, const T* __restrict__ a,
+                                 const T* __restrict__ b, const int* __restrict__ offs,
+                                 const T* __restrict__ bias, T* __restrict__ out) {
+  using A = typename Acc<T>::type;
+  const int col = blockIdx.y * blockDim.x + threadIdx.x;
+  const int row = blockIdx.x;
+  if (col >= n || row >= offs[num_groups]) return;
+  const int g = group_of_row(offs, num_groups, row);
+  A acc = 0;
+  const T* ar = a + static_cast<long>(row) * k;
+  if (mode == 0) {
+    const T* br = b + (static_cast<long>(g) * n + col) * k;
+    for (int i = 0; i < k; ++i) acc += ldv<T>(ar, i) * ldv<T>(br, i);
+  } else {
+    const T* bg = b + static_cast<long>(g) * k * n + col;
+    for (int i = 0; i < k; ++i) acc += ldv<T>(ar, i) * ldv<T>(bg, static_cast<long>(i) * n);
+  }
+  if (bias != nullptr) acc += ldv<T>(bias, static_cast<long>(g) * n + col);
+  stv<T>(out, static_cast<long>(row) * n + col, acc);
+}
+
+// out[g, mi, ni] = sum_r P[r, mi] * Q[r, ni]
+template <typename T>
+__global__ void simt_wgrad_kernel(int m, int n, const T* __restrict__ p, const T* __restrict__ q,
+                                  const int* __restrict__ offs, T* __restrict__ out) {
+  using A = typename Acc<T>::type;
+  const int ni = blockIdx.x * blockDim.x + threadIdx.x;
+  const int mi = blockIdx.y;
+  const int g = blockIdx.z;
+  if (ni >= n) return;
+  A acc = 0;
+  for (int r = offs[g]; r < offs[g + 1]; ++r) {
+    acc += ldv<T>(p, static_cast<long>(r) * m + mi) * ldv<T>(q, static_cast<long>(r) * n + ni);
+  }
+  stv<T>(out, (static_cast<long>(g) * m + mi) * n + ni, acc);
+}
+
+template <typename T>
+cudaError_t simt_typed(int mode, int num_groups, long rows_cap, int m, int n, int k, const void* a,
+                       const void* b, const int* offs, const void* bias, void* out,
+                       cudaStream_t stream) {
+  if (mode == 2) {
+    dim3 grid((n + 127) / 128, m, num_groups);
+    simt_wgrad_kernel<T><<<grid, 128, 0, stream>>>(m, n, static_cast<const T*>(a),
+                                                   static_cast<const T*>(b), offs,
+                                                   static_cast<T*>(out));
+  } else {
+    if (rows_cap == 0) return cudaSuccess;
+    dim3 grid(static_cast<unsigned>(rows_cap), (n + 127) / 128);
+    simt_rows_kernel<T><<<grid, 128, 0, stream>>>(mode, num_groups, n, k, static_cast<const T*>(a),
+                                                  static_cast<const T*>(b), offs,
+                                                  static_cast<const T*>(bias), static_cast<T*>(out));
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------ launchers
+cudaError_t launch_route(const int64_t* idx, int n_slots, int tot, int* counts, int* rank,
+                         int* offs, cudaStream_t stream) {
+  if (tot <= 0) return cudaErrorInvalidValue;
+  int nw = kRouteSmemLimit / (4 * tot);
+  if (nw < 1) return cudaErrorInvalidValue;
+  if (nw > 32) nw = 32;
+  const int by_work = (n_slots + 31) / 32;
+  if (nw > by_work) nw = by_work > 0 ? by_work : 1;
+  const size_t smem = static_cast<size_t>(nw) * tot * 4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kRouteSmemLimit);
+    if (e != cudaSuccess) return e;
+  }
+  route_kernel<<<1, kRouteThreads, smem, stream>>>(idx, n_slots, tot, nw, counts, rank, offs);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_prune(const int64_t* idx, const int* rank, const int* cap, int n_slots, int tot,
+                         int64_t* new_idx, cudaStream_t stream) {
+  if (n_slots == 0) return cudaSuccess;
+  prune_kernel<<<(n_slots + 255) / 256, 256, 0, stream>>>(idx, rank, cap, n_slots, tot, new_idx);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_limit_by_capacity(const int64_t* ec, int* cap, int64_t* eca, int n_expert,
+                                     int n_worker, cudaStream_t stream) {
+  limit_kernel<<<(n_expert + 127) / 128, 128, 0, stream>>>(ec, cap, eca, n_expert, n_worker);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fill_pos(const int64_t* idx, const int* rank, const int* cum_incl, int n_slots,
+                            int tot, int64_t* pos, cudaStream_t stream) {
+  if (n_slots == 0) return cudaSuccess;
+  fill_pos_kernel<<<(n_slots + 255) / 256, 256, 0, stream>>>(idx, rank, cum_incl, n_slots, tot, pos);
+  return cudaGetLastError();
+}
+
+#define FMOE_DISPATCH_16(dtype, ...)                                  \
+  if ((dtype) == 0) { using T = __nv_bfloat16; __VA_ARGS__; }         \
+  else { using T = __half; __VA_ARGS__; }
+
+cudaError_t launch_scatter_rows(int dtype, const void* src, const int64_t* idx, const int* rank,
+                                const int* base, const void* scale, int n_slots, int k, int d,
+                                void* dst, int* row_slot, cudaStream_t stream) {
+  if (n_slots == 0) return cudaSuccess;
+  if (d % 8 != 0) return cudaErrorInvalidValue;
+  const int wpb = 8;
+  FMOE_DISPATCH_16(dtype, (scatter_rows_kernel<T><<<(n_slots + wpb - 1) / wpb, wpb * 32, 0, stream>>>(
+      static_cast<const T*>(src), idx, rank, base, static_cast<const T*>(scale), n_slots, k, d,
+      static_cast<T*>(dst), row_slot)));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_combine(int dtype, const void* rows, const int64_t* idx, const int* rank,
+                                  const int* base, const void* weight, int n_tokens, int k, int d,
+                                  void* out, cudaStream_t stream) {
+  if (n_tokens == 0) return cudaSuccess;
+  if (d % 8 != 0) return cudaErrorInvalidValue;
+  const int wpb = 8;
+  FMOE_DISPATCH_16(dtype, (gather_combine_kernel<T><<<(n_tokens + wpb - 1) / wpb, wpb * 32, 0, stream>>>(
+      static_cast<const T*>(rows), idx, rank, base, static_cast<const T*>(weight), n_tokens, k, d,
+      static_cast<T*>(out))));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_bwd(int dtype, const void* dout, const void* rows, const int64_t* idx,
+                               const int* rank, const int* base, const void* weight, int n_tokens,
+                               int k, int d, void* drows, void* dscore, cudaStream_t stream) {
+  const int n_slots = n_tokens * k;
+  if (n_slots == 0) return cudaSuccess;
+  if (d % 8 != 0) return cudaErrorInvalidValue;
+  const int wpb = 8;
+  FMOE_DISPATCH_16(dtype, (combine_bwd_kernel<T><<<(n_slots + wpb - 1) / wpb, wpb * 32, 0, stream>>>(
+      static_cast<const T*>(dout), static_cast<const T*>(rows), idx, rank, base,
+      static_cast<const T*>(weight), n_slots, k, d, static_cast<T*>(drows),
+      static_cast<T*>(dscore))));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_colsum(int dtype, const void* x, const int* offs, int num_groups, long rows_cap,
+                          int n, float* out, cudaStream_t stream) {
+  if (rows_cap == 0) return cudaSuccess;
+  if (n % 8 != 0) return cudaErrorInvalidValue;
+  dim3 grid((n + 255) / 256, static_cast<unsigned>((rows_cap + 127) / 128 + num_groups));
+  FMOE_DISPATCH_16(dtype, (colsum_kernel<T><<<grid, 256, 0, stream>>>(
+      static_cast<const T*>(x), offs, num_groups, n, out)));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gate_topk_softmax(int logit_dtype, const void* logits, int n_rows, int n_experts,
+                                     int k, int64_t* idx, void* prob, cudaStream_t stream) {
+  if (n_rows == 0) return cudaSuccess;
+  if (k < 1 || k > kMaxK || k > n_experts) return cudaErrorInvalidValue;
+  const int wpb = 8;
+  const int grid = (n_rows + wpb - 1) / wpb;
+  if (logit_dtype == 0) {
+    gate_topk_softmax_kernel<__nv_bfloat16><<<grid, wpb * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(logits), n_rows, n_experts, k, idx,
+        static_cast<__nv_bfloat16*>(prob));
+  } else if (logit_dtype == 1) {
+    gate_topk_softmax_kernel<__half><<<grid, wpb * 32, 0, stream>>>(
+        static_cast<const __half*>(logits), n_rows, n_experts, k, idx, static_cast<__half*>(prob));
+  } else {
+    gate_topk_softmax_kernel<float><<<grid, wpb * 32, 0, stream>>>(
+        static_cast<const float*>(logits), n_rows, n_experts, k, idx, static_cast<float*>(prob));
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gate_topk_softmax_bwd(int logit_dtype, const void* dprob, const int64_t* idx,
+                                         const void* prob, int n_rows, int n_experts, int k,
+                                         void* dlogits, cudaStream_t stream) {
+  if (n_rows == 0) return cudaSuccess;
+  if (k < 1 || k > kMaxK) return cudaErrorInvalidValue;
+  const int wpb = 8;
+  const int grid = (n_rows + wpb - 1) / wpb;
+  if (logit_dtype == 0) {
+    gate_topk_softmax_bwd_kernel<__nv_bfloat16><<<grid, wpb * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(dprob), idx, static_cast<const __nv_bfloat16*>(prob),
+        n_rows, n_experts, k, static_cast<__nv_bfloat16*>(dlogits));
+  } else if (logit_dtype == 1) {
+    gate_topk_softmax_bwd_kernel<__half><<<grid, wpb * 32, 0, stream>>>(
+        static_cast<const __half*>(dprob), idx, static_cast<const __half*>(prob), n_rows,
+        n_experts, k, static_cast<__half*>(dlogits));
+  } else {
+    gate_topk_softmax_bwd_kernel<float><<<grid, wpb * 32, 0, stream>>>(
+        static_cast<const float*>(dprob), idx, static_cast<const float*>(prob), n_rows, n_experts,
+        k, static_cast<float*>(dlogits));
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_simt_grouped_gemm(int mode, int elem, int num_groups, long rows_cap, int m, int n,
+                                     int k, const void* a, const void* b, const int* offs,
+                                     const void* bias, void* out, cudaStream_t stream) {
+  switch (elem) {
+    case 0: return simt_typed<__nv_bfloat16>(mode, num_groups, rows_cap, m, n, k, a, b, offs, bias, out, stream);
+    case 1: return simt_typed<__half>(mode, num_groups, rows_cap, m, n, k, a, b, offs, bias, out, stream);
+    case 2: return simt_typed<float>(mode, num_groups, rows_cap, m, n, k, a, b, offs, bias, out, stream);
+    case 3: return simt_typed<double>(mode, num_groups, rows_cap, m, n, k, a, b, offs, bias, out, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace fmoe

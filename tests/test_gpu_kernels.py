@@ -1,0 +1,211 @@
+r"""GPU tier: every sm_100a kernel against a plain PyTorch fp32 restatement of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _native():
+    from fastmoe_b200.ops import native
+    return native.get()
+
+
+def _offs(counts):
+    o = torch.zeros(len(counts) + 1, dtype=torch.int32)
+    o[1:] = torch.cumsum(torch.tensor(counts), 0)
+    return o.to(DEV)
+
+
+def _segments(counts):
+    base = 0
+    for e, n in enumerate(counts):
+        yield e, base, base + n
+        base += n
+
+
+def _tol(dtype, k):
+    # bf16 has 8 bits of mantissa: inputs are exact in fp32, the only error is the output rounding.
+    return (2e-2 if dtype == torch.bfloat16 else 4e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("counts,k,n", [
+    ([100, 200], 64, 32),
+    ([128, 0, 257, 5], 128, 256),
+    ([300, 1, 511], 256, 320),
+    ([1000, 24], 1024, 512),
+])
+def test_grouped_gemm_forward(dtype, counts, k, n):
+    from fastmoe_b200.ops import grouped_gemm as gg
+    torch.manual_seed(0)
+    rows = sum(counts)
+    pad = 7  # rows past the last segment must stay untouched
+    x = torch.randn(rows + pad, k, device=DEV, dtype=dtype)
+    w = (torch.randn(len(counts), n, k, device=DEV) / k ** 0.5).to(dtype)
+    b = torch.randn(len(counts), n, device=DEV).to(dtype)
+    offs = _offs(counts)
+    out, pre = gg.forward(x, w, offs, b, act="gelu", want_pre=True)
+    for e, lo, hi in _segments(counts):
+        ref_pre = x[lo:hi].float() @ w[e].float().t() + b[e].float()
+        ref = torch.nn.functional.gelu(ref_pre)
+        assert torch.allclose(pre[lo:hi].float(), ref_pre, atol=_tol(dtype, k), rtol=2e-2)
+        assert torch.allclose(out[lo:hi].float(), ref, atol=_tol(dtype, k), rtol=2e-2)
+    assert _native().read_status(0) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("counts,k,n", [
+    ([100, 200], 64, 64),
+    ([128, 0, 257, 5], 256, 128),
+    ([700, 324], 512, 1024),
+])
+def test_grouped_gemm_dgrad(dtype, counts, k, n):
+    r"""dX = (dY W) * gelu'(pre) with W stored [E, k(out), n(in)]."""
+    from fastmoe_b200.ops import grouped_gemm as gg
+    torch.manual_seed(1)
+    rows = sum(counts)
+    dy = torch.randn(rows, k, device=DEV, dtype=dtype)
+    w = (torch.randn(len(counts), k, n, device=DEV) / k ** 0.5).to(dtype)
+    pre = torch.randn(rows, n, device=DEV, dtype=dtype)
+    offs = _offs(counts)
+    plain = gg.dgrad(dy, w, offs)
+    fused = gg.dgrad(dy, w, offs, pre=pre, act="gelu")
+    p32 = pre.float().requires_grad_(True)
+    torch.nn.functional.gelu(p32).sum().backward()
+    for e, lo, hi in _segments(counts):
+        ref = dy[lo:hi].float() @ w[e].float()
+        assert torch.allclose(plain[lo:hi].float(), ref, atol=_tol(dtype, k), rtol=2e-2)
+        assert torch.allclose(fused[lo:hi].float(), ref * p32.grad[lo:hi], atol=_tol(dtype, k), rtol=2e-2)
+    assert _native().read_status(0) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("counts,m,n", [
+    ([64, 128], 128, 256),
+    ([100, 0, 37, 300], 64, 32),
+    ([1000, 24, 513], 256, 512),
+])
+def test_grouped_gemm_wgrad(dtype, counts, m, n):
+    from fastmoe_b200.ops import grouped_gemm as gg
+    torch.manual_seed(2)
+    rows = sum(counts)
+    pad = 70  # garbage rows after the last segment must not leak into the last expert
+    dy = torch.randn(rows + pad, m, device=DEV, dtype=dtype)
+    x = torch.randn(rows + pad, n, device=DEV, dtype=dtype)
+    dy[rows:] = float("nan")
+    x[rows:] = float("nan")
+    offs = _offs(counts)
+    out = gg.wgrad(dy, x, offs, len(counts))
+    for e, lo, hi in _segments(counts):
+        ref = dy[lo:hi].float().t() @ x[lo:hi].float()
+        scale = max(1.0, (hi - lo) ** 0.5)
+        assert torch.allclose(out[e].float(), ref, atol=_tol(dtype, hi - lo) * scale, rtol=2e-2), e
+    bg = gg.bias_grad(dy[:rows].contiguous(), offs)
+    for e, lo, hi in _segments(counts):
+        ref = dy[lo:hi].float().sum(0)
+        assert torch.allclose(bg[e].float(), ref, atol=0.3, rtol=2e-2)
+    assert _native().read_status(0) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_simt_grouped_linear(dtype):
+    from fastmoe_b200.ops import grouped_gemm as gg
+    torch.manual_seed(3)
+    counts = [5, 0, 9, 3]
+    rows, k, n = sum(counts), 16, 24
+    x = torch.randn(rows, k, device=DEV, dtype=dtype)
+    w = torch.randn(len(counts), n, k, device=DEV, dtype=dtype)
+    b = torch.randn(len(counts), n, device=DEV, dtype=dtype)
+    go = torch.randn(rows, n, device=DEV, dtype=dtype)
+    cnt = torch.tensor(counts)
+    out = gg.linear_forward_host_counts(x, cnt, w, b)
+    gi, gw, gb = gg.linear_backward_host_counts(go, x, cnt, w, b)
+    for e, lo, hi in _segments(counts):
+        assert torch.allclose(out[lo:hi], x[lo:hi] @ w[e].t() + b[e], atol=1e-4)
+        assert torch.allclose(gi[lo:hi], go[lo:hi] @ w[e], atol=1e-4)
+        assert torch.allclose(gw[e], go[lo:hi].t() @ x[lo:hi], atol=1e-4)
+        assert torch.allclose(gb[e], go[lo:hi].sum(0), atol=1e-4)
+
+
+@pytest.mark.parametrize("n_slots,tot", [(7, 3), (64, 4), (8192, 16), (50001, 64), (4096, 1024)])
+def test_route_matches_cpu(n_slots, tot):
+    from fastmoe_b200.ops import torch_impl
+    torch.manual_seed(4)
+    idx = torch.randint(-1, tot, (n_slots,), device=DEV)
+    counts, rank, offs = _native().route_offs(idx, tot)
+    ref_counts = torch_impl.expert_count(idx.cpu(), tot)
+    ref_rank = torch_impl.slot_rank(idx.cpu(), tot)
+    assert torch.equal(counts.cpu(), ref_counts)
+    assert torch.equal(rank.cpu().long(), ref_rank)
+    assert torch.equal(offs.cpu()[1:].long(), torch.cumsum(ref_counts.long(), 0))
+
+
+def test_capacity_kernels_match_cpu():
+    from fastmoe_b200.ops import api, torch_impl
+    torch.manual_seed(5)
+    n_expert, n_worker = 4, 3
+    ec = torch.randint(0, 20, (n_expert * n_worker,), dtype=torch.int64)
+    cap = torch.full((n_expert,), 25, dtype=torch.int32)
+    ref = torch_impl.limit_by_capacity(ec.clone(), cap.clone(), n_expert, n_worker)
+    cap_d = cap.to(DEV)
+    got = api.limit_by_capacity(ec.to(DEV), cap_d, n_expert, n_worker)
+    assert torch.equal(got.cpu(), ref)
+    idx = torch.randint(-1, n_expert * n_worker, (100, 2))
+    capg = torch.randint(0, 12, (n_expert * n_worker,), dtype=torch.int32)
+    ref_idx = torch_impl.prune_gate_by_capacity(idx.clone(), capg.clone(), n_expert, n_worker)
+    got_idx = api.prune_gate_by_capacity(idx.to(DEV), capg.to(DEV), n_expert, n_worker)
+    assert torch.equal(got_idx.cpu(), ref_idx)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scatter_combine_roundtrip(dtype):
+    torch.manual_seed(6)
+    nat = _native()
+    n_tok, k, d, tot = 300, 2, 256, 8
+    x = torch.randn(n_tok, d, device=DEV, dtype=dtype)
+    idx = torch.randint(-1, tot, (n_tok * k,), device=DEV)
+    score = torch.rand(n_tok * k, device=DEV).to(dtype)
+    counts, rank, offs = nat.route_offs(idx, tot)
+    rows = torch.full((n_tok * k, d), float("nan"), device=DEV, dtype=dtype)
+    row_slot = torch.full((n_tok * k,), -1, device=DEV, dtype=torch.int32)
+    nat.scatter_rows(x, idx, rank, offs, None, k, rows, row_slot)
+    n_valid = int(offs[-1])
+    slots = row_slot[:n_valid].long()
+    assert torch.equal(rows[:n_valid], x[slots // k])
+    # rows are grouped by expert, ascending slot inside an expert
+    assert torch.equal(idx[slots], torch.sort(idx[idx >= 0], stable=True).values)
+    out = torch.empty(n_tok, d, device=DEV, dtype=dtype)
+    nat.gather_combine(rows, idx, rank, offs, score, k, out)
+    w = torch.where(idx >= 0, score.float(), torch.zeros_like(score, dtype=torch.float32))
+    ref = (x.float().repeat_interleave(k, 0) * w[:, None]).view(n_tok, k, d).sum(1)
+    assert torch.allclose(out.float(), ref, atol=3e-2, rtol=2e-2)
+    # backward of the weighted combine
+    dout = torch.randn(n_tok, d, device=DEV, dtype=dtype)
+    drows = torch.zeros_like(rows)
+    dscore = torch.empty(n_tok * k, device=DEV, dtype=dtype)
+    nat.combine_bwd(dout, rows, idx, rank, offs, score, k, drows, dscore)
+    ref_ds = (dout.float().repeat_interleave(k, 0) * x.float().repeat_interleave(k, 0)).sum(1)
+    ref_ds = torch.where(idx >= 0, ref_ds, torch.zeros_like(ref_ds))
+    assert torch.allclose(dscore.float(), ref_ds, atol=0.25, rtol=2e-2)
+    ref_dr = dout.float().repeat_interleave(k, 0)[slots] * score.float()[slots][:, None]
+    assert torch.allclose(drows[:n_valid].float(), ref_dr, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_exp,k", [(16, 2), (4, 1), (64, 3), (200, 8)])
+def test_gate_topk_softmax(dtype, n_exp, k):
+    from fastmoe_b200.ops import gating
+    torch.manual_seed(7)
+    logits = torch.randn(500, n_exp, device=DEV, dtype=dtype).requires_grad_(True)
+    idx, prob = gating.topk_softmax(logits, k)
+    ref_l = logits.detach().float().requires_grad_(True)
+    rv, ri = torch.topk(ref_l, k, dim=-1)
+    rp = torch.softmax(rv, -1)
+    assert torch.equal(idx, ri)
+    assert torch.allclose(prob.float(), rp, atol=1e-2 if dtype != torch.float32 else 1e-5)
+    g = torch.randn_like(prob)
+    prob.backward(g)
+    rp.backward(g.float())
+    assert torch.allclose(logits.grad.float(), ref_l.grad, atol=2e-2 if dtype != torch.float32 else 1e-5)
