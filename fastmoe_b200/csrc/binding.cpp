@@ -185,6 +185,11 @@ void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor 
     TORCH_CHECK(out.size(0) == a.size(0) && out.size(1) == g.n, "out shape");
     TORCH_CHECK(out.scalar_type() == a.scalar_type(), "out dtype");
   }
+  auto aligned32 = [](const torch::Tensor& t) {
+    return reinterpret_cast<uintptr_t>(t.data_ptr()) % 32 == 0;
+  };
+  TORCH_CHECK(aligned32(a) && aligned32(b) && aligned32(out),
+              "grouped_gemm: operands must be 32-byte aligned");
   g.a = a.data_ptr();
   g.b = b.data_ptr();
   g.offs = offs.data_ptr<int>();
@@ -192,14 +197,17 @@ void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor 
   if (bias.has_value() && bias->defined()) {
     check_cuda_contig(*bias, "bias");
     TORCH_CHECK(bias->scalar_type() == a.scalar_type(), "bias dtype");
+    TORCH_CHECK(aligned32(*bias), "grouped_gemm: bias must be 32-byte aligned");
     g.bias = bias->data_ptr();
   }
   if (pre_out.has_value() && pre_out->defined()) {
     check_cuda_contig(*pre_out, "pre_out");
+    TORCH_CHECK(aligned32(*pre_out), "grouped_gemm: pre_out must be 32-byte aligned");
     g.pre_out = pre_out->data_ptr();
   }
   if (aux.has_value() && aux->defined()) {
     check_cuda_contig(*aux, "aux");
+    TORCH_CHECK(aligned32(*aux), "grouped_gemm: aux must be 32-byte aligned");
     g.aux = aux->data_ptr();
   }
   g.act = static_cast<int>(act);

@@ -29,7 +29,7 @@ def offsets_from_counts(counts, device):
 
 def _tc_ok(t, mode, m, n, k, groups):
     return (t.dtype in _TC and native.get().grouped_gemm_supported(mode, m, n, k, groups)
-            and t.data_ptr() % 16 == 0)
+            and t.data_ptr() % 32 == 0)
 
 
 def forward(x, weight, offs, bias=None, act=None, want_pre=False):
@@ -83,7 +83,7 @@ def wgrad(dy, x, offs, groups, out=None, accumulate=False):
     if out is None:
         out = torch.empty(groups, m, n, dtype=dy.dtype, device=dy.device)
         accumulate = False
-    if _tc_ok(dy, MODE_WGRAD, m, n, 0, groups) and x.data_ptr() % 16 == 0:
+    if _tc_ok(dy, MODE_WGRAD, m, n, 0, groups) and x.data_ptr() % 32 == 0:
         nat.grouped_gemm(MODE_WGRAD, dy, x, offs, out, None, None, None, 0, 0, accumulate)
     else:
         tmp = torch.empty(groups, m, n, dtype=dy.dtype, device=dy.device)
