@@ -1,0 +1,315 @@
+r"""
+Headline benchmark: expert-parallel MoE MLP layer, forward + backward, tokens/s.
+
+Config (fixed): bf16, 4096 tokens per GPU, d_model 1024, d_hidden 4096, 2 experts per GPU,
+NaiveGate top-2 with a random-init gate, GELU; synthetic N(0,1) inputs, random-init weights.
+One step = forward, backward, gradient all-reduce of the replicated (gate) parameters when
+N > 1, and a fused Adam step on all parameters.  Weak scaling: per-GPU work is fixed.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5            # this framework
+    python bench.py --impl reference ...                      # unmodified FastMoE from baseline/_ref
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N ...                 # N > 1
+
+Timing: after W warm-up steps, every step is bracketed by CUDA events on the launching stream;
+an L2 flush (a 256 MiB fill) runs between steps outside the events; the K per-step times are
+summed per rank and the maximum over ranks is reported.  The end-to-end number re-runs the K
+steps through the same public call with, per step, a host-to-device copy of the inputs from
+pinned memory and a device-to-host read of the loss inside the timed region.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+TOKENS_PER_GPU = 4096
+D_MODEL = 1024
+D_HIDDEN = 4096
+EXPERTS_PER_GPU = 2
+TOP_K = 2
+METRIC = "moe_fwd_bwd_tokens_per_s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    return ap.parse_args()
+
+
+def emit(obj):
+    print(json.dumps(obj), flush=True)
+
+
+# ------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    r"""Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------ the two arms
+def build_ours(rank, world, device):
+    import torch
+    sys.path.insert(0, ROOT)
+    from fastmoe_b200 import DistributedGroupedDataParallel, FMoETransformerMLP
+    from fastmoe_b200.gates import NaiveGate
+    from fastmoe_b200.ops import native
+    native.get()  # fail loudly if the extension is missing
+    torch.manual_seed(1234 + rank)
+    layer = FMoETransformerMLP(num_expert=EXPERTS_PER_GPU, d_model=D_MODEL, d_hidden=D_HIDDEN,
+                               world_size=world, top_k=TOP_K, gate=NaiveGate,
+                               activation=torch.nn.GELU()).to(device).to(torch.bfloat16)
+    model = layer
+    if world > 1:
+        model = DistributedGroupedDataParallel(layer)
+    return layer, model, (lambda: native.get().launch_count())
+
+
+def build_reference(rank, world, device):
+    import torch
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    shim_dir = os.path.join(ROOT, "baseline", "shims")
+    # The reference imports `tree` (dm-tree), which is not installed: a small pure-python
+    # stand-in lives in baseline/shims.  Nothing of this repository's package is imported.
+    sys.path.insert(0, shim_dir)
+    sys.path.insert(0, ref_dir)
+    from fmoe import FMoETransformerMLP  # noqa: E402  (the reference's own package)
+    from fmoe.distributed import DistributedGroupedDataParallel
+    from fmoe.gates import NaiveGate
+    assert os.path.realpath(sys.modules["fmoe"].__file__).startswith(os.path.realpath(ref_dir))
+    torch.manual_seed(1234 + rank)
+    layer = FMoETransformerMLP(num_expert=EXPERTS_PER_GPU, d_model=D_MODEL, d_hidden=D_HIDDEN,
+                               world_size=world, top_k=TOP_K, gate=NaiveGate,
+                               activation=torch.nn.GELU()).to(device).to(torch.bfloat16)
+    model = layer
+    if world > 1:
+        model = DistributedGroupedDataParallel(layer)
+    return layer, model, (lambda: 0)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "fmoe")):
+        emit({"impl": "reference", "unavailable": "baseline/_ref is not installed"})
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    try:
+        build = build_reference if args.impl == "reference" else build_ours
+        layer, model, launch_counter = build(rank, world, device)
+    except Exception as exc:  # pylint: disable=broad-except
+        if args.impl == "reference":
+            if rank == 0:
+                emit({"impl": "reference", "unavailable": "reference failed to start: %r" % (exc,)})
+            return
+        raise
+
+    graphed = args.impl == "ours" and os.environ.get("FMOE_BENCH_GRAPH", "1") == "1"
+    opt = torch.optim.Adam(layer.parameters(), lr=1e-4, fused=True, capturable=graphed)
+    n_inputs = 4
+    gen = torch.Generator(device="cpu").manual_seed(99 + rank)
+    host_inputs = [torch.randn(TOKENS_PER_GPU, D_MODEL, generator=gen).to(torch.bfloat16).pin_memory()
+                   for _ in range(n_inputs)]
+    dev_inputs = [h.to(device) for h in host_inputs]
+    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
+
+    def step(x):
+        opt.zero_grad(set_to_none=True)
+        x = x.detach().requires_grad_(True)
+        y = model(x)
+        loss = y.sum()
+        loss.backward()
+        if world > 1:
+            model.allreduce_params()
+        opt.step()
+        return loss
+
+    if graphed:
+        # The fused path has no host read, so the whole step is captured into one CUDA graph
+        # through the framework's public helper; inputs are copied into its static buffer.
+        from fastmoe_b200.utils.graph import GraphedStep
+        eager_step = step
+        count0 = launch_counter()
+        stepper = GraphedStep(lambda x: eager_step(x), dev_inputs[0], warmup=3)
+        # Replays do not pass through the Python bindings that count launches: one replay
+        # launches what one eager step launched (3 warm-up runs + 1 captured run were counted).
+        launches_per_step = (launch_counter() - count0) // 4
+
+        def step(x):  # noqa: F811
+            return stepper(x)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    try:
+        # At least W warm-up steps, and at least ~1 s of them so that clocks have ramped up.
+        warm_done = 0
+        t_warm = time.perf_counter()
+        while warm_done < max(args.warmup, 3) or time.perf_counter() - t_warm < 1.0:
+            step(dev_inputs[warm_done % n_inputs])
+            warm_done += 1
+            if warm_done % 8 == 0:
+                torch.cuda.synchronize()
+        barrier()
+    except Exception as exc:  # pylint: disable=broad-except
+        if args.impl == "reference":
+            if rank == 0:
+                emit({"impl": "reference", "unavailable": "reference step failed: %r" % (exc,)})
+            return
+        raise
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    # ------------------------------------------------ device-timed region (inputs resident)
+    launches_before = launch_counter()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        flush.fill_(float(i))
+        starts[i].record()
+        step(dev_inputs[i % n_inputs])
+        ends[i].record()
+    barrier()
+    launches = launch_counter() - launches_before
+    if graphed:
+        launches = launches_per_step * args.steps
+    dev_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+
+    # ------------------------------------------------ end-to-end region (H2D inputs, D2H loss)
+    staging = torch.empty_like(dev_inputs[0])
+    barrier()
+    e2e_ms = 0.0
+    loss_host = 0.0
+    for i in range(args.steps):
+        flush.fill_(float(i))
+        s_ev = torch.cuda.Event(enable_timing=True)
+        e_ev = torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        s_ev.record()
+        if graphed:
+            stepper.static_input.copy_(host_inputs[i % n_inputs], non_blocking=True)
+            loss = stepper(None)
+        else:
+            staging.copy_(host_inputs[i % n_inputs], non_blocking=True)
+            loss = step(staging)
+        loss_host = float(loss.item())       # device -> host read of the step's result
+        e_ev.record()
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) * 1e3
+        e2e_ms += max(s_ev.elapsed_time(e_ev), wall)
+    barrier()
+
+    clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = float(times[0]), float(times[1])
+
+    if rank == 0:
+        tokens = TOKENS_PER_GPU * world * args.steps
+        value = tokens / (dev_ms / 1e3)
+        e2e_value = tokens / (e2e_ms / 1e3)
+        flops_per_step = 3 * 2 * 2 * TOKENS_PER_GPU * TOP_K * D_MODEL * D_HIDDEN * world
+        out = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm_done,
+            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1) inputs, random-init weights",
+            "impl": args.impl,
+            "tflops": flops_per_step / (dev_ms / args.steps / 1e3) / 1e12,
+            "config": {
+                "model": "FMoETransformerMLP (EP MoE MLP layer, NaiveGate top-2, GELU)",
+                "tokens_per_gpu": TOKENS_PER_GPU, "global_batch": TOKENS_PER_GPU * world,
+                "seq_len": 1, "d_model": D_MODEL, "d_hidden": D_HIDDEN,
+                "experts_per_gpu": EXPERTS_PER_GPU, "top_k": TOP_K,
+                "parallelism": "ep%d" % world,
+                "step": "fwd+bwd+gate-grad-allreduce+fused-adam",
+                "cuda_graph": bool(graphed),
+                "l2": "flushed between timed steps (256 MiB fill outside the events)",
+            },
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s",
+                    "h2d_bytes_per_step": TOKENS_PER_GPU * D_MODEL * 2,
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps,
+                    "last_loss": loss_host},
+            "gpu_launches": int(launches),
+        }
+        emit(out)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -10,6 +10,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
 
@@ -27,7 +28,13 @@ namespace {
                 cudaGetErrorString(_e));                                            \
   } while (0)
 
-cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+// Number of kernels of this library launched by this process (benchmarks report it).
+std::atomic<int64_t> g_launches{0};
+
+cudaStream_t cur_stream() {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return at::cuda::getCurrentCUDAStream().stream();
+}
 
 int dtype16(const torch::Tensor& t) {
   if (t.scalar_type() == torch::kBFloat16) return fmoe::kBF16;
@@ -379,6 +386,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colsum", &colsum);
   m.def("gate_topk_softmax", &gate_topk_softmax);
   m.def("gate_topk_softmax_bwd", &gate_topk_softmax_bwd);
+  m.def("launch_count", []() { return g_launches.load(); });
   m.def("read_status", &read_status);
   m.def("clear_status", &clear_status);
   m.def("status_word", &status_word);

@@ -22,7 +22,7 @@ class NaiveGate(BaseGate):
         logits = self.gate(inp)
         idx, score = gating.topk_softmax(logits.view(-1, self.tot_expert), self.top_k)
         # The reference installs a zero "dummy" loss so that callers can always add it.
-        self.set_loss(torch.zeros(1, requires_grad=True, device=inp.device))
+        self.set_loss(torch.zeros(1, device=inp.device, requires_grad=True))
         if return_all_scores:
             return idx, score, logits
         return idx, score
