@@ -1,0 +1,505 @@
+// Peer-to-peer exchange kernels: see p2p.cuh for the contract of each launcher.
+//
+// Memory model.  Data rows are written into a peer's memory with ordinary 16-byte stores;
+// a producer then executes a system-scope fence and a release store of the exchange epoch
+// into the consumer's flag word; the consumer polls that word with acquire loads.  Epochs
+// only grow, live in device memory and are advanced by the kernels themselves, so the same
+// launch sequence can be replayed from a CUDA graph.  A wait gives up after
+// `timeout_ns`, records kStatusPeerTimeout and lets the kernel finish.
+#include "p2p.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace fmoe {
+namespace {
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ int* flag_of(void* signal_base, int channel, int src) {
+  return static_cast<int*>(signal_base) + channel * kMaxPeers + src;
+}
+
+// Polls my flag of `src` on `channel` until it reaches `target`.  False on time-out or when
+// the status word already reports a failure (so that one failure does not cost a full
+// time-out in every later wait of the step).
+__device__ __forceinline__ bool wait_flag(const ExchangeCtx& c, int channel, int src, int target) {
+  const int* f = flag_of(c.flags.p[c.me], channel, src);
+  if (ld_acquire_sys(f) - target >= 0) return true;
+  const unsigned long long t0 = now_ns();
+  unsigned spins = 0;
+  while (true) {
+    if (ld_acquire_sys(f) - target >= 0) return true;
+    if ((++spins & 0xff) == 0) {
+      if (*reinterpret_cast<volatile int*>(c.status) != 0) return false;
+      if (now_ns() - t0 > c.timeout_ns) {
+        atomicCAS(c.status, 0, kStatusPeerTimeout);
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+}
+
+// All threads of the block call this; threads 0..world-1 each wait for one peer.
+__device__ __forceinline__ void block_wait_all(const ExchangeCtx& c, int channel, int target) {
+  if (static_cast<int>(threadIdx.x) < c.world) wait_flag(c, channel, threadIdx.x, target);
+  __syncthreads();
+}
+
+// Called by one thread after the whole grid's stores are ordered before it.
+__device__ __forceinline__ void signal_all(const ExchangeCtx& c, int channel, int value) {
+  __threadfence_system();
+  for (int p = 0; p < c.world; ++p) st_release_sys(flag_of(c.flags.p[p], channel, c.me), value);
+}
+
+// Grid-wide "I am the last CTA" test on a counter in local memory (reset for the next use).
+__device__ __forceinline__ bool last_block(int* counter) {
+  __shared__ int is_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(counter, 1);
+    is_last = (prev == static_cast<int>(gridDim.x) - 1);
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  return is_last != 0;
+}
+
+// ------------------------------------------------------------------------------ counts
+__global__ void __launch_bounds__(1024, 1)
+count_exchange_kernel(ExchangeCtx c, const int* __restrict__ lec, PeerPtrs cnt, int n_expert,
+                      int capacity_rows, int* __restrict__ dst_base, int* __restrict__ expert_offs,
+                      int* __restrict__ total_rows) {
+  extern __shared__ int sh[];  // [world * tot] matrix, then [tot] column sums
+  const int tot = n_expert * c.world;
+  const int epoch = c.epoch[0] + 1;
+  // 1. my row into every peer's matrix
+  for (int g = threadIdx.x; g < tot; g += blockDim.x) {
+    const int v = lec[g];
+    for (int p = 0; p < c.world; ++p) static_cast<int*>(cnt.p[p])[c.me * tot + g] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < c.world) {
+    st_release_sys(flag_of(c.flags.p[threadIdx.x], kChanCounts, c.me), epoch);
+  }
+  // 2. everybody's rows
+  block_wait_all(c, kChanCounts, epoch);
+  const volatile int* mine = static_cast<const volatile int*>(cnt.p[c.me]);
+  int* mat = sh;
+  int* col = sh + c.world * tot;
+  for (int i = threadIdx.x; i < c.world * tot; i += blockDim.x) mat[i] = mine[i];
+  __syncthreads();
+  for (int g = threadIdx.x; g < tot; g += blockDim.x) {
+    int s = 0;
+    for (int w = 0; w < c.world; ++w) s += mat[w * tot + g];
+    col[g] = s;
+  }
+  __syncthreads();
+  // 3. offsets.  Receive layout on every rank: local expert outer, source rank inner.
+  for (int g = threadIdx.x; g < tot; g += blockDim.x) {
+    const int p = g / n_expert;
+    const int e = g - p * n_expert;
+    int base = 0;
+    for (int e2 = 0; e2 < e; ++e2) base += col[p * n_expert + e2];
+    for (int w = 0; w < c.me; ++w) base += mat[w * tot + g];
+    dst_base[g] = base;
+  }
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < n_expert; ++e) {
+      expert_offs[e] = run;
+      run += col[c.me * n_expert + e];
+    }
+    expert_offs[n_expert] = run < capacity_rows ? run : capacity_rows;
+    total_rows[0] = expert_offs[n_expert];
+    // Overflow anywhere is visible to everybody (same matrix): report it on every rank.
+    for (int p = 0; p < c.world; ++p) {
+      int t = 0;
+      for (int e = 0; e < n_expert; ++e) t += col[p * n_expert + e];
+      if (t > capacity_rows) atomicCAS(c.status, 0, kStatusRecvOverflow);
+    }
+    if (run > capacity_rows) {
+      // Clamp the local expert segments to the buffer.
+      for (int e = 0; e <= n_expert; ++e) {
+        if (expert_offs[e] > capacity_rows) expert_offs[e] = capacity_rows;
+      }
+    }
+    c.epoch[0] = epoch;
+  }
+}
+
+__global__ void begin_epoch_kernel(ExchangeCtx c) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) c.epoch[0] = c.epoch[0] + 1;
+}
+
+// ------------------------------------------------------------------------------ row helpers
+template <typename T> struct V2;
+template <> struct V2<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ float2 to_f2(type v) { return __bfloat1622float2(v); }
+  static __device__ __forceinline__ type from_f2(float a, float b) { return __floats2bfloat162_rn(a, b); }
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16(v); }
+};
+template <> struct V2<__half> {
+  using type = __half2;
+  static __device__ __forceinline__ float2 to_f2(type v) { return __half22float2(v); }
+  static __device__ __forceinline__ type from_f2(float a, float b) { return __floats2half2_rn(a, b); }
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half(v); }
+};
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
+  using P = typename V2<T>::type;
+  const P* p = reinterpret_cast<const P*>(&w);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 v = V2<T>::to_f2(p[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  using P = typename V2<T>::type;
+  uint4 w;
+  P* p = reinterpret_cast<P*>(&w);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = V2<T>::from_f2(f[2 * i], f[2 * i + 1]);
+  return w;
+}
+
+// ------------------------------------------------------------------------------ dispatch
+// One warp per slot, persistent grid.  Stores go to the owner's staging buffer over NVLink.
+template <typename T>
+__global__ void dispatch_push_kernel(ExchangeCtx c, const T* __restrict__ x,
+                                     const int64_t* __restrict__ idx, const int* __restrict__ rank,
+                                     const int* __restrict__ dst_base, const T* __restrict__ scale,
+                                     PeerPtrs rows, PeerPtrs meta, int n_expert, int n_slots, int k,
+                                     int d, int capacity_rows) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int nv = d >> 3;
+  for (int s = blockIdx.x * warps_per_block + (threadIdx.x >> 5); s < n_slots;
+       s += gridDim.x * warps_per_block) {
+    const long g = idx[s];
+    if (g < 0) continue;
+    const int p = static_cast<int>(g / n_expert);
+    const long row = static_cast<long>(dst_base[g]) + rank[s];
+    if (row >= capacity_rows) continue;  // overflow is reported by the count exchange
+    const uint4* in = reinterpret_cast<const uint4*>(x + static_cast<long>(s / k) * d);
+    uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(rows.p[p]) + row * d);
+    if (scale == nullptr) {
+      for (int i = lane; i < nv; i += 32) out[i] = __ldg(in + i);
+    } else {
+      const float sc = V2<T>::to_f(scale[s]);
+      for (int i = lane; i < nv; i += 32) {
+        float f[8];
+        unpack8<T>(__ldg(in + i), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] *= sc;
+        out[i] = pack8<T>(f);
+      }
+    }
+    if (lane == 0 && meta.p[p] != nullptr) {
+      static_cast<int64_t*>(meta.p[p])[row] = (static_cast<int64_t>(c.me) << 32) | static_cast<int64_t>(s);
+    }
+  }
+  if (last_block(c.epoch + 1)) {
+    if (threadIdx.x == 0) signal_all(c, kChanDispatch, c.epoch[0]);
+  }
+}
+
+template <typename T>
+__global__ void wait_copy_kernel(ExchangeCtx c, int channel, const T* __restrict__ stage_rows,
+                                 const int64_t* __restrict__ stage_meta,
+                                 const int* __restrict__ total_rows, int d, int capacity_rows,
+                                 T* __restrict__ out_rows, int64_t* __restrict__ out_meta) {
+  block_wait_all(c, channel, c.epoch[0]);
+  int n_rows = total_rows[0];
+  if (n_rows > capacity_rows) n_rows = capacity_rows;
+  const long nv = static_cast<long>(n_rows) * (d >> 3);
+  const uint4* in = reinterpret_cast<const uint4*>(stage_rows);
+  uint4* out = reinterpret_cast<uint4*>(out_rows);
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    out[i] = __ldcg(in + i);
+  }
+  if (out_meta != nullptr) {
+    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n_rows;
+         i += static_cast<long>(gridDim.x) * blockDim.x) {
+      out_meta[i] = __ldcg(stage_meta + i);
+    }
+  }
+}
+
+// One warp per received row.
+template <typename T>
+__global__ void return_push_kernel(ExchangeCtx c, const T* __restrict__ rows_in,
+                                   const int64_t* __restrict__ meta,
+                                   const int* __restrict__ total_rows, PeerPtrs ret, int d,
+                                   int capacity_rows) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  int n_rows = total_rows[0];
+  if (n_rows > capacity_rows) n_rows = capacity_rows;
+  const int nv = d >> 3;
+  for (int r = blockIdx.x * warps_per_block + (threadIdx.x >> 5); r < n_rows;
+       r += gridDim.x * warps_per_block) {
+    const int64_t m = meta[r];
+    const int src = static_cast<int>(m >> 32);
+    const long slot = static_cast<long>(m & 0xffffffffll);
+    if (src < 0 || src >= c.world) continue;
+    const uint4* in = reinterpret_cast<const uint4*>(rows_in + static_cast<long>(r) * d);
+    uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(ret.p[src]) + slot * d);
+    for (int i = lane; i < nv; i += 32) out[i] = __ldg(in + i);
+  }
+  if (last_block(c.epoch + 2)) {
+    if (threadIdx.x == 0) signal_all(c, kChanReturn, c.epoch[0]);
+  }
+}
+
+// One warp per token.
+template <typename T>
+__global__ void wait_combine_kernel(ExchangeCtx c, const T* __restrict__ ret,
+                                    const int64_t* __restrict__ idx, const T* __restrict__ weight,
+                                    int n_tokens, int k, int d, T* __restrict__ out,
+                                    T* __restrict__ keep) {
+  block_wait_all(c, kChanReturn, c.epoch[0]);
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int nv = d >> 3;
+  for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < n_tokens;
+       t += gridDim.x * warps_per_block) {
+    uint4* o = reinterpret_cast<uint4*>(out + static_cast<long>(t) * d);
+    for (int i = lane; i < nv; i += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < k; ++j) {
+        const long s = static_cast<long>(t) * k + j;
+        if (idx[s] < 0) continue;
+        const uint4 w4 = __ldcg(reinterpret_cast<const uint4*>(ret + s * d) + i);
+        if (keep != nullptr) reinterpret_cast<uint4*>(keep + s * d)[i] = w4;
+        const float w = weight != nullptr ? V2<T>::to_f(weight[s]) : 1.f;
+        float f[8];
+        unpack8<T>(w4, f);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += w * f[q];
+      }
+      o[i] = pack8<T>(acc);
+    }
+  }
+}
+
+template <typename T>
+__global__ void slot_dot_kernel(const T* __restrict__ dout, const T* __restrict__ y,
+                                const int64_t* __restrict__ idx, int n_slots, int k, int d,
+                                T* __restrict__ dscore) {
+  const int s = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (s >= n_slots) return;
+  float dot = 0.f;
+  if (idx[s] >= 0) {
+    const uint4* g = reinterpret_cast<const uint4*>(dout + static_cast<long>(s / k) * d);
+    const uint4* v = reinterpret_cast<const uint4*>(y + static_cast<long>(s) * d);
+    for (int i = lane; i < (d >> 3); i += 32) {
+      float gf[8], yf[8];
+      unpack8<T>(__ldg(g + i), gf);
+      unpack8<T>(__ldg(v + i), yf);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) dot += gf[q] * yf[q];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (lane == 0) dscore[s] = V2<T>::from_f(dot);
+}
+
+// ------------------------------------------------------------------------------ all-reduce
+__device__ __forceinline__ float as_float(float v) { return v; }
+__device__ __forceinline__ float as_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float as_float(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half(v); }
+
+// One-shot: after everybody published "my buffer is filled", every rank reads all peers'
+// buffers in rank order (so all ranks compute bit-identical sums), scales and writes its own
+// output; the kernel leaves only when every peer has finished reading this rank's buffer.
+template <typename T, typename Vec, int PER>
+__global__ void allreduce_kernel(ExchangeCtx c, PeerPtrs bufs, T* __restrict__ out, long n,
+                                 float scale) {
+  const int target_ready = 2 * c.epoch[0];
+  if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(c, kChanReduce, target_ready);
+  block_wait_all(c, kChanReduce, target_ready);
+  const long nvec = n / PER;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float acc[PER];
+#pragma unroll
+    for (int q = 0; q < PER; ++q) acc[q] = 0.f;
+    for (int p = 0; p < c.world; ++p) {
+      Vec v = __ldcg(reinterpret_cast<const Vec*>(bufs.p[p]) + i);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int q = 0; q < PER; ++q) acc[q] += as_float(e[q]);
+    }
+    Vec r;
+    T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+    for (int q = 0; q < PER; ++q) e[q] = from_float<T>(acc[q] * scale);
+    reinterpret_cast<Vec*>(out)[i] = r;
+  }
+  // tail elements
+  for (long i = nvec * PER + blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float acc = 0.f;
+    for (int p = 0; p < c.world; ++p) acc += as_float(static_cast<const T*>(bufs.p[p])[i]);
+    out[i] = from_float<T>(acc * scale);
+  }
+  if (last_block(c.epoch + 3)) {
+    if (threadIdx.x == 0) signal_all(c, kChanReduce, target_ready + 1);
+    block_wait_all(c, kChanReduce, target_ready + 1);
+  }
+}
+
+__global__ void wait_only_kernel(ExchangeCtx c, int channel) {
+  // Waits for an epoch nobody will publish: exercises the time-out path.
+  block_wait_all(c, channel, c.epoch[0] + 1000000);
+}
+
+int push_grid(int work_items, int warps_per_block) {
+  int blocks = (work_items + warps_per_block - 1) / warps_per_block;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  return blocks;
+}
+
+}  // namespace
+
+#define FMOE_P2P_16(dtype, ...)                                        \
+  if ((dtype) == 0) { using T = __nv_bfloat16; __VA_ARGS__; }          \
+  else { using T = __half; __VA_ARGS__; }
+
+cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const PeerPtrs& cnt,
+                                  int n_expert, int capacity_rows, int* dst_base,
+                                  int* expert_offs, int* total_rows, cudaStream_t stream) {
+  const int tot = n_expert * ctx.world;
+  const size_t smem = static_cast<size_t>(ctx.world + 1) * tot * sizeof(int);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(count_exchange_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+  }
+  count_exchange_kernel<<<1, 1024, smem, stream>>>(ctx, lec, cnt, n_expert, capacity_rows, dst_base,
+                                                   expert_offs, total_rows);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_begin_epoch(const ExchangeCtx& ctx, cudaStream_t stream) {
+  begin_epoch_kernel<<<1, 32, 0, stream>>>(ctx);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dispatch_push(const ExchangeCtx& ctx, int dtype, const void* x,
+                                 const int64_t* idx, const int* rank, const int* dst_base,
+                                 const void* scale, const PeerPtrs& rows, const PeerPtrs& meta,
+                                 int n_expert, int n_slots, int k, int d, int capacity_rows,
+                                 cudaStream_t stream) {
+  if (d % 8 != 0) return cudaErrorInvalidValue;
+  const int wpb = 8;
+  FMOE_P2P_16(dtype, (dispatch_push_kernel<T><<<push_grid(n_slots, wpb), wpb * 32, 0, stream>>>(
+      ctx, static_cast<const T*>(x), idx, rank, dst_base, static_cast<const T*>(scale), rows, meta,
+      n_expert, n_slots, k, d, capacity_rows)));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_copy(const ExchangeCtx& ctx, int channel, int dtype, const void* stage_rows,
+                             const int64_t* stage_meta, const int* total_rows, int d,
+                             int capacity_rows, void* out_rows, int64_t* out_meta,
+                             cudaStream_t stream) {
+  if (d % 8 != 0) return cudaErrorInvalidValue;
+  FMOE_P2P_16(dtype, (wait_copy_kernel<T><<<148 * 4, 256, 0, stream>>>(
+      ctx, channel, static_cast<const T*>(stage_rows), stage_meta, total_rows, d, capacity_rows,
+      static_cast<T*>(out_rows), out_meta)));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_return_push(const ExchangeCtx& ctx, int dtype, const void* rows,
+                               const int64_t* meta, const int* total_rows, const PeerPtrs& ret,
+                               int d, int capacity_rows, cudaStream_t stream) {
+  if (d % 8 != 0) return cudaErrorInvalidValue;
+  const int wpb = 8;
+  FMOE_P2P_16(dtype, (return_push_kernel<T><<<148 * 4, wpb * 32, 0, stream>>>(
+      ctx, static_cast<const T*>(rows), meta, total_rows, ret, d, capacity_rows)));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_combine(const ExchangeCtx& ctx, int dtype, const void* ret,
+                                const int64_t* idx, const void* weight, int n_tokens, int k, int d,
+                                void* out, void* keep, cudaStream_t stream) {
+  if (d % 8 != 0) return cudaErrorInvalidValue;
+  const int wpb = 8;
+  FMOE_P2P_16(dtype, (wait_combine_kernel<T><<<push_grid(n_tokens, wpb), wpb * 32, 0, stream>>>(
+      ctx, static_cast<const T*>(ret), idx, static_cast<const T*>(weight), n_tokens, k, d,
+      static_cast<T*>(out), static_cast<T*>(keep))));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_slot_dot(int dtype, const void* dout, const void* y, const int64_t* idx,
+                            int n_slots, int k, int d, void* dscore, cudaStream_t stream) {
+  if (n_slots == 0) return cudaSuccess;
+  if (d % 8 != 0) return cudaErrorInvalidValue;
+  const int wpb = 8;
+  FMOE_P2P_16(dtype, (slot_dot_kernel<T><<<(n_slots + wpb - 1) / wpb, wpb * 32, 0, stream>>>(
+      static_cast<const T*>(dout), static_cast<const T*>(y), idx, n_slots, k, d,
+      static_cast<T*>(dscore))));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_allreduce(const ExchangeCtx& ctx, int dtype, const PeerPtrs& bufs, void* out,
+                             long n, float scale, cudaStream_t stream) {
+  long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks < 1) blocks = 1;
+  const int grid = static_cast<int>(blocks);
+  if (dtype == 0) {
+    allreduce_kernel<__nv_bfloat16, uint4, 8><<<grid, 256, 0, stream>>>(
+        ctx, bufs, static_cast<__nv_bfloat16*>(out), n, scale);
+  } else if (dtype == 1) {
+    allreduce_kernel<__half, uint4, 8><<<grid, 256, 0, stream>>>(ctx, bufs, static_cast<__half*>(out),
+                                                               n, scale);
+  } else if (dtype == 2) {
+    allreduce_kernel<float, uint4, 4><<<grid, 256, 0, stream>>>(ctx, bufs, static_cast<float*>(out),
+                                                              n, scale);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_only(const ExchangeCtx& ctx, int channel, cudaStream_t stream) {
+  wait_only_kernel<<<1, 32, 0, stream>>>(ctx, channel);
+  return cudaGetLastError();
+}
+
+}  // namespace fmoe

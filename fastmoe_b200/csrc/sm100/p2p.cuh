@@ -1,4 +1,93 @@
-// Peer-to-peer (NVLink / NVSwitch) kernels: see p2p.cu.
+// Peer-to-peer (NVLink 5 / NVSwitch) kernels of the expert-parallel data path.
+//
+// They replace the reference's host-driven exchange — the NCCL all-to-all of counts
+// (cuda/global_exchange.cpp:9-46) and the per-(expert, peer) ncclSend/ncclRecv loops of
+// global_scatter / global_gather (cuda/global_exchange.h:11-100) — with kernels that store
+// straight into the peers' symmetric buffers and publish completion through flags.  No count
+// ever reaches the host, and every wait on a peer is bounded.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+namespace fmoe {
+
+constexpr int kMaxPeers = 16;
+
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+
+// Status codes written to the status word when something goes wrong (0 = fine).
+constexpr int kStatusPeerTimeout = 201;      // a peer's flag did not arrive in time
+constexpr int kStatusRecvOverflow = 202;     // more rows routed to a rank than its buffer holds
+
+// Flag channels inside the symmetric signal buffer: int32 [kNumChannels][kMaxPeers].
+constexpr int kChanCounts = 0;
+constexpr int kChanDispatch = 1;
+constexpr int kChanReturn = 2;
+constexpr int kChanReduce = 3;
+constexpr int kNumChannels = 4;
+
+struct ExchangeCtx {
+  PeerPtrs flags;        // each peer's signal buffer
+  int* epoch;            // local: [0] current epoch, [1] CTA completion counter (dispatch), [2] (return)
+  int me;
+  int world;
+  int* status;           // local status word
+  unsigned long long timeout_ns;
+};
+
+// Starts a new exchange epoch and (forward only) exchanges the routing counts:
+//   lec[tot]            my tokens per global expert
+//   cnt                 every peer's count matrix int32 [world][tot] (symmetric)
+// Outputs, all in local memory:
+//   dst_base[tot]       first row of my rows inside the owner's receive buffer, per global expert
+//   expert_offs[E + 1]  row offsets of my local experts inside my receive buffer
+//   total_rows[1]
+cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const PeerPtrs& cnt,
+                                  int n_expert, int capacity_rows, int* dst_base,
+                                  int* expert_offs, int* total_rows, cudaStream_t stream);
+
+// Backward passes reuse the forward routing: only the epoch advances.
+cudaError_t launch_begin_epoch(const ExchangeCtx& ctx, cudaStream_t stream);
+
+// rows[p][dst_base[g] + rank[s]] = scale[s] * x[s / k]  on the owner p = g / n_expert of the
+// slot's expert g, plus meta[p][row] = (me << 32) | s.  The last CTA publishes the flags.
+cudaError_t launch_dispatch_push(const ExchangeCtx& ctx, int dtype, const void* x,
+                                 const int64_t* idx, const int* rank, const int* dst_base,
+                                 const void* scale, const PeerPtrs& rows, const PeerPtrs& meta,
+                                 int n_expert, int n_slots, int k, int d, int capacity_rows,
+                                 cudaStream_t stream);
+
+// Waits for every peer's flag on `channel`, then copies the first total_rows rows (and their
+// meta words when requested) out of the staging buffers.
+cudaError_t launch_wait_copy(const ExchangeCtx& ctx, int channel, int dtype, const void* stage_rows,
+                             const int64_t* stage_meta, const int* total_rows, int d,
+                             int capacity_rows, void* out_rows, int64_t* out_meta,
+                             cudaStream_t stream);
+
+// ret[src][slot] = rows[r] for every received row r with meta[r] = (src << 32) | slot.
+cudaError_t launch_return_push(const ExchangeCtx& ctx, int dtype, const void* rows,
+                               const int64_t* meta, const int* total_rows, const PeerPtrs& ret,
+                               int d, int capacity_rows, cudaStream_t stream);
+
+// Waits for the return flags, then out[t] = sum_j w[t, j] * ret[t * k + j] over kept slots
+// (w = 1 when null) and, when `keep` is given, keep[s] = ret[s] for the backward pass.
+cudaError_t launch_wait_combine(const ExchangeCtx& ctx, int dtype, const void* ret,
+                                const int64_t* idx, const void* weight, int n_tokens, int k, int d,
+                                void* out, void* keep, cudaStream_t stream);
+
+// dscore[s] = <dout[s / k], y[s]>  (0 for dropped slots)
+cudaError_t launch_slot_dot(int dtype, const void* dout, const void* y, const int64_t* idx,
+                            int n_slots, int k, int d, void* dscore, cudaStream_t stream);
+
+// In-place sum over ranks of a symmetric buffer (one-shot: every rank reads all peers), with
+// scaling; `n` elements of 16-bit or fp32 type (dtype: 0 bf16, 1 f16, 2 f32).
+cudaError_t launch_allreduce(const ExchangeCtx& ctx, int dtype, const PeerPtrs& bufs, void* out,
+                             long n, float scale, cudaStream_t stream);
+
+// Test hook: waits on `channel` for flags that nothing sets, with the given limit; the
+// kernel returns and leaves kStatusPeerTimeout in the status word.
+cudaError_t launch_wait_only(const ExchangeCtx& ctx, int channel, cudaStream_t stream);
+
+}  // namespace fmoe

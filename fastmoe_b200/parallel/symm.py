@@ -1,5 +1,277 @@
-r"""Symmetric-memory rendezvous and the kernels that run over it (see the module body)."""
+r"""
+Symmetric-memory workspace and the fused expert-parallel path on top of it.
+
+Every rank of an expert-parallel group allocates the same staging buffers with
+``torch.distributed._symmetric_memory`` (CUDA virtual-memory handles exchanged through the
+group's store) and learns the peers' addresses.  The kernels of ``csrc/sm100/p2p.cu`` then
+move token rows with NVLink stores and publish completion through flag words, which replaces
+what the reference does with a private NCCL communicator obtained by subclassing
+``ProcessGroupNCCL`` (``cuda/global_exchange.cpp:108-158``) and host loops of send/recv
+(``cuda/global_exchange.h:28-53,73-98``).
+
+One layer call is, per rank and without any host read:
+
+    route → count_exchange (counts to all peers; offsets from the full matrix)
+          → dispatch_push (rows + (source, slot) words into the owners' staging buffers)
+          → wait_copy     (arrival flags, rows into the tensor kept for backward)
+          → grouped GEMM 1 / activation / grouped GEMM 2 on the received rows
+          → return_push   (output rows back into the sources' slot-indexed staging buffer)
+          → wait_combine  (arrival flags, gate-weighted sum over the k slots of a token)
+
+Backward runs the same two exchanges with gradient rows.  Staging buffers are shared by all
+layers: a rank can only start the next exchange after it has seen every peer's flags of the
+current one, and a peer only raises them after it is done reading, so no buffer is
+overwritten early.
+
+Requirements of the fused path: one process per GPU on one NVLink domain, at most 16 ranks,
+and the same number of tokens on every rank of the group.
+"""
+import math
+import os
+
+import torch
+import torch.distributed as dist
+from torch.autograd import Function
+
+from .. import config
+from ..ops import native
+
+_WORKSPACES = {}
+_FAILED = set()
+_MAX_TOT_EXPERT = 4096
 
 
-def allreduce_grads(grads, comm, scale, fp32_accumulate):  # pylint: disable=unused-argument
-    return False
+def _group_key(group, device):
+    name = getattr(group, "group_name", None) or str(id(group))
+    return (name, device.index)
+
+
+class SymmWorkspace:
+    r"""Symmetric buffers, peer address tables and the native exchange context of one group."""
+
+    def __init__(self, group, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        self._symm_mem = symm_mem
+        self.group = group
+        self.device = device
+        self.world = dist.get_world_size(group)
+        self.me = dist.get_rank(group)
+        nat = native.get()
+        if self.world > nat.P2P_MAX_PEERS:
+            raise RuntimeError("fused expert parallelism supports at most %d ranks" % nat.P2P_MAX_PEERS)
+        self._buffers = {}
+        self.signal, self.signal_ptrs = self._alloc("signal", nat.P2P_NUM_CHANNELS * nat.P2P_MAX_PEERS * 4)
+        self.cnt, self.cnt_ptrs = self._alloc("counts", self.world * _MAX_TOT_EXPERT * 4)
+        self.signal.zero_()
+        self.cnt.zero_()
+        self.epoch = torch.zeros(8, dtype=torch.int32, device=device)
+        self.status = nat.status_word(device.index)
+        self.ctx = nat.ExchangeContext(self.signal_ptrs, self.epoch, self.me, self.world,
+                                       self.status, float(config.wait_timeout_ms()))
+        # Nobody may store into a peer's flags before that peer has zeroed them.
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def _alloc(self, name, nbytes):
+        nbytes = int(math.ceil(nbytes / 256) * 256)
+        t = self._symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        hdl = self._symm_mem.rendezvous(t, group=self.group)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self._buffers[name] = (t, ptrs, hdl)
+        return t, ptrs
+
+    def buffer(self, name, nbytes):
+        r"""Symmetric byte buffer of at least ``nbytes`` (collective when it has to grow)."""
+        have = self._buffers.get(name)
+        if have is None or have[0].numel() < nbytes:
+            torch.cuda.synchronize(self.device)
+            self._alloc(name, max(nbytes, 1))
+            have = self._buffers[name]
+        return have[0], have[1]
+
+    def set_timeout_ms(self, ms):
+        self.ctx.set_timeout_ms(float(ms))
+
+
+def get_workspace(group, device):
+    r"""Workspace of ``group`` on ``device`` or ``None`` when symmetric memory cannot be set up."""
+    if group is None:
+        group = dist.group.WORLD
+    key = _group_key(group, device)
+    if key in _FAILED:
+        return None
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        try:
+            ws = SymmWorkspace(group, device)
+        except Exception as exc:  # pylint: disable=broad-except
+            _FAILED.add(key)
+            if os.environ.get("FMOE_DEBUG", "0") == "1":
+                print("[fastmoe_b200] symmetric memory unavailable: %r" % (exc,))
+            return None
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def _layer_group(layer):
+    return layer.moe_group if layer.moe_group is not None else dist.group.WORLD
+
+
+def fused_available(layer, x):
+    r"""True when the peer-to-peer path can serve this layer call."""
+    if not config.fused_enabled() or not dist.is_available() or not dist.is_initialized():
+        return False
+    group = _layer_group(layer)
+    if dist.get_backend(group) != "nccl" or dist.get_world_size(group) != layer.world_size:
+        return False
+    if layer.world_size * layer.num_expert > _MAX_TOT_EXPERT:
+        return False
+    return get_workspace(group, x.device) is not None
+
+
+def receive_capacity(n_tokens, k, world):
+    r"""Rows reserved for tokens arriving at one rank (see ``config.recv_capacity_factor``)."""
+    factor = config.recv_capacity_factor()
+    worst = n_tokens * k * world
+    if factor <= 0:
+        return worst
+    return min(worst, int(math.ceil(factor * n_tokens * k)))
+
+
+class _DispatchP2P(Function):
+    r"""Token rows → the owning ranks' expert segments (forward); row gradients back, summed
+    over the k copies of a token (backward)."""
+
+    @staticmethod
+    def forward(ctx, x, idx, rank, lec, ws, n_expert, k, capacity):
+        nat = native.get()
+        tot = n_expert * ws.world
+        d = x.shape[1]
+        dev = x.device
+        dst_base = torch.empty(tot, dtype=torch.int32, device=dev)
+        expert_offs = torch.empty(n_expert + 1, dtype=torch.int32, device=dev)
+        total = torch.empty(1, dtype=torch.int32, device=dev)
+        ws.ctx.count_exchange(lec, ws.cnt_ptrs, n_expert, capacity, dst_base, expert_offs, total)
+        stage_rows, rows_ptrs = ws.buffer("rows", capacity * d * x.element_size())
+        stage_meta, meta_ptrs = ws.buffer("meta", capacity * 8)
+        ws.ctx.dispatch_push(x, idx, rank, dst_base, None, rows_ptrs, meta_ptrs, n_expert, k, capacity)
+        xs = torch.empty(capacity, d, dtype=x.dtype, device=dev)
+        meta = torch.empty(capacity, dtype=torch.int64, device=dev)
+        ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, stage_meta.view(torch.int64), total, xs, meta)
+        ctx.ws = ws
+        ctx.k = k
+        ctx.n_tok = x.shape[0]
+        ctx.save_for_backward(idx, meta, total)
+        ctx.mark_non_differentiable(expert_offs, meta, total, dst_base)
+        return xs, expert_offs, meta, total, dst_base
+
+    @staticmethod
+    def backward(ctx, dxs, _g1, _g2, _g3, _g4):
+        idx, meta, total = ctx.saved_tensors
+        ws = ctx.ws
+        dxs = dxs.contiguous()
+        d = dxs.shape[1]
+        stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * dxs.element_size())
+        ws.ctx.return_push(dxs, meta, total, ret_ptrs)
+        dx = torch.empty(ctx.n_tok, d, dtype=dxs.dtype, device=dxs.device)
+        ws.ctx.wait_combine(stage_ret, idx, None, ctx.k, dx, None)
+        return dx, None, None, None, None, None, None, None
+
+
+class _CombineP2P(Function):
+    r"""Expert output rows → back to their source slots and gate-weighted sum (forward);
+    ``d score`` and score-scaled output gradients to the owners (backward)."""
+
+    @staticmethod
+    def forward(ctx, ys, score, idx, rank, dst_base, meta, total, ws, n_expert, k, capacity):
+        d = ys.shape[1]
+        n_tok = idx.numel() // k
+        stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * ys.element_size())
+        ws.ctx.return_push(ys, meta, total, ret_ptrs)
+        out = torch.empty(n_tok, d, dtype=ys.dtype, device=ys.device)
+        y_slots = torch.empty(idx.numel(), d, dtype=ys.dtype, device=ys.device)
+        ws.ctx.wait_combine(stage_ret, idx, score, k, out, y_slots)
+        ctx.ws = ws
+        ctx.args = n_expert, k, capacity
+        ctx.save_for_backward(y_slots, score, idx, rank, dst_base, total)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        nat = native.get()
+        y_slots, score, idx, rank, dst_base, total = ctx.saved_tensors
+        n_expert, k, capacity = ctx.args
+        ws = ctx.ws
+        dout = dout.contiguous()
+        d = dout.shape[1]
+        dscore = torch.empty_like(score)
+        nat.slot_dot(dout, y_slots, idx, k, dscore)
+        ws.ctx.begin_epoch()
+        stage_rows, rows_ptrs = ws.buffer("rows", capacity * d * dout.element_size())
+        ws.ctx.dispatch_push(dout, idx, rank, dst_base, score, rows_ptrs, [0] * ws.world,
+                             n_expert, k, capacity)
+        dys = torch.empty(capacity, d, dtype=dout.dtype, device=dout.device)
+        ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, None, total, dys, None)
+        return dys, dscore, None, None, None, None, None, None, None, None, None
+
+
+def moe_mlp_forward(layer, x, gate_idx, gate_score):
+    r"""Fused ``FMoETransformerMLP`` call under expert parallelism (``world_size > 1``)."""
+    from ..ops import fused
+    nat = native.get()
+    ws = get_workspace(_layer_group(layer), x.device)
+    k = gate_idx.shape[1]
+    n_expert = layer.num_expert
+    idx = gate_idx.contiguous().view(-1)
+    score = gate_score.reshape(-1).to(x.dtype)
+    lec, rank = nat.route(idx, n_expert * ws.world)
+    capacity = receive_capacity(x.shape[0], k, ws.world)
+    xs, expert_offs, meta, total, dst_base = _DispatchP2P.apply(
+        x.contiguous(), idx, rank, lec, ws, n_expert, k, capacity)
+    ys = fused.expert_mlp(layer, xs, expert_offs)
+    return _CombineP2P.apply(ys, score, idx, rank, dst_base, meta, total, ws, n_expert, k, capacity)
+
+
+# ------------------------------------------------------------------------------------------
+# Gradient all-reduce of replicated parameters
+# ------------------------------------------------------------------------------------------
+_AR_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
+_AR_MAX_BYTES = 64 * 1024 * 1024
+
+
+def allreduce_grads(grads, comm, scale, fp32_accumulate=False):  # pylint: disable=unused-argument
+    r"""Sum ``grads`` over ``comm`` in place with the one-shot peer-to-peer kernel.
+
+    Every rank reads all peers' copies in rank order and accumulates in fp32, so the result is
+    bit-identical on all ranks and ``fp32_accumulate`` is implied.  Returns ``False`` (caller
+    falls back to the collective library) for unsupported dtypes, very large buckets or when
+    no symmetric workspace exists for the group.
+    """
+    if not config.fused_enabled() or not grads:
+        return False
+    dtype = grads[0].dtype
+    if dtype not in _AR_DTYPES or dist.get_backend(comm) != "nccl":
+        return False
+    n = sum(g.numel() for g in grads)
+    if n * grads[0].element_size() > _AR_MAX_BYTES:
+        return False
+    ws = get_workspace(comm, grads[0].device)
+    if ws is None:
+        return False
+    buf, ptrs = ws.buffer("allreduce", n * grads[0].element_size())
+    flat = buf[:n * grads[0].element_size()].view(dtype)
+    views = []
+    offset = 0
+    for g in grads:
+        views.append(flat[offset:offset + g.numel()].view_as(g))
+        offset += g.numel()
+    torch._foreach_copy_(views, grads)  # pylint: disable=protected-access
+    out = torch.empty(n, dtype=dtype, device=grads[0].device)
+    ws.ctx.allreduce(ptrs, out, n, float(scale))
+    outs = []
+    offset = 0
+    for g in grads:
+        outs.append(out[offset:offset + g.numel()].view_as(g))
+        offset += g.numel()
+    torch._foreach_copy_(grads, outs)  # pylint: disable=protected-access
+    return True

@@ -1,0 +1,149 @@
+r"""Worker of the CPU multi-process tests (gloo): one process per emulated rank."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from fastmoe_b200 import DistributedGroupedDataParallel, FMoETransformerMLP  # noqa: E402
+from fastmoe_b200 import gates  # noqa: E402
+from oracle import moe_mlp_bruteforce  # noqa: E402
+
+
+def _gather(t):
+    parts = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(parts, t.contiguous())
+    return parts
+
+
+def case_ep_matches_bruteforce():
+    r"""Expert-parallel layer (general path) == brute force over the gathered experts."""
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(7)  # same gate on every rank
+    moe = FMoETransformerMLP(num_expert=2, d_model=8, d_hidden=16, world_size=world, top_k=2)
+    torch.manual_seed(100 + rank)  # different experts and data per rank
+    for p in moe.experts.parameters():
+        nn.init.normal_(p, std=0.3)
+    x = torch.randn(10 + rank, 8, requires_grad=True)
+    y = moe(x)
+    y.sum().backward()
+
+    e = moe.experts
+    w1 = torch.cat(_gather(e.htoh4.weight.detach()))
+    b1 = torch.cat(_gather(e.htoh4.bias.detach()))
+    w2 = torch.cat(_gather(e.h4toh.weight.detach()))
+    b2 = torch.cat(_gather(e.h4toh.bias.detach()))
+    x2 = x.detach().clone().requires_grad_(True)
+    val, idx = torch.topk(moe.gate.gate(x2), 2, dim=-1)
+    ref = moe_mlp_bruteforce(x2, idx, torch.softmax(val, -1), w1, b1, w2, b2, nn.GELU())
+    ref.sum().backward()
+    assert torch.allclose(y, ref, atol=1e-5), (y - ref).abs().max()
+    assert torch.allclose(x.grad, x2.grad, atol=1e-5)
+
+
+def case_capacity_gates():
+    r"""Switch / DC / GShard gates respect their capacities across ranks."""
+    world = dist.get_world_size()
+    torch.manual_seed(3)
+    n_tok, n_exp = 64, 2
+    for name, topk in (("SwitchGate", 1), ("DCGate", 2), ("GShardGate", 2)):
+        gate = getattr(gates, name)(8, n_exp, world, topk, capacity=(0.5, 0.5))
+        gate.train()
+        x = torch.randn(n_tok, 8)
+        idx, score = gate(x)
+        assert idx.shape == (n_tok, topk)
+        counts = torch.bincount(idx[idx >= 0].reshape(-1), minlength=n_exp * world)
+        tot = counts.clone()
+        dist.all_reduce(tot)
+        if name == "SwitchGate":
+            cap = -(-int(0.5 * n_tok) // n_exp) if False else int(torch.ceil(torch.tensor(0.5 * n_tok / n_exp)))
+            assert int(tot.max()) <= cap, (name, tot, cap)
+        elif name == "DCGate":
+            assert int(tot.max()) <= int(0.5 * n_tok + 0.999), (name, tot)
+        else:
+            cap = int(0.5 * n_tok + 0.999) * 2 // (n_exp * world)
+            assert int(counts.max()) <= cap, (name, counts, cap)
+        assert gate.has_loss
+
+
+def case_swipe_gate():
+    world = dist.get_world_size()
+    from fastmoe_b200.functions import ensure_comm
+    ensure_comm(torch.zeros(1), None)
+    torch.manual_seed(11 + dist.get_rank())
+    gate = gates.SwipeGate(8, 2, world, 2)
+    gate.train()
+    x = torch.randn(32, 8)
+    idx, score = gate(x)
+    assert idx.shape == (32, 2) and (idx >= 0).all() and (idx < 2 * world).all()
+    # no worker receives more than batch * top_k tokens
+    worker = torch.div(idx.reshape(-1), 2, rounding_mode="floor")
+    load = torch.bincount(worker, minlength=world)
+    dist.all_reduce(load)
+    assert int(load.max()) <= 32 * 2, load
+    assert torch.allclose(score.sum(-1), torch.ones(32), atol=1e-5)
+
+
+def case_grouped_ddp():
+    r"""Gate grads are averaged over the world, expert grads ('none') are left alone."""
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(5 + rank)
+    moe = FMoETransformerMLP(num_expert=2, d_model=8, d_hidden=16, world_size=world, top_k=2)
+    model = DistributedGroupedDataParallel(moe)
+    gate_w = _gather(moe.gate.gate.weight.detach())
+    assert all(torch.equal(gate_w[0], g) for g in gate_w), "gate not synchronised at construction"
+    x = torch.randn(12, 8)
+    model(x).pow(2).sum().backward()
+    local_gate = moe.gate.gate.weight.grad.clone()
+    local_exp = moe.experts.htoh4.weight.grad.clone()
+    model.allreduce_params()
+    expect = torch.stack(_gather(local_gate)).mean(0)
+    assert torch.allclose(moe.gate.gate.weight.grad, expect, atol=1e-6)
+    assert torch.equal(moe.experts.htoh4.weight.grad, local_exp)
+
+
+def case_slice_group():
+    r"""slice_group: ranks share the input, each routes its slice, outputs are all-gathered."""
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(9)
+    moe = FMoETransformerMLP(num_expert=2, d_model=8, d_hidden=16, world_size=1, top_k=2,
+                             slice_group=dist.group.WORLD)
+    x = torch.randn(4 * world, 8, requires_grad=True)
+    y = moe(x)
+    assert y.shape == x.shape
+    ref_layer = FMoETransformerMLP(num_expert=2, d_model=8, d_hidden=16, world_size=1, top_k=2)
+    ref_layer.load_state_dict(moe.state_dict())
+    ref = ref_layer(x.detach())
+    assert torch.allclose(y, ref, atol=1e-5)
+    y.sum().backward()
+    assert x.grad.shape == x.shape
+
+
+def case_rank_failure():
+    r"""A rank that raises before a collective: the others get an error from the bounded
+    process-group timeout instead of hanging."""
+    rank = dist.get_rank()
+    if rank == 1:
+        raise SystemExit(3)
+    t = torch.ones(1)
+    try:
+        dist.all_reduce(t)
+    except Exception:  # pylint: disable=broad-except
+        raise SystemExit(0)
+    raise SystemExit(4)
+
+
+if __name__ == "__main__":
+    case = sys.argv[1]
+    from datetime import timedelta
+    timeout = timedelta(seconds=8 if case == "rank_failure" else 120)
+    dist.init_process_group("gloo", timeout=timeout)
+    globals()["case_" + case]()
+    if case != "rank_failure":
+        dist.barrier()
+        dist.destroy_process_group()

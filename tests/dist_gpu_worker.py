@@ -1,0 +1,151 @@
+r"""Worker of the multi-GPU tests: one process per GPU (NCCL for the comparison path, the
+peer-to-peer kernels for the fused path).  No test here faults, traps or hangs a GPU: the
+failure case lets a bounded device wait run out and reads the status word."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from fastmoe_b200 import DistributedGroupedDataParallel, FMoETransformerMLP  # noqa: E402
+from fastmoe_b200.ops import native  # noqa: E402
+from fastmoe_b200.parallel import symm  # noqa: E402
+
+
+def _dev():
+    return torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+
+
+def _make_layer(world, rank, num_expert=2, d=256, h=512, top_k=2, dtype=torch.bfloat16):
+    torch.manual_seed(7)
+    layer = FMoETransformerMLP(num_expert=num_expert, d_model=d, d_hidden=h, world_size=world,
+                               top_k=top_k)
+    torch.manual_seed(100 + rank)
+    for p in layer.experts.parameters():
+        nn.init.normal_(p, std=0.05)
+    return layer.to(_dev()).to(dtype)
+
+
+def _run(layer, x, gy):
+    layer.zero_grad()
+    xx = x.detach().clone().requires_grad_(True)
+    y = layer(xx)
+    y.backward(gy)
+    grads = {n: p.grad.detach().float().clone() for n, p in layer.named_parameters()}
+    return y.detach().float(), xx.grad.detach().float(), grads
+
+
+def case_fused_vs_general():
+    r"""Peer-to-peer fused path == collective-library general path (same kernels for the GEMMs)."""
+    rank, world = dist.get_rank(), dist.get_world_size()
+    for num_expert, top_k, n_tok in ((2, 2, 512), (1, 1, 300), (4, 3, 1000)):
+        layer = _make_layer(world, rank, num_expert=num_expert, top_k=top_k)
+        torch.manual_seed(1000 + rank)
+        x = torch.randn(n_tok, 256, device=_dev(), dtype=torch.bfloat16)
+        gy = torch.randn(n_tok, 256, device=_dev(), dtype=torch.bfloat16)
+        assert symm.fused_available(layer, x), "fused path unavailable"
+        y1, gx1, g1 = _run(layer, x, gy)
+        os.environ["FMOE_FUSED"] = "0"
+        assert not symm.fused_available(layer, x)
+        y2, gx2, g2 = _run(layer, x, gy)
+        os.environ["FMOE_FUSED"] = "1"
+        assert torch.allclose(y1, y2, atol=2e-2, rtol=2e-2), float((y1 - y2).abs().max())
+        assert torch.allclose(gx1, gx2, atol=2e-2, rtol=2e-2), float((gx1 - gx2).abs().max())
+        for name in g1:
+            tol = 0.25 if "weight" in name else 0.5
+            assert torch.allclose(g1[name], g2[name], atol=tol, rtol=5e-2), \
+                (name, float((g1[name] - g2[name]).abs().max()))
+        assert native.get().read_status(_dev().index) == 0
+
+
+def case_allreduce():
+    rank, world = dist.get_rank(), dist.get_world_size()
+    for dtype in (torch.bfloat16, torch.float32):
+        torch.manual_seed(rank)
+        grads = [torch.randn(1000, 37, device=_dev()).to(dtype), torch.randn(5, device=_dev()).to(dtype)]
+        ref = [g.float().clone() for g in grads]
+        for r in ref:
+            dist.all_reduce(r)
+        ok = symm.allreduce_grads(grads, dist.group.WORLD, 1.0 / world)
+        assert ok
+        for g, r in zip(grads, ref):
+            assert torch.allclose(g.float(), r / world, atol=2e-2, rtol=2e-2)
+        # bit-identical on all ranks
+        mine = grads[0].float()
+        other = mine.clone()
+        dist.broadcast(other, 0)
+        assert torch.equal(mine, other)
+
+
+def case_grouped_ddp():
+    rank, world = dist.get_rank(), dist.get_world_size()
+    layer = _make_layer(world, rank)
+    model = DistributedGroupedDataParallel(layer)
+    torch.manual_seed(50 + rank)
+    x = torch.randn(256, 256, device=_dev(), dtype=torch.bfloat16)
+    model(x).float().pow(2).mean().backward()
+    local = layer.gate.gate.weight.grad.float().clone()
+    expert_before = layer.experts.htoh4.weight.grad.clone()
+    model.allreduce_params()
+    ref = local.clone()
+    dist.all_reduce(ref)
+    assert torch.allclose(layer.gate.gate.weight.grad.float(), ref / world, atol=1e-2, rtol=2e-2)
+    assert torch.equal(layer.experts.htoh4.weight.grad, expert_before)
+
+
+def case_wait_timeout():
+    r"""A device wait on a flag that nothing sets returns after its limit with a status code;
+    the context stays usable."""
+    nat = native.get()
+    ws = symm.get_workspace(dist.group.WORLD, _dev())
+    assert ws is not None
+    ws.set_timeout_ms(300)
+    ws.ctx.wait_only(nat.P2P_CHAN_RETURN)
+    torch.cuda.synchronize()
+    assert nat.read_status(_dev().index) == nat.STATUS_PEER_TIMEOUT
+    nat.clear_status(_dev().index)
+    ws.set_timeout_ms(4000)
+    dist.barrier()
+    # the exchange still works afterwards
+    case_allreduce()
+    assert nat.read_status(_dev().index) == 0
+
+
+def case_graph_step():
+    r"""A whole expert-parallel training step replays from a CUDA graph."""
+    from fastmoe_b200.utils.graph import GraphedStep
+    rank, world = dist.get_rank(), dist.get_world_size()
+    layer = _make_layer(world, rank)
+    model = DistributedGroupedDataParallel(layer)
+    opt = torch.optim.Adam(layer.parameters(), lr=1e-3, fused=True, capturable=True)
+
+    def step(x):
+        opt.zero_grad(set_to_none=True)
+        loss = model(x).float().pow(2).mean()
+        loss.backward()
+        model.allreduce_params()
+        opt.step()
+        return loss
+
+    torch.manual_seed(60 + rank)
+    x = torch.randn(512, 256, device=_dev(), dtype=torch.bfloat16)
+    g = GraphedStep(step, x, warmup=3)
+    losses = [float(g(x)) for _ in range(5)]
+    assert all(l == l for l in losses)
+    assert losses[-1] < losses[0], losses
+    assert native.get().read_status(_dev().index) == 0
+
+
+if __name__ == "__main__":
+    case = sys.argv[1]
+    torch.cuda.set_device(_dev())
+    dist.init_process_group("nccl", device_id=_dev())
+    globals()["case_" + case]()
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()

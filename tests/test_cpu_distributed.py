@@ -1,0 +1,20 @@
+r"""CPU tier, several ranks: gloo processes exercise the multi-rank host logic (count exchange,
+variable all-to-all layouts, capacity gates, SWIPE, grouped DDP, slice group, rank failure)."""
+import pytest
+
+from dist_launch import run_ranks
+
+
+@pytest.mark.parametrize("case", ["ep_matches_bruteforce", "capacity_gates", "swipe_gate",
+                                  "grouped_ddp", "slice_group"])
+@pytest.mark.parametrize("world", [2, 3])
+def test_cpu_ranks(case, world):
+    codes = run_ranks("dist_cpu_worker.py", case, world, timeout=240)
+    assert codes == [0] * world, codes
+
+
+def test_rank_failure_is_detected():
+    r"""Rank 1 exits before the collective; rank 0 must come back with an error, not hang."""
+    codes = run_ranks("dist_cpu_worker.py", "rank_failure", 2, timeout=120)
+    assert codes[1] == 3
+    assert codes[0] == 0, codes

@@ -1,0 +1,37 @@
+r"""GPU tier, several ranks (one process per GPU): fused peer-to-peer path vs the
+collective-library path, the one-shot all-reduce, grouped DDP, bounded-wait time-out and
+CUDA-graph replay of an expert-parallel step.  Skipped when fewer GPUs than ranks exist,
+like the reference's distributed tests (``tests/test_ddp.py:31-33``)."""
+import os
+
+import pytest
+import torch
+
+from dist_launch import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+# NVLS is switched off for these runs: no kernel here uses multimem, and a rank that died
+# while bound to a multicast object could disturb the other GPUs.
+ENV = {"NCCL_NVLS_ENABLE": "0"}
+
+
+def _need(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+
+
+@pytest.mark.parametrize("case", ["fused_vs_general", "allreduce", "grouped_ddp", "wait_timeout",
+                                  "graph_step"])
+def test_two_ranks(case):
+    _need(2)
+    codes = run_ranks("dist_gpu_worker.py", case, 2, timeout=300, extra_env=ENV)
+    assert codes == [0, 0], codes
+
+
+@pytest.mark.parametrize("case", ["fused_vs_general", "allreduce"])
+def test_many_ranks(case):
+    world = int(os.environ.get("FMOE_TEST_WORLD", "4"))
+    _need(world)
+    codes = run_ranks("dist_gpu_worker.py", case, world, timeout=300, extra_env=ENV)
+    assert codes == [0] * world, codes
