@@ -57,9 +57,10 @@ def case_fused_vs_general():
         assert torch.allclose(y1, y2, atol=2e-2, rtol=2e-2), float((y1 - y2).abs().max())
         assert torch.allclose(gx1, gx2, atol=2e-2, rtol=2e-2), float((gx1 - gx2).abs().max())
         for name in g1:
-            tol = 0.25 if "weight" in name else 0.5
-            assert torch.allclose(g1[name], g2[name], atol=tol, rtol=5e-2), \
-                (name, float((g1[name] - g2[name]).abs().max()))
+            # bf16 gradients: compare against the magnitude of the tensor
+            err = float((g1[name] - g2[name]).abs().max())
+            ref = float(g2[name].abs().max())
+            assert err <= 0.04 * ref + 1e-3, (name, err, ref)
         assert native.get().read_status(_dev().index) == 0
 
 
