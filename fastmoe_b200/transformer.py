@@ -121,6 +121,9 @@ class FMoETransformerMLP(FMoE):
     def _fused_forward(self, moe_inp, gate_top_k_idx, gate_score):
         if not torch.is_tensor(moe_inp) or not moe_inp.is_cuda:
             return None
+        from . import config
+        if config.faster_schedule_enabled() and config.faster_shadow_enabled():
+            return None  # shadow experts are served by the smart schedule
         from .ops import fused
         if not fused.supports(self, moe_inp, gate_top_k_idx):
             return None

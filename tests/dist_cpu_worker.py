@@ -124,6 +124,55 @@ def case_slice_group():
     assert x.grad.shape == x.shape
 
 
+def case_smart_schedule():
+    r"""Smart schedule (all group sizes, with and without shadow experts) == general path."""
+    from fastmoe_b200.fastermoe import schedule
+    from fastmoe_b200.functions import ensure_comm
+    from fastmoe_b200.layers import _fmoe_general_global_forward as naive_forward
+    from oracle import LinearExpert
+    from fastmoe_b200 import FMoE
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ensure_comm(torch.zeros(1), None)
+    for fused_experts in (False, True):
+        for group_size in (1, 2, 4):
+            for shadow in (False, True):
+                os.environ["FMOE_FASTER_GROUP_SIZE"] = str(group_size)
+                torch.manual_seed(21 + rank)
+                if fused_experts:
+                    layer = FMoETransformerMLP(num_expert=2, d_model=8, d_hidden=16, world_size=world, top_k=2)
+                else:
+                    layer = FMoE(num_expert=2, d_model=8, world_size=world, top_k=2, expert=LinearExpert)
+                x = torch.randn(9 + rank, 8)
+                idx = torch.randint(0, 2 * world, (x.shape[0], 2))
+                torch.manual_seed(77)
+                stored = torch.rand(2 * world) < 0.4 if shadow else torch.zeros(2 * world, dtype=torch.bool)
+
+                xa = x.clone().requires_grad_(True)
+                ya = naive_forward(xa, idx, layer.expert_fn, 2, world)
+                ya.pow(2).sum().backward()
+                ga = [p.grad.clone() for p in layer.experts.parameters()]
+                layer.zero_grad()
+
+                xb = x.clone().requires_grad_(True)
+                yb = schedule._fmoe_general_global_forward(
+                    xb, idx, layer.expert_fn_single, 2, world, experts=layer.experts, stored_models=stored)
+                yb.pow(2).sum().backward()
+                gb = [p.grad.clone() for p in layer.experts.parameters()]
+                assert torch.allclose(ya, yb, atol=1e-5), (group_size, shadow, (ya - yb).abs().max())
+                assert torch.allclose(xa.grad, xb.grad, atol=1e-5)
+                for a, b in zip(ga, gb):
+                    assert torch.allclose(a, b, atol=1e-4), (group_size, shadow, (a - b).abs().max())
+
+
+def case_shadow_policy():
+    r"""The policy shadows the overloaded expert and nothing when the load is flat."""
+    from fastmoe_b200.fastermoe.shadow_policy import shadow_plan
+    flat = shadow_plan([100] * 8, 1024, 2, 900e9, 1.3e15, 2)
+    assert not any(flat)
+    skew = shadow_plan([100000, 10, 10, 10, 10, 10, 10, 10], 1024, 2, 900e9, 1.3e15, 2)
+    assert skew[0] and not any(skew[1:])
+
+
 def case_rank_failure():
     r"""A rank that raises before a collective: the others get an error from the bounded
     process-group timeout instead of hanging."""

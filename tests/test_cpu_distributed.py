@@ -6,8 +6,9 @@ from dist_launch import run_ranks
 
 
 @pytest.mark.parametrize("case", ["ep_matches_bruteforce", "capacity_gates", "swipe_gate",
-                                  "grouped_ddp", "slice_group"])
-@pytest.mark.parametrize("world", [2, 3])
+                                  "grouped_ddp", "slice_group", "smart_schedule",
+                                  "shadow_policy"])
+@pytest.mark.parametrize("world", [2, 4])
 def test_cpu_ranks(case, world):
     codes = run_ranks("dist_cpu_worker.py", case, world, timeout=240)
     assert codes == [0] * world, codes
