@@ -1,0 +1,107 @@
+r"""
+Tracing and timing helpers.
+
+The reference has none (its ``cuda/utils/timer.hh`` is commented out and
+``tests/benchmark_mlp.py:92-106`` times with ``time.time()`` without synchronising).  Here:
+NVTX ranges for every fused path, CUDA-event timers whose result is reduced with MAX over the
+ranks of a group (the way every multi-GPU number of this project is reported), and a JSON-lines
+logger for benchmark output.
+"""
+import contextlib
+import json
+import time
+
+import torch
+import torch.distributed as dist
+
+
+@contextlib.contextmanager
+def nvtx_range(name):
+    r"""NVTX range on the current thread (no-op without CUDA)."""
+    if torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        yield
+
+
+class EventTimer:
+    r"""Accumulates CUDA-event durations of named regions on the current stream.
+
+        timer = EventTimer()
+        with timer("dispatch"):
+            ...
+        timer.summary(group)   # {"dispatch": {"ms": max over ranks, "calls": n}}
+    """
+
+    def __init__(self):
+        self._pending = {}
+        self._totals = {}
+
+    @contextlib.contextmanager
+    def __call__(self, name):
+        if not torch.cuda.is_available():
+            t0 = time.perf_counter()
+            yield
+            tot = self._totals.setdefault(name, [0.0, 0])
+            tot[0] += (time.perf_counter() - t0) * 1e3
+            tot[1] += 1
+            return
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
+        with nvtx_range(name):
+            yield
+        end.record()
+        self._pending.setdefault(name, []).append((start, end))
+
+    def _flush(self):
+        if self._pending:
+            torch.cuda.synchronize()
+        for name, pairs in self._pending.items():
+            tot = self._totals.setdefault(name, [0.0, 0])
+            for s, e in pairs:
+                tot[0] += s.elapsed_time(e)
+                tot[1] += 1
+        self._pending.clear()
+
+    def summary(self, group=None):
+        self._flush()
+        out = {}
+        for name in sorted(self._totals):
+            ms, calls = self._totals[name]
+            if dist.is_available() and dist.is_initialized():
+                dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+                t = torch.tensor([ms], dtype=torch.float64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+                ms = float(t)
+            out[name] = {"ms": ms, "calls": calls}
+        return out
+
+    def reset(self):
+        self._pending.clear()
+        self._totals.clear()
+
+
+def roofline_fraction(flops, nvlink_bytes, seconds, peak_flops, link_bytes_per_s=770e9):
+    r"""Achieved fraction of ``max(flops / peak_flops, nvlink_bytes / link_bandwidth)``."""
+    bound = max(flops / peak_flops if peak_flops else 0.0,
+                nvlink_bytes / link_bytes_per_s if link_bytes_per_s else 0.0)
+    return bound / seconds if seconds > 0 else 0.0
+
+
+class JsonlLogger:
+    r"""Appends one JSON object per line (rank 0 only when a process group exists)."""
+
+    def __init__(self, path):
+        self.path = path
+
+    def log(self, **fields):
+        if dist.is_available() and dist.is_initialized() and dist.get_rank() != 0:
+            return
+        fields.setdefault("time", time.time())
+        with open(self.path, "a") as f:
+            f.write(json.dumps(fields) + "\n")

@@ -173,6 +173,99 @@ def case_shadow_policy():
     assert skew[0] and not any(skew[1:])
 
 
+def case_megatron_checkpoint():
+    r"""Megatron adapter under expert parallelism: fmoefy, grouped DDP with a gate group, and
+    sharded save / load (rank 0 full file, other ranks expert shards) giving identical models."""
+    import tempfile
+    import types
+    from fastmoe_b200.megatron import stub
+    from fastmoe_b200.models import GPTConfig, GPTModel
+    rank, world = dist.get_rank(), dist.get_world_size()
+    save_dir = os.environ["FMOE_TEST_TMP"]
+    args = types.SimpleNamespace(hidden_size=16, num_layers=2, balance_strategy="naive",
+                                 init_method_std=0.02, save=save_dir, load=save_dir)
+    stub.install(args)
+    from fastmoe_b200 import megatron as fm
+    cfg = GPTConfig(hidden_size=16, num_layers=2, num_attention_heads=2, ffn_hidden_size=32,
+                    vocab_size=50, max_position_embeddings=8)
+
+    def build():
+        torch.manual_seed(3)
+        import numpy as np
+        np.random.seed(5)
+        model = fm.fmoefy(GPTModel(cfg), fmoe_num_experts=2, distributed_experts=True,
+                          hidden_hidden_size=16, top_k=2, megatron_version="v3.0.2")
+        return model, fm.DistributedDataParallel(model)
+
+    model, ddp = build()
+    mlp = model.language_model.encoder.layers[0].mlp
+    assert mlp.world_size == world and mlp.experts.htoh4.weight.dp_comm == "none"
+    # experts differ per rank, dense parameters are synchronised
+    w = _gather(mlp.experts.htoh4.weight.detach())
+    assert not torch.equal(w[0], w[1])
+    q = _gather(model.language_model.encoder.layers[0].self_attention.dense.weight.detach())
+    assert torch.equal(q[0], q[1])
+
+    opt = torch.optim.Adam(model.parameters(), lr=1e-2)
+    tokens = torch.randint(0, 50, (2, 8))
+    loss = ddp(tokens, tokens)
+    loss.backward()
+    ddp.allreduce_params()
+    opt.step()
+    wrapper = types.SimpleNamespace(optimizer=opt, state_dict=opt.state_dict,
+                                    load_state_dict=opt.load_state_dict)
+    fm.save_checkpoint(7, ddp, wrapper, None)
+    name = "mp_rank_00" if rank == 0 else "mp_rank_00_dp_rank_{:04d}".format(rank)
+    path = os.path.join(save_dir, "iter_0000007", name, "model_optim_rng.pt")
+    assert os.path.exists(path), path
+    if rank > 0:
+        shard = torch.load(path, weights_only=False)
+        keys = []
+
+        def walk(d, prefix=""):
+            for k, v in d.items():
+                walk(v, prefix + k + ".") if isinstance(v, dict) else keys.append(prefix + k)
+
+        walk(shard["model"])
+        assert keys and all("experts" in k for k in keys), keys
+
+    model2, ddp2 = build()
+    for p in model2.parameters():
+        torch.nn.init.zeros_(p)
+    opt2 = torch.optim.Adam(model2.parameters(), lr=1e-2)
+    wrapper2 = types.SimpleNamespace(optimizer=opt2, state_dict=opt2.state_dict,
+                                     load_state_dict=opt2.load_state_dict)
+    it = fm.load_checkpoint(ddp2, wrapper2, None)
+    assert it == 7
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), model2.named_parameters()):
+        assert torch.equal(p1, p2), n1
+    stub.uninstall()
+
+
+def case_generic_checkpoint():
+    r"""fastmoe_b200.checkpoint under expert parallelism: every rank gets its own experts back."""
+    from fastmoe_b200 import checkpoint
+    rank, world = dist.get_rank(), dist.get_world_size()
+    save_dir = os.environ["FMOE_TEST_TMP"]
+    torch.manual_seed(40 + rank)
+    moe = FMoETransformerMLP(num_expert=2, d_model=8, d_hidden=16, world_size=world, top_k=2)
+    model = DistributedGroupedDataParallel(moe)
+    opt = torch.optim.Adam(moe.parameters(), lr=1e-2)
+    model(torch.randn(6, 8)).pow(2).mean().backward()
+    model.allreduce_params()
+    opt.step()
+    checkpoint.save(save_dir, 3, moe, opt)
+    torch.manual_seed(999)
+    fresh = FMoETransformerMLP(num_expert=2, d_model=8, d_hidden=16, world_size=world, top_k=2)
+    opt2 = torch.optim.Adam(fresh.parameters(), lr=1e-2)
+    step, _ = checkpoint.load(save_dir, fresh, opt2)
+    assert step == 3
+    for a, b in zip(moe.parameters(), fresh.parameters()):
+        assert torch.equal(a, b)
+    assert torch.equal(opt.state[moe.experts.htoh4.weight]["exp_avg"],
+                       opt2.state[fresh.experts.htoh4.weight]["exp_avg"])
+
+
 def case_rank_failure():
     r"""A rank that raises before a collective: the others get an error from the bounded
     process-group timeout instead of hanging."""

@@ -19,3 +19,10 @@ def test_rank_failure_is_detected():
     codes = run_ranks("dist_cpu_worker.py", "rank_failure", 2, timeout=120)
     assert codes[1] == 3
     assert codes[0] == 0, codes
+
+
+@pytest.mark.parametrize("case", ["megatron_checkpoint", "generic_checkpoint"])
+def test_checkpoints_under_expert_parallelism(case, tmp_path):
+    codes = run_ranks("dist_cpu_worker.py", case, 2, timeout=240,
+                      extra_env={"FMOE_TEST_TMP": str(tmp_path)})
+    assert codes == [0, 0], codes
