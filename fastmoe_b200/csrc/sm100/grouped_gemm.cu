@@ -85,6 +85,13 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a) {
   kp.accumulate = a.accumulate;
   kp.out_fp32 = a.out_fp32;
   kp.status = a.status;
+  kp.push_meta = a.push_meta;
+  kp.push_dst = a.push_dst;
+  kp.push_flags = a.push_flags;
+  kp.push_epoch = a.push_epoch;
+  kp.push_counter = a.push_counter;
+  kp.push_me = a.push_me;
+  kp.push_world = a.push_world;
 
   const int grid = a.num_sms > 0 ? a.num_sms : 148;
   return a.dtype == kBF16 ? gg::launch_bf16(a.mode, ta, tb, kp, grid, a.stream)

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "p2p.cuh"
+
 namespace fmoe {
 
 enum GemmMode : int {
@@ -46,6 +48,18 @@ struct GroupedGemmArgs {
   int accumulate = 0;            // wgrad: out += result
   int out_fp32 = 0;              // wgrad: output buffer is fp32
   int* status = nullptr;         // device status word (0 = ok)
+  // Row modes, optional: instead of storing row r of the result into `out`, store it into
+  // row (meta[r] & 0xffffffff) of the buffer push_dst.p[meta[r] >> 32] — a peer's slot-indexed
+  // return buffer — and, once the whole grid is done, publish `*push_epoch` on the return
+  // channel of every peer's signal buffer.  This fuses the second expert GEMM (or the last
+  // input-gradient GEMM) with the combine direction of the exchange.
+  const int64_t* push_meta = nullptr;
+  PeerPtrs push_dst = {};
+  PeerPtrs push_flags = {};
+  const int* push_epoch = nullptr;
+  int* push_counter = nullptr;   // zero-initialised word in local memory (CTA completion count)
+  int push_me = 0;
+  int push_world = 0;
   int num_sms = 148;
   cudaStream_t stream = nullptr;
 };

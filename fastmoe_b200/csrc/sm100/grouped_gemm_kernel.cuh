@@ -78,7 +78,8 @@ struct SharedAux {
 };
 
 constexpr int AUX_BYTES = (static_cast<int>(sizeof(SharedAux)) + 127) & ~127;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + NUM_EPI_WARPS * SIDE_BYTES + 1024;
+constexpr int BIAS_BYTES = CHUNKS_PER_WARP * 64;  // per epilogue warp: its four 32-column bias slices
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + NUM_EPI_WARPS * (SIDE_BYTES + BIAS_BYTES) + 1024;
 
 struct KernelParams {
   int num_groups;
@@ -95,6 +96,13 @@ struct KernelParams {
   int accumulate;
   int out_fp32;
   int* status;
+  const int64_t* push_meta;
+  PeerPtrs push_dst;
+  PeerPtrs push_flags;
+  const int* push_epoch;
+  int* push_counter;
+  int push_me;
+  int push_world;
 };
 
 struct TileCoord {
@@ -312,11 +320,14 @@ struct EpiTile {
   const uint8_t* side;
   long side_pitch;
   uint8_t* patch;
+  uint8_t* out_row_base;    // first byte of this lane's output row (local, or a peer's slot row)
+  const uint8_t* bias_sm;   // staged bias slices of this tile (null when there is no bias)
+  uint64_t* empty_bar;      // accumulator-free barrier, signalled once the last tcgen05.ld landed
 };
 
 // Arithmetic and stores of one 32-column chunk held in `r` (raw accumulator bits).
 template <int MODE, typename T, int ACT>
-__device__ __forceinline__ void finish_chunk(const KernelParams& p, const EpiTile& et, int col0,
+__device__ __forceinline__ void finish_chunk(const KernelParams& p, const EpiTile& et, int col0, int ch,
                                              const uint32_t (&r)[32], const Packed32& side_cur) {
   const long off = et.out_row * p.n + col0;
   if (MODE == kWgrad) {
@@ -368,17 +379,19 @@ __device__ __forceinline__ void finish_chunk(const KernelParams& p, const EpiTil
         const float b = __uint_as_float(r[q * 16 + 2 * j + 1]) * act_grad<ACT>(sb);
         w[j] = Cvt<T>::pack(a, b);
       }
-      st256(reinterpret_cast<uint8_t*>(static_cast<T*>(p.out) + off) + q * 32, w);
+      st256(et.out_row_base + col0 * 2 + q * 32, w);
     }
   } else {
-    const uint8_t* bias =
-        p.bias == nullptr ? nullptr
-                          : reinterpret_cast<const uint8_t*>(static_cast<const T*>(p.bias) +
-                                                             static_cast<long>(et.group) * p.n + col0);
+    const uint8_t* bias = et.bias_sm == nullptr ? nullptr : et.bias_sm + ch * 64;
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
       uint32_t bw[8];
-      if (bias != nullptr) ldg256(bias + q * 32, bw);
+      if (bias != nullptr) {
+        const uint4 b0 = *reinterpret_cast<const uint4*>(bias + q * 32);
+        const uint4 b1 = *reinterpret_cast<const uint4*>(bias + q * 32 + 16);
+        bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w;
+        bw[4] = b1.x; bw[5] = b1.y; bw[6] = b1.z; bw[7] = b1.w;
+      }
       uint32_t wp[8], wo[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -400,7 +413,7 @@ __device__ __forceinline__ void finish_chunk(const KernelParams& p, const EpiTil
       if (ACT != kActNone && p.pre_out != nullptr) {
         st256(reinterpret_cast<uint8_t*>(static_cast<T*>(p.pre_out) + off) + q * 32, wp);
       }
-      st256(reinterpret_cast<uint8_t*>(static_cast<T*>(p.out) + off) + q * 32, wo);
+      st256(et.out_row_base + col0 * 2 + q * 32, wo);
     }
   }
 }
@@ -412,40 +425,55 @@ template <int MODE, typename T, int ACT>
 __device__ __forceinline__ void epilogue_tile(const KernelParams& p, const EpiTile& et) {
   const int lane = et.lane;
   uint32_t ra[32], rb[32];
+  bool released = false;
   const int first_col = et.n0 + et.half * 32;
-  if (first_col >= p.n) return;
-  if (et.have_acc) ptx::tmem_ld_32x32(et.t_row + et.half * 32, ra);
+  if (first_col < p.n) {
+    if (et.have_acc) ptx::tmem_ld_32x32(et.t_row + et.half * 32, ra);
 
 #pragma unroll 1
-  for (int pair = 0; pair < CHUNKS_PER_WARP / 2; ++pair) {
-    // ---- even chunk of the pair (held in ra)
-    {
-      const int cg = 2 * (2 * pair) + et.half;
-      const int col0 = et.n0 + cg * 32;
-      if (col0 >= p.n) break;
-      if (et.have_acc) ptx::tmem_ld_wait();
-      Packed32 side_cur;
-      if (et.use_side) read_side(et.patch, lane, side_cur);
-      if (col0 + 64 < p.n) {
-        if (et.have_acc) ptx::tmem_ld_32x32(et.t_row + (cg + 2) * 32, rb);
-        if (et.use_side) stage_side(et.patch, et.side + (cg + 2) * 64, et.side_pitch, et.warp_valid, lane);
+    for (int pair = 0; pair < CHUNKS_PER_WARP / 2; ++pair) {
+      // ---- even chunk of the pair (held in ra)
+      {
+        const int cg = 2 * (2 * pair) + et.half;
+        const int col0 = et.n0 + cg * 32;
+        if (col0 >= p.n) break;
+        if (et.have_acc) ptx::tmem_ld_wait();
+        Packed32 side_cur;
+        if (et.use_side) read_side(et.patch, lane, side_cur);
+        if (col0 + 64 < p.n) {
+          if (et.have_acc) ptx::tmem_ld_32x32(et.t_row + (cg + 2) * 32, rb);
+          if (et.use_side) stage_side(et.patch, et.side + (cg + 2) * 64, et.side_pitch, et.warp_valid, lane);
+        } else if (!released) {
+          // nothing more to read from this accumulator: hand it back to the MMA warp now
+          ptx::tc_fence_before_sync();
+          ptx::mbar_arrive(et.empty_bar);
+          released = true;
+        }
+        if (et.row_ok) finish_chunk<MODE, T, ACT>(p, et, col0, 2 * pair, ra, side_cur);
       }
-      if (et.row_ok) finish_chunk<MODE, T, ACT>(p, et, col0, ra, side_cur);
-    }
-    // ---- odd chunk of the pair (held in rb)
-    {
-      const int cg = 2 * (2 * pair + 1) + et.half;
-      const int col0 = et.n0 + cg * 32;
-      if (col0 >= p.n) break;
-      if (et.have_acc) ptx::tmem_ld_wait();
-      Packed32 side_cur;
-      if (et.use_side) read_side(et.patch, lane, side_cur);
-      if (pair + 1 < CHUNKS_PER_WARP / 2 && col0 + 64 < p.n) {
-        if (et.have_acc) ptx::tmem_ld_32x32(et.t_row + (cg + 2) * 32, ra);
-        if (et.use_side) stage_side(et.patch, et.side + (cg + 2) * 64, et.side_pitch, et.warp_valid, lane);
+      // ---- odd chunk of the pair (held in rb)
+      {
+        const int cg = 2 * (2 * pair + 1) + et.half;
+        const int col0 = et.n0 + cg * 32;
+        if (col0 >= p.n) break;
+        if (et.have_acc) ptx::tmem_ld_wait();
+        Packed32 side_cur;
+        if (et.use_side) read_side(et.patch, lane, side_cur);
+        if (pair + 1 < CHUNKS_PER_WARP / 2 && col0 + 64 < p.n) {
+          if (et.have_acc) ptx::tmem_ld_32x32(et.t_row + (cg + 2) * 32, ra);
+          if (et.use_side) stage_side(et.patch, et.side + (cg + 2) * 64, et.side_pitch, et.warp_valid, lane);
+        } else if (!released) {
+          ptx::tc_fence_before_sync();
+          ptx::mbar_arrive(et.empty_bar);
+          released = true;
+        }
+        if (et.row_ok) finish_chunk<MODE, T, ACT>(p, et, col0, 2 * pair + 1, rb, side_cur);
       }
-      if (et.row_ok) finish_chunk<MODE, T, ACT>(p, et, col0, rb, side_cur);
     }
+  }
+  if (!released) {
+    ptx::tc_fence_before_sync();
+    ptx::mbar_arrive(et.empty_bar);
   }
 }
 
@@ -630,6 +658,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     const int part = warp & 3;                          // TMEM lane quarter this warp may read
     const int half = (warp - FIRST_EPI_WARP) >> 2;      // takes the 32-column chunks 2 * i + half
     uint8_t* patch = smem + STAGES * STAGE_BYTES + AUX_BYTES + (warp - FIRST_EPI_WARP) * SIDE_BYTES;
+    uint8_t* bias_sm = smem + STAGES * STAGE_BYTES + AUX_BYTES + NUM_EPI_WARPS * SIDE_BYTES +
+                       (warp - FIRST_EPI_WARP) * BIAS_BYTES;
     int iter = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
       const TileCoord c = decode_tile<MODE>(p, aux, tile);
@@ -667,6 +697,39 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       if (use_side && first_col < p.n) {
         stage_side(patch, side + half * 64, side_pitch, warp_valid, lane);
       }
+      // Bias slices of this warp's four chunks go to shared memory once per tile.
+      const bool use_bias = (MODE != kWgrad) && !use_aux && p.bias != nullptr;
+      if (use_bias) {
+        __syncwarp();
+        if (lane < CHUNKS_PER_WARP * 4) {
+          const int q = lane >> 2, seg = lane & 3;
+          const int col = n0 + (2 * q + half) * 32;
+          if (col < p.n) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.bias) +
+                                 (static_cast<long>(c.group) * p.n + col) * 2 + seg * 16;
+            *reinterpret_cast<uint4*>(bias_sm + q * 64 + seg * 16) =
+                __ldg(reinterpret_cast<const uint4*>(src));
+          }
+        }
+        __syncwarp();
+      }
+      // Pull the side operand of the next tile of this CTA towards L2 while this tile is
+      // being finished: each lane asks for two of the four 128-byte lines of its row.
+      if (use_aux && tile + static_cast<int>(gridDim.x) < total_tiles) {
+        const TileCoord nx = decode_tile<MODE>(p, aux, tile + gridDim.x);
+        const int r0 = nx.m_tile * BM + part * 32 + lane;
+        if (r0 < nx.row_end - nx.row_begin) {
+          const uint8_t* row = reinterpret_cast<const uint8_t*>(p.aux) +
+                               ((static_cast<long>(nx.row_begin) + r0) * p.n + nx.n_tile * BN) * 2;
+#pragma unroll
+          for (int l = 0; l < 2; ++l) {
+            const int line = half * 2 + l;
+            if (nx.n_tile * BN + line * 64 < p.n) {
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(row + line * 128));
+            }
+          }
+        }
+      }
 
       if (!ptx::mbar_wait(&aux->tmem_full[acc], acc_phase, abort_flag)) {
         if (lane == 0) fail(aux, p.status, STATUS_TIMEOUT_EPILOGUE);
@@ -690,9 +753,39 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       et.side = side;
       et.side_pitch = side_pitch;
       et.patch = patch;
+      if (MODE != kWgrad && p.push_meta != nullptr) {
+        // Fused combine: this lane's output row lives in the source rank's return buffer.
+        et.out_row_base = nullptr;
+        if (row_ok) {
+          const int64_t m = p.push_meta[out_row];
+          const int src = static_cast<int>(m >> 32);
+          const long slot = static_cast<long>(m & 0xffffffffll);
+          et.out_row_base = static_cast<uint8_t*>(p.push_dst.p[src]) + slot * p.n * 2;
+        }
+      } else {
+        et.out_row_base = static_cast<uint8_t*>(p.out) + out_row * p.n * 2;
+      }
+      et.bias_sm = use_bias ? bias_sm : nullptr;
+      et.empty_bar = &aux->tmem_empty[acc];
       epilogue_tile<MODE, T, ACT>(p, et);
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&aux->tmem_empty[acc]);
+    }
+    if (MODE != kWgrad && p.push_meta != nullptr) {
+      // All rows of this CTA are on their way: order them before the completion count; the
+      // last CTA of the grid publishes the epoch on every peer's return channel.
+      __threadfence_system();
+      asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
+      if (threadIdx.x == FIRST_EPI_WARP * 32) {
+        const int prev = atomicAdd(p.push_counter, 1);
+        if (prev == static_cast<int>(gridDim.x) - 1) {
+          *p.push_counter = 0;
+          __threadfence_system();
+          const int epoch = *p.push_epoch;
+          for (int peer = 0; peer < p.push_world; ++peer) {
+            int* flag = static_cast<int*>(p.push_flags.p[peer]) + kChanReturn * kMaxPeers + p.push_me;
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+          }
+        }
+      }
     }
   }
 

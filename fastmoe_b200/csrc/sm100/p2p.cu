@@ -207,16 +207,25 @@ __global__ void dispatch_push_kernel(ExchangeCtx c, const T* __restrict__ x,
     if (row >= capacity_rows) continue;  // overflow is reported by the count exchange
     const uint4* in = reinterpret_cast<const uint4*>(x + static_cast<long>(s / k) * d);
     uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(rows.p[p]) + row * d);
-    if (scale == nullptr) {
-      for (int i = lane; i < nv; i += 32) out[i] = __ldg(in + i);
-    } else {
-      const float sc = V2<T>::to_f(scale[s]);
-      for (int i = lane; i < nv; i += 32) {
-        float f[8];
-        unpack8<T>(__ldg(in + i), f);
+    const float sc = scale == nullptr ? 1.f : V2<T>::to_f(scale[s]);
+    for (int i0 = lane; i0 < nv; i0 += 128) {
+      uint4 v[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] *= sc;
-        out[i] = pack8<T>(f);
+      for (int u = 0; u < 4; ++u) {
+        if (i0 + u * 32 < nv) v[u] = __ldg(in + i0 + u * 32);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i0 + u * 32 < nv) {
+          if (scale != nullptr) {
+            float f[8];
+            unpack8<T>(v[u], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] *= sc;
+            v[u] = pack8<T>(f);
+          }
+          out[i0 + u * 32] = v[u];
+        }
       }
     }
     if (lane == 0 && meta.p[p] != nullptr) {
@@ -270,7 +279,17 @@ __global__ void return_push_kernel(ExchangeCtx c, const T* __restrict__ rows_in,
     if (src < 0 || src >= c.world) continue;
     const uint4* in = reinterpret_cast<const uint4*>(rows_in + static_cast<long>(r) * d);
     uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(ret.p[src]) + slot * d);
-    for (int i = lane; i < nv; i += 32) out[i] = __ldg(in + i);
+    for (int i0 = lane; i0 < nv; i0 += 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i0 + u * 32 < nv) v[u] = __ldg(in + i0 + u * 32);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i0 + u * 32 < nv) out[i0 + u * 32] = v[u];
+      }
+    }
   }
   if (last_block(c.epoch + 2)) {
     if (threadIdx.x == 0) signal_all(c, kChanReturn, c.epoch[0]);
@@ -290,20 +309,37 @@ __global__ void wait_combine_kernel(ExchangeCtx c, const T* __restrict__ ret,
   for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < n_tokens;
        t += gridDim.x * warps_per_block) {
     uint4* o = reinterpret_cast<uint4*>(out + static_cast<long>(t) * d);
-    for (int i = lane; i < nv; i += 32) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i0 = lane; i0 < nv; i0 += 64) {
+      float acc[2][8];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
+      }
       for (int j = 0; j < k; ++j) {
         const long s = static_cast<long>(t) * k + j;
         if (idx[s] < 0) continue;
-        const uint4 w4 = __ldcg(reinterpret_cast<const uint4*>(ret + s * d) + i);
-        if (keep != nullptr) reinterpret_cast<uint4*>(keep + s * d)[i] = w4;
         const float w = weight != nullptr ? V2<T>::to_f(weight[s]) : 1.f;
-        float f[8];
-        unpack8<T>(w4, f);
+        uint4 v[2];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) acc[q] += w * f[q];
+        for (int u = 0; u < 2; ++u) {
+          if (i0 + u * 32 < nv) v[u] = __ldcg(reinterpret_cast<const uint4*>(ret + s * d) + i0 + u * 32);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (i0 + u * 32 < nv) {
+            if (keep != nullptr) reinterpret_cast<uint4*>(keep + s * d)[i0 + u * 32] = v[u];
+            float f[8];
+            unpack8<T>(v[u], f);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[u][q] += w * f[q];
+          }
+        }
       }
-      o[i] = pack8<T>(acc);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (i0 + u * 32 < nv) o[i0 + u * 32] = pack8<T>(acc[u]);
+      }
     }
   }
 }

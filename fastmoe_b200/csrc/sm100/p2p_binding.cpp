@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include "grouped_gemm.cuh"
 #include "p2p.cuh"
 
 namespace {
@@ -125,6 +126,46 @@ class ExchangeContext {
                                           static_cast<float>(scale), stream()));
   }
 
+  // Grouped GEMM (forward mode 0 or input-gradient mode 1) whose epilogue stores each result
+  // row into the slot-indexed return buffer of the row's source rank (`meta`, `ret_ptrs`) and
+  // publishes the return flags when the grid is done: GEMM + combine-direction exchange in
+  // one kernel.
+  void gemm_push(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor offs,
+                 c10::optional<torch::Tensor> bias, torch::Tensor meta,
+                 std::vector<int64_t> ret_ptrs) {
+    c10::cuda::CUDAGuard guard(a.device());
+    TORCH_CHECK(mode == fmoe::kRowsNT || mode == fmoe::kRowsNN, "gemm_push: row modes only");
+    TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && offs.scalar_type() == torch::kInt,
+                "gemm_push: contiguous operands, int32 offsets");
+    fmoe::GroupedGemmArgs g;
+    g.mode = static_cast<int>(mode);
+    g.dtype = dtype16(a);
+    g.num_groups = static_cast<int>(offs.numel() - 1);
+    g.rows_cap = a.size(0);
+    g.k = static_cast<int>(a.size(1));
+    g.n = static_cast<int>(mode == fmoe::kRowsNT ? b.size(1) : b.size(2));
+    g.a = a.data_ptr();
+    g.b = b.data_ptr();
+    g.offs = offs.data_ptr<int>();
+    g.out = nullptr;
+    if (bias.has_value() && bias->defined()) g.bias = bias->data_ptr();
+    g.status = ctx_.status;
+    g.push_meta = meta.data_ptr<int64_t>();
+    g.push_dst = to_ptrs(ret_ptrs);
+    g.push_flags = ctx_.flags;
+    g.push_epoch = ctx_.epoch;
+    g.push_counter = ctx_.epoch + 4;
+    g.push_me = ctx_.me;
+    g.push_world = ctx_.world;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, a.device().index());
+    g.num_sms = sms;
+    g.stream = stream();
+    TORCH_CHECK(fmoe::grouped_gemm_supported(g.mode, 0, g.n, g.k, g.num_groups),
+                "gemm_push: shape not supported by the tcgen05 kernel");
+    FMOE_P2P_CHECK(fmoe::launch_grouped_gemm(g));
+  }
+
   void wait_only(int64_t channel) {
     c10::cuda::CUDAGuard guard(epoch_.device());
     FMOE_P2P_CHECK(fmoe::launch_wait_only(ctx_, static_cast<int>(channel), stream()));
@@ -161,6 +202,7 @@ void bind_p2p(pybind11::module& m) {
       .def("return_push", &ExchangeContext::return_push)
       .def("wait_combine", &ExchangeContext::wait_combine)
       .def("allreduce", &ExchangeContext::allreduce)
+      .def("gemm_push", &ExchangeContext::gemm_push)
       .def("wait_only", &ExchangeContext::wait_only);
   m.def("slot_dot", &slot_dot);
   m.attr("P2P_CHAN_COUNTS") = fmoe::kChanCounts;

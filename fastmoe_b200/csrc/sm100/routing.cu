@@ -178,16 +178,26 @@ __global__ void scatter_rows_kernel(const T* __restrict__ src, const int64_t* __
   const uint4* in = reinterpret_cast<const uint4*>(src + static_cast<long>(s / k) * d);
   uint4* out = reinterpret_cast<uint4*>(dst + row * d);
   const int nv = d >> 3;
-  if (scale == nullptr) {
-    for (int i = lane; i < nv; i += 32) out[i] = __ldg(in + i);
-  } else {
-    const float sc = V2<T>::to_f(scale[s]);
-    for (int i = lane; i < nv; i += 32) {
-      float f[8];
-      unpack8<T>(__ldg(in + i), f);
+  const float sc = scale == nullptr ? 1.f : V2<T>::to_f(scale[s]);
+  // Four 16-byte loads in flight per lane before the first store.
+  for (int i0 = lane; i0 < nv; i0 += 128) {
+    uint4 v[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] *= sc;
-      out[i] = pack8<T>(f);
+    for (int u = 0; u < 4; ++u) {
+      if (i0 + u * 32 < nv) v[u] = __ldg(in + i0 + u * 32);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (i0 + u * 32 < nv) {
+        if (scale != nullptr) {
+          float f[8];
+          unpack8<T>(v[u], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] *= sc;
+          v[u] = pack8<T>(f);
+        }
+        out[i0 + u * 32] = v[u];
+      }
     }
   }
   if (row_slot != nullptr && lane == 0) row_slot[row] = s;
@@ -204,20 +214,70 @@ __global__ void gather_combine_kernel(const T* __restrict__ rows, const int64_t*
   if (t >= n_tokens) return;
   const int nv = d >> 3;
   uint4* o = reinterpret_cast<uint4*>(out + static_cast<long>(t) * d);
-  for (int i = lane; i < nv; i += 32) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int j = 0; j < k; ++j) {
+  // Rows and weights of the k slots first, then two 16-byte chunks of every row in flight.
+  constexpr int kMaxInline = 8;
+  long rows_of[kMaxInline];
+  float w_of[kMaxInline];
+  const int kk = k < kMaxInline ? k : kMaxInline;
+#pragma unroll
+  for (int j = 0; j < kMaxInline; ++j) {
+    rows_of[j] = -1;
+    w_of[j] = 0.f;
+    if (j < kk) {
+      const int s = t * k + j;
+      const long e = idx[s];
+      if (e >= 0) {
+        rows_of[j] = static_cast<long>(base[e]) + rank[s];
+        w_of[j] = weight != nullptr ? V2<T>::to_f(weight[s]) : 1.f;
+      }
+    }
+  }
+  for (int i0 = lane; i0 < nv; i0 += 64) {
+    float acc[2][8];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxInline; ++j) {
+      if (j >= kk || rows_of[j] < 0) continue;
+      const uint4* src = reinterpret_cast<const uint4*>(rows + rows_of[j] * d);
+      uint4 v[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (i0 + u * 32 < nv) v[u] = __ldg(src + i0 + u * 32);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (i0 + u * 32 < nv) {
+          float f[8];
+          unpack8<T>(v[u], f);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[u][q] += w_of[j] * f[q];
+        }
+      }
+    }
+    for (int j = kk; j < k; ++j) {  // more than kMaxInline slots per token: plain path
       const int s = t * k + j;
       const long e = idx[s];
       if (e < 0) continue;
       const long row = static_cast<long>(base[e]) + rank[s];
       const float w = weight != nullptr ? V2<T>::to_f(weight[s]) : 1.f;
-      float f[8];
-      unpack8<T>(__ldg(reinterpret_cast<const uint4*>(rows + row * d) + i), f);
 #pragma unroll
-      for (int q = 0; q < 8; ++q) acc[q] += w * f[q];
+      for (int u = 0; u < 2; ++u) {
+        if (i0 + u * 32 < nv) {
+          float f[8];
+          unpack8<T>(__ldg(reinterpret_cast<const uint4*>(rows + row * d) + i0 + u * 32), f);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[u][q] += w * f[q];
+        }
+      }
     }
-    o[i] = pack8<T>(acc);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (i0 + u * 32 < nv) o[i0 + u * 32] = pack8<T>(acc[u]);
+    }
   }
 }
 

@@ -215,9 +215,87 @@ class _CombineP2P(Function):
         return dys, dscore, None, None, None, None, None, None, None, None, None
 
 
+class _FusedEPMLP(Function):
+    r"""The whole expert-parallel MLP as one autograd node (activations the GEMM epilogue knows).
+
+    Forward: count exchange → dispatch push → wait/copy → GEMM 1 (+bias, activation) → GEMM 2
+    whose epilogue stores every output row straight into the source rank's return buffer and
+    raises the return flags → wait + gate-weighted combine.  Backward: ``d score`` locally,
+    score-scaled output gradients pushed to the owners, bias/weight/input gradients of both
+    linears, and the last input-gradient GEMM again pushes its rows home, where the k copies of
+    a token are summed.  GEMM 2's result and the expert input gradient never exist as local
+    tensors.
+    """
+
+    @staticmethod
+    def forward(ctx, x, score, w1, b1, w2, b2, idx, rank, lec, ws, n_expert, k, capacity, act):
+        from ..ops import grouped_gemm as gg
+        nat = native.get()
+        tot = n_expert * ws.world
+        d = x.shape[1]
+        dev = x.device
+        dst_base = torch.empty(tot, dtype=torch.int32, device=dev)
+        expert_offs = torch.empty(n_expert + 1, dtype=torch.int32, device=dev)
+        total = torch.empty(1, dtype=torch.int32, device=dev)
+        ws.ctx.count_exchange(lec, ws.cnt_ptrs, n_expert, capacity, dst_base, expert_offs, total)
+        stage_rows, rows_ptrs = ws.buffer("rows", capacity * d * x.element_size())
+        stage_meta, meta_ptrs = ws.buffer("meta", capacity * 8)
+        ws.ctx.dispatch_push(x, idx, rank, dst_base, None, rows_ptrs, meta_ptrs, n_expert, k, capacity)
+        xs = torch.empty(capacity, d, dtype=x.dtype, device=dev)
+        meta = torch.empty(capacity, dtype=torch.int64, device=dev)
+        ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, stage_meta.view(torch.int64), total, xs, meta)
+
+        a, pre = gg.forward(xs, w1, expert_offs, b1, act=act, want_pre=True)
+        stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * x.element_size())
+        ws.ctx.gemm_push(gg.MODE_NT, a, w2, expert_offs, b2, meta, ret_ptrs)
+        n_tok = x.shape[0]
+        out = torch.empty(n_tok, d, dtype=x.dtype, device=dev)
+        y_slots = torch.empty(idx.numel(), d, dtype=x.dtype, device=dev)
+        ws.ctx.wait_combine(stage_ret, idx, score, k, out, y_slots)
+
+        ctx.ws = ws
+        ctx.args = n_expert, k, capacity, act, n_tok
+        ctx.save_for_backward(xs, pre, a, w1, w2, expert_offs, meta, total, idx, rank, dst_base,
+                              score, y_slots)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops import grouped_gemm as gg
+        nat = native.get()
+        (xs, pre, a, w1, w2, expert_offs, meta, total, idx, rank, dst_base, score,
+         y_slots) = ctx.saved_tensors
+        n_expert, k, capacity, act, n_tok = ctx.args
+        ws = ctx.ws
+        dout = dout.contiguous()
+        d = dout.shape[1]
+        dscore = torch.empty_like(score)
+        nat.slot_dot(dout, y_slots, idx, k, dscore)
+        ws.ctx.begin_epoch()
+        stage_rows, rows_ptrs = ws.buffer("rows", capacity * d * dout.element_size())
+        ws.ctx.dispatch_push(dout, idx, rank, dst_base, score, rows_ptrs, [0] * ws.world,
+                             n_expert, k, capacity)
+        dys = torch.empty(capacity, d, dtype=dout.dtype, device=dout.device)
+        ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, None, total, dys, None)
+
+        db2 = gg.bias_grad(dys, expert_offs)
+        dw2 = gg.wgrad(dys, a, expert_offs, n_expert)
+        da = gg.dgrad(dys, w2, expert_offs, pre=pre, act=act)
+        db1 = gg.bias_grad(da, expert_offs)
+        dw1 = gg.wgrad(da, xs, expert_offs, n_expert)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * dout.element_size())
+            ws.ctx.gemm_push(gg.MODE_NN, da, w1, expert_offs, None, meta, ret_ptrs)
+            dx = torch.empty(n_tok, d, dtype=dout.dtype, device=dout.device)
+            ws.ctx.wait_combine(stage_ret, idx, None, k, dx, None)
+        return (dx, dscore, dw1, db1, dw2, db2) + (None,) * 8
+
+
 def moe_mlp_forward(layer, x, gate_idx, gate_score):
     r"""Fused ``FMoETransformerMLP`` call under expert parallelism (``world_size > 1``)."""
     from ..ops import fused
+    from ..transformer import activation_kind
     nat = native.get()
     ws = get_workspace(_layer_group(layer), x.device)
     k = gate_idx.shape[1]
@@ -226,6 +304,11 @@ def moe_mlp_forward(layer, x, gate_idx, gate_score):
     score = gate_score.reshape(-1).to(x.dtype)
     lec, rank = nat.route(idx, n_expert * ws.world)
     capacity = receive_capacity(x.shape[0], k, ws.world)
+    act = activation_kind(layer.experts.activation)
+    if act is not None:
+        e = layer.experts
+        return _FusedEPMLP.apply(x.contiguous(), score, e.htoh4.weight, e.htoh4.bias, e.h4toh.weight,
+                                 e.h4toh.bias, idx, rank, lec, ws, n_expert, k, capacity, act)
     xs, expert_offs, meta, total, dst_base = _DispatchP2P.apply(
         x.contiguous(), idx, rank, lec, ws, n_expert, k, capacity)
     ys = fused.expert_mlp(layer, xs, expert_offs)

@@ -21,10 +21,11 @@ def _dev():
     return torch.device("cuda", int(os.environ["LOCAL_RANK"]))
 
 
-def _make_layer(world, rank, num_expert=2, d=256, h=512, top_k=2, dtype=torch.bfloat16):
+def _make_layer(world, rank, num_expert=2, d=256, h=512, top_k=2, dtype=torch.bfloat16,
+                activation=None):
     torch.manual_seed(7)
     layer = FMoETransformerMLP(num_expert=num_expert, d_model=d, d_hidden=h, world_size=world,
-                               top_k=top_k)
+                               top_k=top_k, activation=activation or nn.GELU())
     torch.manual_seed(100 + rank)
     for p in layer.experts.parameters():
         nn.init.normal_(p, std=0.05)
@@ -43,8 +44,10 @@ def _run(layer, x, gy):
 def case_fused_vs_general():
     r"""Peer-to-peer fused path == collective-library general path (same kernels for the GEMMs)."""
     rank, world = dist.get_rank(), dist.get_world_size()
-    for num_expert, top_k, n_tok in ((2, 2, 512), (1, 1, 300), (4, 3, 1000)):
-        layer = _make_layer(world, rank, num_expert=num_expert, top_k=top_k)
+    cases = ((2, 2, 512, None), (1, 1, 300, None), (4, 3, 1000, nn.ReLU()),
+             (2, 2, 640, nn.Sequential(nn.ReLU(), nn.Dropout(0.0))))
+    for num_expert, top_k, n_tok, activation in cases:
+        layer = _make_layer(world, rank, num_expert=num_expert, top_k=top_k, activation=activation)
         torch.manual_seed(1000 + rank)
         x = torch.randn(n_tok, 256, device=_dev(), dtype=torch.bfloat16)
         gy = torch.randn(n_tok, 256, device=_dev(), dtype=torch.bfloat16)
