@@ -27,12 +27,35 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
-TOKENS_PER_GPU = 4096
-D_MODEL = 1024
-D_HIDDEN = 4096
-EXPERTS_PER_GPU = 2
-TOP_K = 2
 METRIC = "moe_fwd_bwd_tokens_per_s"
+
+# The headline config and the skewed, capacity-limited config of the baseline definition.
+CONFIGS = {
+    "ep_mlp": dict(tokens=4096, d_model=1024, d_hidden=4096, experts=2, top_k=2, gate="NaiveGate",
+                   zipf=0.0, label="FMoETransformerMLP (EP MoE MLP layer, NaiveGate top-2, GELU)"),
+    "skewed": dict(tokens=8192, d_model=2048, d_hidden=8192, experts=8, top_k=2, gate="GShardGate",
+                   zipf=1.2, label="FMoETransformerMLP (GShardGate top-2, capacity 1.2, Zipf(1.2) gate bias, GELU)"),
+}
+TOKENS_PER_GPU = D_MODEL = D_HIDDEN = EXPERTS_PER_GPU = TOP_K = None
+GATE_NAME = ZIPF = MODEL_LABEL = None
+
+
+def select_config(name):
+    global TOKENS_PER_GPU, D_MODEL, D_HIDDEN, EXPERTS_PER_GPU, TOP_K, GATE_NAME, ZIPF, MODEL_LABEL
+    c = CONFIGS[name]
+    TOKENS_PER_GPU, D_MODEL, D_HIDDEN = c["tokens"], c["d_model"], c["d_hidden"]
+    EXPERTS_PER_GPU, TOP_K, GATE_NAME, ZIPF, MODEL_LABEL = c["experts"], c["top_k"], c["gate"], c["zipf"], c["label"]
+
+
+def skew_gate(layer, world):
+    r"""Gate bias -s*log(rank of expert): expert popularity follows a Zipf law (random-init weights)."""
+    import torch
+    if ZIPF > 0:
+        tot = EXPERTS_PER_GPU * world
+        bias = -ZIPF * torch.log(torch.arange(1, tot + 1, dtype=torch.float32))
+        with torch.no_grad():
+            layer.gate.gate.weight.mul_(0.1)
+            layer.gate.gate.bias.copy_(bias)
 
 
 def parse_args():
@@ -41,6 +64,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="ep_mlp", choices=sorted(CONFIGS))
     return ap.parse_args()
 
 
@@ -102,13 +126,15 @@ def build_ours(rank, world, device):
     import torch
     sys.path.insert(0, ROOT)
     from fastmoe_b200 import DistributedGroupedDataParallel, FMoETransformerMLP
-    from fastmoe_b200.gates import NaiveGate
+    from fastmoe_b200 import gates
     from fastmoe_b200.ops import native
     native.get()  # fail loudly if the extension is missing
     torch.manual_seed(1234 + rank)
     layer = FMoETransformerMLP(num_expert=EXPERTS_PER_GPU, d_model=D_MODEL, d_hidden=D_HIDDEN,
-                               world_size=world, top_k=TOP_K, gate=NaiveGate,
-                               activation=torch.nn.GELU()).to(device).to(torch.bfloat16)
+                               world_size=world, top_k=TOP_K, gate=getattr(gates, GATE_NAME),
+                               activation=torch.nn.GELU())
+    skew_gate(layer, world)
+    layer = layer.to(device).to(torch.bfloat16)
     model = layer
     if world > 1:
         model = DistributedGroupedDataParallel(layer)
@@ -125,12 +151,14 @@ def build_reference(rank, world, device):
     sys.path.insert(0, ref_dir)
     from fmoe import FMoETransformerMLP  # noqa: E402  (the reference's own package)
     from fmoe.distributed import DistributedGroupedDataParallel
-    from fmoe.gates import NaiveGate
+    from fmoe import gates
     assert os.path.realpath(sys.modules["fmoe"].__file__).startswith(os.path.realpath(ref_dir))
     torch.manual_seed(1234 + rank)
     layer = FMoETransformerMLP(num_expert=EXPERTS_PER_GPU, d_model=D_MODEL, d_hidden=D_HIDDEN,
-                               world_size=world, top_k=TOP_K, gate=NaiveGate,
-                               activation=torch.nn.GELU()).to(device).to(torch.bfloat16)
+                               world_size=world, top_k=TOP_K, gate=getattr(gates, GATE_NAME),
+                               activation=torch.nn.GELU())
+    skew_gate(layer, world)
+    layer = layer.to(device).to(torch.bfloat16)
     model = layer
     if world > 1:
         model = DistributedGroupedDataParallel(layer)
@@ -139,6 +167,7 @@ def build_reference(rank, world, device):
 
 def main():
     args = parse_args()
+    select_config(args.config)
     if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "fmoe")):
         emit({"impl": "reference", "unavailable": "baseline/_ref is not installed"})
         return
@@ -182,6 +211,8 @@ def main():
         x = x.detach().requires_grad_(True)
         y = model(x)
         loss = y.sum()
+        if layer.gate.has_loss:
+            loss = loss + layer.gate.get_loss().sum().to(loss.dtype)
         loss.backward()
         if world > 1:
             model.allreduce_params()
@@ -290,7 +321,7 @@ def main():
             "impl": args.impl,
             "tflops": flops_per_step / (dev_ms / args.steps / 1e3) / 1e12,
             "config": {
-                "model": "FMoETransformerMLP (EP MoE MLP layer, NaiveGate top-2, GELU)",
+                "name": args.config, "model": MODEL_LABEL,
                 "tokens_per_gpu": TOKENS_PER_GPU, "global_batch": TOKENS_PER_GPU * world,
                 "seq_len": 1, "d_model": D_MODEL, "d_hidden": D_HIDDEN,
                 "experts_per_gpu": EXPERTS_PER_GPU, "top_k": TOP_K,

@@ -15,7 +15,9 @@ def gshard_balance_loss(logits, top1_idx, tot_expert, num_expert):
     r"""``mean(c_e · m_e) · num_expert²`` with ``c_e`` the fraction of tokens whose first choice
     is expert ``e`` and ``m_e`` the mean softmax probability of ``e``."""
     n = logits.shape[0]
-    c_e = torch.bincount(top1_idx, minlength=tot_expert)[:tot_expert].to(torch.float32) / n
+    # scatter_add instead of bincount: no device->host read, so the gate can be graph-captured
+    c_e = torch.zeros(tot_expert, device=logits.device).scatter_add_(
+        0, top1_idx, torch.ones_like(top1_idx, dtype=torch.float32)) / n
     m_e = F.softmax(logits, dim=1).mean(dim=0)
     return torch.mean(c_e * m_e.float()) * (num_expert ** 2)
 

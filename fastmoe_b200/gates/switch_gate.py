@@ -36,9 +36,12 @@ class SwitchGate(NaiveGate):
         cap = math.ceil(rate * inp.shape[0] / self.num_expert)
         _lec, _gec, top1_idx = limit_by_capacity(top1_idx, self.num_expert, self.world_size, cap)
 
-        kept = top1_idx[top1_idx > -1]
-        n_kept = max(int(kept.numel()), 1)
-        fraction = torch.bincount(kept, minlength=self.tot_expert)[:self.tot_expert].float() / n_kept
+        # mask arithmetic instead of boolean indexing: no device->host read
+        flat = top1_idx.reshape(-1)
+        kept = (flat > -1).float()
+        n_kept = kept.sum().clamp(min=1.0)
+        fraction = torch.zeros(self.tot_expert, device=inp.device).scatter_add_(
+            0, flat.clamp(min=0), kept) / n_kept
         prob_expert = prob.sum(dim=0) / n_kept
         self.set_loss((fraction * prob_expert).sum() * self.tot_expert)
         return top1_idx, top1_score
