@@ -120,6 +120,41 @@ def case_wait_timeout():
     assert nat.read_status(_dev().index) == 0
 
 
+def case_smart_schedule():
+    r"""FasterMoE smart schedule with shadow experts on GPUs (NCCL exchange on a side stream,
+    bf16 backward) against the plain general path."""
+    from fastmoe_b200.fastermoe import schedule
+    from fastmoe_b200.functions import ensure_comm
+    from fastmoe_b200.layers import _fmoe_general_global_forward as naive_forward
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ensure_comm(torch.zeros(1, device=_dev()), None)
+    for dtype in (torch.float32, torch.bfloat16):
+        for group_size, shadow in ((1, False), (2, True)):
+            os.environ["FMOE_FASTER_GROUP_SIZE"] = str(group_size)
+            layer = _make_layer(world, rank, num_expert=2, d=128, h=256, dtype=dtype)
+            torch.manual_seed(300 + rank)
+            x = torch.randn(200 + 8 * rank, 128, device=_dev(), dtype=dtype)
+            idx = torch.randint(0, 2 * world, (x.shape[0], 2), device=_dev())
+            torch.manual_seed(77)
+            stored = torch.rand(2 * world) < 0.5 if shadow else torch.zeros(2 * world, dtype=torch.bool)
+
+            xa = x.clone().requires_grad_(True)
+            ya = naive_forward(xa, idx, layer.expert_fn, 2, world)
+            ya.float().pow(2).sum().backward()
+            ga = [p.grad.float().clone() for p in layer.experts.parameters()]
+            layer.zero_grad()
+            xb = x.clone().requires_grad_(True)
+            yb = schedule._fmoe_general_global_forward(
+                xb, idx, layer.expert_fn_single, 2, world, experts=layer.experts, stored_models=stored)
+            yb.float().pow(2).sum().backward()
+            gb = [p.grad.float().clone() for p in layer.experts.parameters()]
+            tol = 1e-3 if dtype == torch.float32 else 4e-2
+            assert torch.allclose(ya.float(), yb.float(), atol=tol, rtol=tol), (dtype, shadow)
+            assert torch.allclose(xa.grad.float(), xb.grad.float(), atol=tol * 4, rtol=tol * 2)
+            for a, b in zip(ga, gb):
+                assert float((a - b).abs().max()) <= 0.05 * float(a.abs().max()) + 1e-3
+
+
 def case_graph_step():
     r"""A whole expert-parallel training step replays from a CUDA graph."""
     from fastmoe_b200.utils.graph import GraphedStep

@@ -22,7 +22,7 @@ def _need(world):
 
 
 @pytest.mark.parametrize("case", ["fused_vs_general", "allreduce", "grouped_ddp", "wait_timeout",
-                                  "graph_step"])
+                                  "graph_step", "smart_schedule"])
 def test_two_ranks(case):
     _need(2)
     codes = run_ranks("dist_gpu_worker.py", case, 2, timeout=300, extra_env=ENV)
@@ -35,3 +35,20 @@ def test_many_ranks(case):
     _need(world)
     codes = run_ranks("dist_gpu_worker.py", case, world, timeout=300, extra_env=ENV)
     assert codes == [0] * world, codes
+
+
+def test_data_parallel_in_one_process():
+    r"""``nn.DataParallel`` replicas on several GPUs of one process (reference: tests/test_dp.py):
+    the extension keeps per-device state, so replicas do not interfere."""
+    _need(2)
+    from fastmoe_b200 import FMoETransformerMLP
+    torch.manual_seed(0)
+    moe = FMoETransformerMLP(num_expert=4, d_model=64, d_hidden=128, top_k=2).cuda().to(torch.bfloat16)
+    par = torch.nn.DataParallel(moe, device_ids=[0, 1])
+    x = torch.randn(256, 64, device="cuda:0", dtype=torch.bfloat16)
+    for _ in range(5):
+        y = par(x)
+    ref = moe(x)
+    assert torch.allclose(y.float(), ref.float(), atol=3e-2, rtol=3e-2)
+    from fastmoe_b200.ops import native
+    assert native.get().read_status(0) == 0 and native.get().read_status(1) == 0
