@@ -28,8 +28,17 @@ def offsets_from_counts(counts, device):
 
 
 def _tc_ok(t, mode, m, n, k, groups):
-    return (t.dtype in _TC and native.get().grouped_gemm_supported(mode, m, n, k, groups)
-            and t.data_ptr() % 32 == 0)
+    return t.dtype in _TC and native.get().grouped_gemm_supported(mode, m, n, k, groups)
+
+
+def _aligned(t):
+    r"""The tensor-core kernel wants 32-byte aligned, contiguous operands.  Views into flat
+    buffers (e.g. the replicas ``nn.DataParallel`` broadcasts) may not be: copy those."""
+    if t is None:
+        return None
+    if not t.is_contiguous() or t.data_ptr() % 32 != 0:
+        return t.contiguous().clone() if t.data_ptr() % 32 != 0 and t.is_contiguous() else t.contiguous()
+    return t
 
 
 def forward(x, weight, offs, bias=None, act=None, want_pre=False):
@@ -44,7 +53,8 @@ def forward(x, weight, offs, bias=None, act=None, want_pre=False):
     if _tc_ok(x, MODE_NT, 0, n, k, groups):
         if want_pre and code != 0:
             pre = torch.empty_like(out)
-        nat.grouped_gemm(MODE_NT, x, weight, offs, out, bias, pre, None, code, EPI_BIAS_ACT, False)
+        nat.grouped_gemm(MODE_NT, _aligned(x), _aligned(weight), offs, out, _aligned(bias), pre, None,
+                         code, EPI_BIAS_ACT, False)
         if want_pre and pre is None:
             pre = out
     else:
@@ -66,8 +76,8 @@ def dgrad(dy, weight, offs, pre=None, act=None):
     if dy.shape[0] == 0:
         return out
     if _tc_ok(dy, MODE_NN, 0, n, k, groups):
-        nat.grouped_gemm(MODE_NN, dy, weight, offs, out, None, None, pre if code else None,
-                         code, EPI_DACT if code else EPI_BIAS_ACT, False)
+        nat.grouped_gemm(MODE_NN, _aligned(dy), _aligned(weight), offs, out, None, None,
+                         _aligned(pre) if code else None, code, EPI_DACT if code else EPI_BIAS_ACT, False)
     else:
         nat.simt_grouped_gemm(MODE_NN, dy, weight, offs, out, None)
         _zero_tail(out, offs)
@@ -83,8 +93,8 @@ def wgrad(dy, x, offs, groups, out=None, accumulate=False):
     if out is None:
         out = torch.empty(groups, m, n, dtype=dy.dtype, device=dy.device)
         accumulate = False
-    if _tc_ok(dy, MODE_WGRAD, m, n, 0, groups) and x.data_ptr() % 32 == 0:
-        nat.grouped_gemm(MODE_WGRAD, dy, x, offs, out, None, None, None, 0, 0, accumulate)
+    if _tc_ok(dy, MODE_WGRAD, m, n, 0, groups) and out.data_ptr() % 32 == 0:
+        nat.grouped_gemm(MODE_WGRAD, _aligned(dy), _aligned(x), offs, out, None, None, None, 0, 0, accumulate)
     else:
         tmp = torch.empty(groups, m, n, dtype=dy.dtype, device=dy.device)
         nat.simt_grouped_gemm(MODE_WGRAD, dy, x, offs, tmp, None)
