@@ -321,6 +321,7 @@ struct EpiTile {
   long side_pitch;
   uint8_t* patch;
   uint8_t* out_row_base;    // first byte of this lane's output row (local, or a peer's slot row)
+  bool remote_row;          // the row lives on another GPU: leave through bulk async stores
   const uint8_t* bias_sm;   // staged bias slices of this tile (null when there is no bias)
   uint64_t* empty_bar;      // accumulator-free barrier, signalled once the last tcgen05.ld landed
 };
@@ -413,7 +414,25 @@ __device__ __forceinline__ void finish_chunk(const KernelParams& p, const EpiTil
       if (ACT != kActNone && p.pre_out != nullptr) {
         st256(reinterpret_cast<uint8_t*>(static_cast<T*>(p.pre_out) + off) + q * 32, wp);
       }
-      st256(et.out_row_base + col0 * 2 + q * 32, wo);
+      if (et.remote_row) {
+        // Rows bound for a peer are staged in this lane's 64-byte slot of the warp's patch and
+        // leave as one bulk asynchronous store per chunk: NVLink sees 64-byte writes instead
+        // of scattered 32-byte ones, and the warp does not wait for them.
+        uint8_t* slot = et.patch + et.lane * SIDE_PITCH + q * 32;
+        if (q == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        *reinterpret_cast<uint4*>(slot) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+        *reinterpret_cast<uint4*>(slot + 16) = make_uint4(wo[4], wo[5], wo[6], wo[7]);
+        if (q == 1) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 64;" ::"l"(
+                           et.out_row_base + col0 * 2),
+                       "r"(ptx::smem_u32(et.patch + et.lane * SIDE_PITCH))
+                       : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      } else {
+        st256(et.out_row_base + col0 * 2 + q * 32, wo);
+      }
     }
   }
 }
@@ -756,22 +775,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       if (MODE != kWgrad && p.push_meta != nullptr) {
         // Fused combine: this lane's output row lives in the source rank's return buffer.
         et.out_row_base = nullptr;
+        et.remote_row = false;
         if (row_ok) {
           const int64_t m = p.push_meta[out_row];
           const int src = static_cast<int>(m >> 32);
           const long slot = static_cast<long>(m & 0xffffffffll);
           et.out_row_base = static_cast<uint8_t*>(p.push_dst.p[src]) + slot * p.n * 2;
+          et.remote_row = src != p.push_me;
         }
       } else {
         et.out_row_base = static_cast<uint8_t*>(p.out) + out_row * p.n * 2;
+        et.remote_row = false;
       }
       et.bias_sm = use_bias ? bias_sm : nullptr;
       et.empty_bar = &aux->tmem_empty[acc];
       epilogue_tile<MODE, T, ACT>(p, et);
     }
     if (MODE != kWgrad && p.push_meta != nullptr) {
-      // All rows of this CTA are on their way: order them before the completion count; the
-      // last CTA of the grid publishes the epoch on every peer's return channel.
+      // All rows of this CTA are on their way: wait for the bulk stores, order everything
+      // before the completion count; the last CTA of the grid publishes the epoch on every
+      // peer's return channel.
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      asm volatile("fence.proxy.async;" ::: "memory");
       __threadfence_system();
       asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
       if (threadIdx.x == FIRST_EPI_WARP * 32) {
