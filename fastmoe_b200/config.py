@@ -84,8 +84,12 @@ def deterministic():
 
 
 def wait_timeout_ms():
-    r"""Upper bound of every device-side wait on a peer, in milliseconds."""
-    return int_from_env("FMOE_WAIT_TIMEOUT_MS", 2000)
+    r"""Upper bound of every device-side wait on a peer, in milliseconds.
+
+    Generous by default (a peer may legitimately be late: a checkpoint being written, a
+    garbage-collection pause); tests that exercise the time-out path set a few hundred ms.
+    """
+    return int_from_env("FMOE_WAIT_TIMEOUT_MS", 30000)
 
 
 def debug_bounds():

@@ -24,6 +24,11 @@ class GraphedStep:
     def __init__(self, fn, example_input, warmup=3, pool=None):
         self.fn = fn
         self.static_input = example_input.detach().clone()
+        # Parameters were created on another stream than the capture stream: harmless here.
+        try:
+            torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
+        except AttributeError:
+            pass
         self.graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
