@@ -24,6 +24,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from _common import Stopwatch, init_distributed, max_over_ranks  # noqa: E402
 
 from fastmoe_b200.megatron import stub  # noqa: E402
+from fastmoe_b200.megatron.optimizer import clip_grad_norm_moe  # noqa: E402
 from fastmoe_b200.megatron.utils import add_fmoe_args  # noqa: E402
 from fastmoe_b200.models.gpt import GPTConfig, GPTModel, gpt_flops_per_token  # noqa: E402
 
@@ -116,7 +117,7 @@ def main():
         loss.backward()
         if world > 1:
             ddp.allreduce_params()
-        torch.nn.utils.clip_grad_norm_(model.parameters(), args.clip_grad)
+        clip_grad_norm_moe(model.parameters(), args.clip_grad)
         opt.step()
         window += 1
         if it % args.log_interval == 0 or it == args.train_iters:

@@ -23,6 +23,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from _common import Stopwatch, init_distributed, max_over_ranks  # noqa: E402
 
 from fastmoe_b200 import DistributedGroupedDataParallel, checkpoint  # noqa: E402
+from fastmoe_b200.megatron.optimizer import clip_grad_norm_moe  # noqa: E402
 from fastmoe_b200.models import MemTransformerLM  # noqa: E402
 
 
@@ -119,7 +120,7 @@ def main():
         total.backward()
         if world > 1:
             para_model.allreduce_params()
-        torch.nn.utils.clip_grad_norm_(model.parameters(), args.clip)
+        clip_grad_norm_moe(model.parameters(), args.clip)
         opt.step()
         sched.step()
         step += 1

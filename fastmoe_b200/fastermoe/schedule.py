@@ -72,6 +72,12 @@ class _BroadcastParams(Function):
     @staticmethod
     def forward(ctx, flat, anchor, owner_global_rank, is_owner, group):
         ctx.args = owner_global_rank, is_owner, group
+        from ..parallel import symm
+        # On B200s: one peer-to-peer kernel (non-owners contribute zeros, the sum is the
+        # owner's parameters); otherwise the collective library's broadcast.
+        summed = symm.allreduce_flat(flat.detach() if is_owner else torch.zeros_like(flat), group)
+        if summed is not None:
+            return summed
         buf = flat.detach().clone()
         dist.broadcast(buf, owner_global_rank, group=group)
         return buf
@@ -79,6 +85,10 @@ class _BroadcastParams(Function):
     @staticmethod
     def backward(ctx, grad):
         owner, is_owner, group = ctx.args
+        from ..parallel import symm
+        summed = symm.allreduce_flat(grad.contiguous(), group)
+        if summed is not None:
+            return (summed if is_owner else torch.zeros_like(summed)), None, None, None, None
         grad = grad.contiguous().clone()
         dist.reduce(grad, owner, op=dist.ReduceOp.SUM, group=group)
         return (grad if is_owner else torch.zeros_like(grad)), None, None, None, None

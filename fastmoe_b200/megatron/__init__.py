@@ -17,8 +17,9 @@ from .distributed import DistributedDataParallel
 from .balance import (add_balance_log, generate_megatron_gate_hook, get_balance_profile,
                       reset_gate_hook)
 from .patch import patch_forward_step, patch_model_provider
+from .optimizer import clip_grad_norm_moe, copy_dp_comm_to_master, grad_norm_moe
 
 __all__ = ["add_fmoe_args", "MegatronMLP", "fmoefy", "save_checkpoint", "load_checkpoint",
            "DistributedDataParallel", "reset_gate_hook", "get_balance_profile",
            "generate_megatron_gate_hook", "add_balance_log", "patch_forward_step",
-           "patch_model_provider"]
+           "patch_model_provider", "clip_grad_norm_moe", "grad_norm_moe", "copy_dp_comm_to_master"]

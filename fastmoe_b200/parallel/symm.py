@@ -358,3 +358,28 @@ def allreduce_grads(grads, comm, scale, fp32_accumulate=False):  # pylint: disab
         offset += g.numel()
     torch._foreach_copy_(grads, outs)  # pylint: disable=protected-access
     return True
+
+
+def allreduce_flat(flat, comm, scale=1.0):
+    r"""Sum of a 1-D tensor over ``comm`` with the one-shot peer-to-peer kernel, or ``None`` when
+    that path is not available (caller falls back to the collective library).
+
+    Used for the shadow-expert traffic: a parameter *broadcast* is the sum of the owner's values
+    and zeros everywhere else, the gradient *reduce* is a sum of which only the owner keeps the
+    result.
+    """
+    if not flat.is_cuda or not config.fused_enabled() or flat.dtype not in _AR_DTYPES:
+        return None
+    if comm is None:
+        comm = dist.group.WORLD
+    if dist.get_backend(comm) != "nccl" or flat.numel() * flat.element_size() > _AR_MAX_BYTES:
+        return None
+    ws = get_workspace(comm, flat.device)
+    if ws is None:
+        return None
+    n = flat.numel()
+    buf, ptrs = ws.buffer("allreduce", n * flat.element_size())
+    buf[:n * flat.element_size()].view(flat.dtype).copy_(flat.reshape(-1))
+    out = torch.empty(n, dtype=flat.dtype, device=flat.device)
+    ws.ctx.allreduce(ptrs, out, n, float(scale))
+    return out
