@@ -157,7 +157,8 @@ torch::Tensor prune_gate_by_capacity(torch::Tensor idx, torch::Tensor cap, int64
 void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor offs,
                   torch::Tensor out, c10::optional<torch::Tensor> bias,
                   c10::optional<torch::Tensor> pre_out, c10::optional<torch::Tensor> aux,
-                  int64_t act, int64_t epi, bool accumulate) {
+                  int64_t act, int64_t epi, bool accumulate,
+                  c10::optional<torch::Tensor> psum) {
   check_cuda_contig(a, "a");
   check_cuda_contig(b, "b");
   check_cuda_contig(offs, "offs");
@@ -216,6 +217,15 @@ void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor 
     check_cuda_contig(*aux, "aux");
     TORCH_CHECK(aligned32(*aux), "grouped_gemm: aux must be 32-byte aligned");
     g.aux = aux->data_ptr();
+  }
+  if (psum.has_value() && psum->defined()) {
+    TORCH_CHECK(mode == fmoe::kWgrad, "psum is an output of the weight-gradient mode");
+    check_cuda_contig(*psum, "psum");
+    TORCH_CHECK(psum->scalar_type() == a.scalar_type() &&
+                    psum->numel() == static_cast<int64_t>(g.num_groups) * g.m,
+                "psum must be [groups, m] in the operands' dtype");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(psum->data_ptr()) % 16 == 0, "psum must be 16-byte aligned");
+    g.psum = psum->data_ptr();
   }
   g.act = static_cast<int>(act);
   g.epi = static_cast<int>(epi);
@@ -347,6 +357,69 @@ torch::Tensor gate_topk_softmax_bwd(torch::Tensor dprob, torch::Tensor idx, torc
   return dlogits;
 }
 
+bool gate_fused_supported(int64_t tot, int64_t d, int64_t k) {
+  return fmoe::gate_fused_supported(static_cast<int>(tot), static_cast<int>(d), static_cast<int>(k));
+}
+
+// logits [B, tot], idx [B, k] and prob [B, k] of a linear gate in one pass over x.
+std::vector<torch::Tensor> gate_linear_topk(torch::Tensor x, torch::Tensor w,
+                                            c10::optional<torch::Tensor> bias, int64_t k) {
+  check_cuda_contig(x, "x");
+  check_cuda_contig(w, "w");
+  TORCH_CHECK(x.scalar_type() == w.scalar_type(), "gate input and weight dtypes differ");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rows = static_cast<int>(x.size(0));
+  const int d = static_cast<int>(x.size(1));
+  const int tot = static_cast<int>(w.size(0));
+  auto logits = torch::empty({rows, tot}, x.options());
+  auto idx = torch::empty({rows, k}, torch::dtype(torch::kLong).device(x.device()));
+  auto prob = torch::empty({rows, k}, x.options());
+  FMOE_CUDA_CHECK(fmoe::launch_gate_linear_topk(
+      dtype16(x), x.data_ptr(), w.data_ptr(), bias.has_value() ? bias->data_ptr() : nullptr, rows, d,
+      tot, static_cast<int>(k), logits.data_ptr(), idx.data_ptr<int64_t>(), prob.data_ptr(),
+      cur_stream()));
+  return {logits, idx, prob};
+}
+
+// Returns {dx or empty, dw (layer dtype), db or empty, dl fp32 [B, tot]}.
+std::vector<torch::Tensor> gate_linear_topk_bwd(c10::optional<torch::Tensor> dprob, torch::Tensor idx,
+                                                torch::Tensor prob,
+                                                c10::optional<torch::Tensor> dlogits,
+                                                torch::Tensor x, torch::Tensor w, bool need_dx,
+                                                bool need_db) {
+  check_cuda_contig(x, "x");
+  check_cuda_contig(w, "w");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rows = static_cast<int>(x.size(0));
+  const int d = static_cast<int>(x.size(1));
+  const int tot = static_cast<int>(w.size(0));
+  const int k = static_cast<int>(idx.size(1));
+  auto f32 = torch::dtype(torch::kFloat).device(x.device());
+  auto dl = torch::empty({rows, tot}, f32);
+  torch::Tensor dx = need_dx ? torch::empty_like(x) : torch::Tensor();
+  const bool fused_dw = tot <= 16;
+  // one zero-filled buffer for dW and db so that a single fill and a single cast serve both
+  torch::Tensor acc = fused_dw ? torch::zeros({static_cast<long>(tot) * d + tot}, f32) : torch::Tensor();
+  FMOE_CUDA_CHECK(fmoe::launch_gate_bwd(
+      dtype16(x), dprob.has_value() ? dprob->data_ptr() : nullptr, idx.data_ptr<int64_t>(),
+      prob.data_ptr(), dlogits.has_value() ? dlogits->data_ptr() : nullptr, x.data_ptr(),
+      w.data_ptr(), rows, d, tot, k, dl.data_ptr<float>(), need_dx ? dx.data_ptr() : nullptr,
+      fused_dw ? acc.data_ptr<float>() : nullptr,
+      fused_dw ? acc.data_ptr<float>() + static_cast<long>(tot) * d : nullptr, cur_stream()));
+  torch::Tensor dw, db;
+  if (fused_dw) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);  // the weight-gradient kernel
+    auto cast = acc.to(x.scalar_type());
+    dw = cast.narrow(0, 0, static_cast<long>(tot) * d).view({tot, d});
+    if (need_db) db = cast.narrow(0, static_cast<long>(tot) * d, tot);
+  } else {
+    auto dl16 = dl.to(x.scalar_type());
+    dw = dl16.t().matmul(x);
+    if (need_db) db = dl.sum(0).to(x.scalar_type());
+  }
+  return {dx, dw, db, dl};
+}
+
 // ------------------------------------------------------------------------------ status
 int64_t read_status(int64_t device) {
   auto t = status_tensor(static_cast<int>(device));
@@ -374,7 +447,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &grouped_gemm, py::arg("mode"), py::arg("a"), py::arg("b"), py::arg("offs"),
         py::arg("out"), py::arg("bias") = py::none(), py::arg("pre_out") = py::none(),
         py::arg("aux") = py::none(), py::arg("act") = 0, py::arg("epi") = 0,
-        py::arg("accumulate") = false);
+        py::arg("accumulate") = false, py::arg("psum") = py::none());
   m.def("grouped_gemm_supported", &grouped_gemm_supported);
   m.def("simt_grouped_gemm", &simt_grouped_gemm, py::arg("mode"), py::arg("a"), py::arg("b"),
         py::arg("offs"), py::arg("out"), py::arg("bias") = py::none());
@@ -386,6 +459,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colsum", &colsum);
   m.def("gate_topk_softmax", &gate_topk_softmax);
   m.def("gate_topk_softmax_bwd", &gate_topk_softmax_bwd);
+  m.def("gate_fused_supported", &gate_fused_supported);
+  m.def("gate_linear_topk", &gate_linear_topk);
+  m.def("gate_linear_topk_bwd", &gate_linear_topk_bwd);
   m.def("launch_count", []() { return g_launches.load(); });
   m.def("read_status", &read_status);
   m.def("clear_status", &clear_status);

@@ -84,6 +84,8 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a) {
   kp.epi = a.epi;
   kp.accumulate = a.accumulate;
   kp.out_fp32 = a.out_fp32;
+  kp.psum = (a.mode == kWgrad) ? a.psum : nullptr;
+  kp.psrc = a.a;
   kp.status = a.status;
   kp.push_meta = a.push_meta;
   kp.push_dst = a.push_dst;

@@ -47,6 +47,10 @@ struct GroupedGemmArgs {
   int epi = kEpiBiasAct;
   int accumulate = 0;            // wgrad: out += result
   int out_fp32 = 0;              // wgrad: output buffer is fp32
+  // wgrad, optional: [num_groups, m] per-group column sums of P in the operands' element type
+  // (the bias gradient of the grouped linear whose weight gradient this is); produced by the
+  // epilogue warps while they wait for the main loop.  `accumulate` applies to it too.
+  void* psum = nullptr;
   int* status = nullptr;         // device status word (0 = ok)
   // Row modes, optional: instead of storing row r of the result into `out`, store it into
   // row (meta[r] & 0xffffffff) of the buffer push_dst.p[meta[r] >> 32] — a peer's slot-indexed

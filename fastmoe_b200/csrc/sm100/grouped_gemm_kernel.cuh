@@ -95,6 +95,8 @@ struct KernelParams {
   int epi;
   int accumulate;
   int out_fp32;
+  void* psum;        // wgrad only, optional: [num_groups, m] column sums of P per group (element type T)
+  const void* psrc;  // wgrad only: P itself, for the warps that form the sums with plain loads
   int* status;
   const int64_t* push_meta;
   PeerPtrs push_dst;
@@ -198,6 +200,7 @@ template <int ACT> __device__ __forceinline__ float act_grad(float x) {
 template <typename T> struct Cvt;
 template <> struct Cvt<__nv_bfloat16> {
   static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
   static __device__ __forceinline__ uint32_t pack(float a, float b) {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -210,6 +213,7 @@ template <> struct Cvt<__nv_bfloat16> {
 };
 template <> struct Cvt<__half> {
   static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
   static __device__ __forceinline__ uint32_t pack(float a, float b) {
     __half2 v = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -711,6 +715,69 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       const long side_pitch = static_cast<long>(p.n) * 2;
       const int first_col = n0 + half * 32;
 
+      if constexpr (MODE == kWgrad) {
+        // The bias gradient of a grouped linear is the per-group column sum of the matrix the
+        // weight gradient takes as P.  The epilogue warps have nothing to do while the main
+        // loop of this tile runs, so on the tiles of the first N column block they add up the
+        // tile's 128 columns of P over the group's rows with plain 16-byte loads (the rows are
+        // on their way through L2 for the TMA loads of this and the neighbouring CTAs) and
+        // write the sums in the operands' type: no extra launch, no atomics, no scratch.
+        if (p.psum != nullptr && c.n_tile == 0) {
+          const int ew = warp - FIRST_EPI_WARP;
+          const int col = c.m_tile * BM + (lane & 15) * 8;
+          float cs[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) cs[q] = 0.f;
+          if (col < p.m) {
+            const T* src = static_cast<const T*>(p.psrc) + col;
+            int r = c.row_begin + ew * 2 + (lane >> 4);
+            constexpr int kUnroll = 8;
+            for (; r + 16 * (kUnroll - 1) < c.row_end; r += 16 * kUnroll) {
+              uint4 v[kUnroll];
+#pragma unroll
+              for (int i = 0; i < kUnroll; ++i) {
+                v[i] = __ldg(reinterpret_cast<const uint4*>(src + static_cast<long>(r + 16 * i) * p.m));
+              }
+#pragma unroll
+              for (int i = 0; i < kUnroll; ++i) {
+                float a, b;
+                Cvt<T>::unpack(v[i].x, a, b); cs[0] += a; cs[1] += b;
+                Cvt<T>::unpack(v[i].y, a, b); cs[2] += a; cs[3] += b;
+                Cvt<T>::unpack(v[i].z, a, b); cs[4] += a; cs[5] += b;
+                Cvt<T>::unpack(v[i].w, a, b); cs[6] += a; cs[7] += b;
+              }
+            }
+            for (; r < c.row_end; r += 16) {
+              const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + static_cast<long>(r) * p.m));
+              float a, b;
+              Cvt<T>::unpack(v.x, a, b); cs[0] += a; cs[1] += b;
+              Cvt<T>::unpack(v.y, a, b); cs[2] += a; cs[3] += b;
+              Cvt<T>::unpack(v.z, a, b); cs[4] += a; cs[5] += b;
+              Cvt<T>::unpack(v.w, a, b); cs[6] += a; cs[7] += b;
+            }
+          }
+          float* mine_f = reinterpret_cast<float*>(patch);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            cs[q] += __shfl_xor_sync(0xffffffffu, cs[q], 16);
+            if (lane < 16) mine_f[lane * 8 + q] = cs[q];
+          }
+          asm volatile("bar.sync 2, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
+          const int tid = static_cast<int>(threadIdx.x) - FIRST_EPI_WARP * 32;
+          if (tid < BM && c.m_tile * BM + tid < p.m) {
+            const uint8_t* first = smem + STAGES * STAGE_BYTES + AUX_BYTES;
+            float total = 0.f;
+#pragma unroll
+            for (int w8 = 0; w8 < NUM_EPI_WARPS; ++w8) {
+              total += reinterpret_cast<const float*>(first + w8 * SIDE_BYTES)[tid];
+            }
+            T* dst = static_cast<T*>(p.psum) + static_cast<long>(c.group) * p.m + c.m_tile * BM + tid;
+            if (p.accumulate) total += Cvt<T>::to_f(*dst);
+            *dst = Cvt<T>::from_f(total);
+          }
+          asm volatile("bar.sync 2, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
+        }
+      }
       // The side operand (saved pre-activation, or the old gradient when accumulating) does
       // not depend on the accumulator: fetch its first chunk before waiting for the MMAs.
       if (use_side && first_col < p.n) {

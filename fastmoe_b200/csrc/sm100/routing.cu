@@ -459,6 +459,209 @@ __global__ void gate_topk_softmax_bwd_kernel(const T* __restrict__ dprob,
   }
 }
 
+// ------------------------------------------------------------------------------ fused gate
+// logits = x W^T + b for a handful of experts (tot <= kGateMaxExperts), top-k and softmax of the
+// selected logits, one warp per token: x is read once, W comes from L1/L2, nothing but the
+// [B, tot] logits and the [B, k] ids / probabilities is written.
+constexpr int kGateMaxExperts = 64;
+
+template <typename T, int TOT>
+__global__ void __launch_bounds__(256)
+gate_linear_topk_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias,
+                        int n_rows, int d, int tot, int k, T* __restrict__ logits,
+                        int64_t* __restrict__ idx, T* __restrict__ prob) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  float acc[TOT];
+#pragma unroll
+  for (int e = 0; e < TOT; ++e) acc[e] = 0.f;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long>(row) * d);
+  const int nv = d >> 3;
+#pragma unroll 4
+  for (int i = lane; i < nv; i += 32) {
+    float xf[8];
+    unpack8<T>(__ldg(xr + i), xf);
+#pragma unroll
+    for (int e = 0; e < TOT; ++e) {
+      if (e < tot) {
+        float wf[8];
+        unpack8<T>(__ldg(reinterpret_cast<const uint4*>(w + static_cast<long>(e) * d) + i), wf);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[e] = fmaf(xf[q], wf[q], acc[e]);
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < TOT; ++e) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+    if (e < tot && bias != nullptr) acc[e] += V2<T>::to_f(bias[e]);
+    // the logits leave in the layer's dtype; selection below uses the rounded values so that
+    // ids and probabilities are consistent with what autograd consumers see
+    if (e < tot) acc[e] = V2<T>::to_f(V2<T>::from_f(acc[e]));
+  }
+  if (lane < tot) {
+    float mine = 0.f;
+#pragma unroll
+    for (int e = 0; e < TOT; ++e) {
+      if (e == lane) mine = acc[e];
+    }
+    logits[static_cast<long>(row) * tot + lane] = V2<T>::from_f(mine);
+  }
+  if (TOT > 32 && lane + 32 < tot) {
+    float mine = 0.f;
+#pragma unroll
+    for (int e = 0; e < TOT; ++e) {
+      if (e == lane + 32) mine = acc[e];
+    }
+    logits[static_cast<long>(row) * tot + lane + 32] = V2<T>::from_f(mine);
+  }
+  if (lane == 0) {
+    float sel_v[kMaxK];
+    int sel_i[kMaxK];
+    unsigned long long taken = 0ull;
+    for (int j = 0; j < k; ++j) {
+      float best = -INFINITY;
+      int best_i = -1;
+#pragma unroll
+      for (int e = 0; e < TOT; ++e) {
+        if (e < tot && !((taken >> e) & 1ull) && (best_i < 0 || acc[e] > best)) {
+          best = acc[e];
+          best_i = e;
+        }
+      }
+      taken |= 1ull << best_i;
+      sel_v[j] = best;
+      sel_i[j] = best_i;
+    }
+    float den = 0.f, ex[kMaxK];
+    for (int j = 0; j < k; ++j) {
+      ex[j] = __expf(sel_v[j] - sel_v[0]);
+      den += ex[j];
+    }
+    for (int j = 0; j < k; ++j) {
+      idx[static_cast<long>(row) * k + j] = sel_i[j];
+      prob[static_cast<long>(row) * k + j] = V2<T>::from_f(ex[j] / den);
+    }
+  }
+}
+
+// dl[t, e] = softmax backward of the selected logits scattered to their experts, plus the
+// gradient that reached the logits directly (may be null).  dx[t, :] = sum_e dl[t, e] W[e, :].
+// dl is written out (fp32) for the weight-gradient kernel.  One warp per token.
+template <typename T, int TOT>
+__global__ void __launch_bounds__(256)
+gate_bwd_dx_kernel(const T* __restrict__ dprob, const int64_t* __restrict__ idx,
+                   const T* __restrict__ prob, const T* __restrict__ dlogits_in,
+                   const T* __restrict__ w, int n_rows, int d, int tot, int k,
+                   float* __restrict__ dl_out, T* __restrict__ dx) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  float dl[TOT];
+#pragma unroll
+  for (int e = 0; e < TOT; ++e) {
+    dl[e] = (e < tot && dlogits_in != nullptr)
+                ? V2<T>::to_f(dlogits_in[static_cast<long>(row) * tot + e]) : 0.f;
+  }
+  if (dprob != nullptr) {
+    float g[kMaxK], pj[kMaxK];
+    int id[kMaxK];
+    float dotp = 0.f;
+    for (int j = 0; j < k; ++j) {
+      g[j] = V2<T>::to_f(dprob[static_cast<long>(row) * k + j]);
+      pj[j] = V2<T>::to_f(prob[static_cast<long>(row) * k + j]);
+      id[j] = static_cast<int>(idx[static_cast<long>(row) * k + j]);
+      dotp += g[j] * pj[j];
+    }
+    for (int j = 0; j < k; ++j) {
+      const float v = pj[j] * (g[j] - dotp);
+#pragma unroll
+      for (int e = 0; e < TOT; ++e) {
+        if (e == id[j]) dl[e] += v;
+      }
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int e = 0; e < TOT; ++e) {
+      if (e < tot) dl_out[static_cast<long>(row) * tot + e] = dl[e];
+    }
+  }
+  if (dx != nullptr) {
+    uint4* out = reinterpret_cast<uint4*>(dx + static_cast<long>(row) * d);
+    const int nv = d >> 3;
+#pragma unroll 4
+    for (int i = lane; i < nv; i += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int e = 0; e < TOT; ++e) {
+        if (e < tot && dl[e] != 0.f) {
+          float wf[8];
+          unpack8<T>(__ldg(reinterpret_cast<const uint4*>(w + static_cast<long>(e) * d) + i), wf);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[q] = fmaf(dl[e], wf[q], acc[q]);
+        }
+      }
+      out[i] = pack8<T>(acc);
+    }
+  }
+}
+
+// dW[e, c] += sum_t dl[t, e] x[t, c] and db[e] += sum_t dl[t, e] (fp32, pre-zeroed).  A block
+// takes a 64-column strip and one of `gridDim.y` token ranges; a lane owns two columns.
+template <typename T, int TOT>
+__global__ void __launch_bounds__(256)
+gate_bwd_dw_kernel(const float* __restrict__ dl, const T* __restrict__ x, int n_rows, int d, int tot,
+                   float* __restrict__ dw, float* __restrict__ db) {
+  __shared__ float red[8][TOT][64 + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 64 + lane * 2;
+  const int per = (n_rows + gridDim.y - 1) / gridDim.y;
+  const int t0 = blockIdx.y * per, t1 = min(n_rows, t0 + per);
+  float a0[TOT], a1[TOT], bsum[TOT];
+#pragma unroll
+  for (int e = 0; e < TOT; ++e) a0[e] = a1[e] = bsum[e] = 0.f;
+  for (int t = t0 + warp; t < t1; t += 8) {
+    float x0 = 0.f, x1 = 0.f;
+    if (col < d) {
+      const typename V2<T>::type v = *reinterpret_cast<const typename V2<T>::type*>(x + static_cast<long>(t) * d + col);
+      const float2 f = V2<T>::to_f2(v);
+      x0 = f.x;
+      x1 = f.y;
+    }
+#pragma unroll
+    for (int e = 0; e < TOT; ++e) {
+      if (e < tot) {
+        const float g = __ldg(dl + static_cast<long>(t) * tot + e);
+        a0[e] = fmaf(g, x0, a0[e]);
+        a1[e] = fmaf(g, x1, a1[e]);
+        bsum[e] += g;
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < TOT; ++e) {
+    red[warp][e][lane * 2] = a0[e];
+    red[warp][e][lane * 2 + 1] = a1[e];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < tot * 64; i += blockDim.x) {
+    const int e = i / 64, c = i % 64;
+    float s = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < 8; ++wv) s += red[wv][e][c];
+    if (blockIdx.x * 64 + c < d) atomicAdd(dw + static_cast<long>(e) * d + blockIdx.x * 64 + c, s);
+  }
+  if (db != nullptr && blockIdx.x == 0 && lane == 0) {
+#pragma unroll
+    for (int e = 0; e < TOT; ++e) {
+      if (e < tot) atomicAdd(db + e, bsum[e]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------ SIMT GEMM
 template <typename T> struct Acc { using type = float; };
 template <> struct Acc<double> { using type = double; };
@@ -681,6 +884,58 @@ cudaError_t launch_gate_topk_softmax_bwd(int logit_dtype, const void* dprob, con
     gate_topk_softmax_bwd_kernel<float><<<grid, wpb * 32, 0, stream>>>(
         static_cast<const float*>(dprob), idx, static_cast<const float*>(prob), n_rows, n_experts,
         k, static_cast<float*>(dlogits));
+  }
+  return cudaGetLastError();
+}
+
+#define FMOE_GATE_TOT(tot, ...)                          \
+  if ((tot) <= 8) { constexpr int TOT = 8; __VA_ARGS__; }       \
+  else if ((tot) <= 16) { constexpr int TOT = 16; __VA_ARGS__; } \
+  else if ((tot) <= 32) { constexpr int TOT = 32; __VA_ARGS__; } \
+  else { constexpr int TOT = 64; __VA_ARGS__; }
+
+bool gate_fused_supported(int tot, int d, int k) {
+  return tot >= 1 && tot <= kGateMaxExperts && d % 8 == 0 && k >= 1 && k <= kMaxK && k <= tot;
+}
+
+cudaError_t launch_gate_linear_topk(int dtype, const void* x, const void* w, const void* bias,
+                                    int n_rows, int d, int tot, int k, void* logits, int64_t* idx,
+                                    void* prob, cudaStream_t stream) {
+  if (n_rows == 0) return cudaSuccess;
+  if (!gate_fused_supported(tot, d, k)) return cudaErrorInvalidValue;
+  const int grid = (n_rows + 7) / 8;
+  FMOE_DISPATCH_16(dtype, FMOE_GATE_TOT(tot, (gate_linear_topk_kernel<T, TOT><<<grid, 256, 0, stream>>>(
+      static_cast<const T*>(x), static_cast<const T*>(w), static_cast<const T*>(bias), n_rows, d, tot,
+      k, static_cast<T*>(logits), idx, static_cast<T*>(prob)))));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gate_bwd(int dtype, const void* dprob, const int64_t* idx, const void* prob,
+                            const void* dlogits_in, const void* x, const void* w, int n_rows, int d,
+                            int tot, int k, float* dl_scratch, void* dx, float* dw, float* db,
+                            cudaStream_t stream) {
+  if (n_rows == 0) return cudaSuccess;
+  if (!gate_fused_supported(tot, d, k)) return cudaErrorInvalidValue;
+  const int grid = (n_rows + 7) / 8;
+  FMOE_DISPATCH_16(dtype, FMOE_GATE_TOT(tot, (gate_bwd_dx_kernel<T, TOT><<<grid, 256, 0, stream>>>(
+      static_cast<const T*>(dprob), idx, static_cast<const T*>(prob), static_cast<const T*>(dlogits_in),
+      static_cast<const T*>(w), n_rows, d, tot, k, dl_scratch, static_cast<T*>(dx)))));
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  if (dw == nullptr) return cudaSuccess;
+  if (tot > 16) return cudaErrorInvalidValue;
+  // Each warp walks its token range serially (one dependent load chain), so the ranges are
+  // kept short: many blocks, a few tokens per warp, partial sums merged with atomics.
+  int splits = n_rows / 64;
+  if (splits < 1) splits = 1;
+  if (splits > 64) splits = 64;
+  dim3 g2((d + 63) / 64, splits);
+  if (tot <= 8) {
+    FMOE_DISPATCH_16(dtype, (gate_bwd_dw_kernel<T, 8><<<g2, 256, 0, stream>>>(
+        dl_scratch, static_cast<const T*>(x), n_rows, d, tot, dw, db)));
+  } else {
+    FMOE_DISPATCH_16(dtype, (gate_bwd_dw_kernel<T, 16><<<g2, 256, 0, stream>>>(
+        dl_scratch, static_cast<const T*>(x), n_rows, d, tot, dw, db)));
   }
   return cudaGetLastError();
 }

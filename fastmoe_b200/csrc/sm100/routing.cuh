@@ -51,6 +51,21 @@ cudaError_t launch_gate_topk_softmax_bwd(int logit_dtype, const void* dprob, con
                                          const void* prob, int n_rows, int n_experts, int k,
                                          void* dlogits, cudaStream_t stream);
 
+// Fused gate: logits = x W^T + b (tot <= 64 experts, 16-bit types), top-k ids (descending) and
+// softmax over the selected logits; one pass over x.
+bool gate_fused_supported(int tot, int d, int k);
+cudaError_t launch_gate_linear_topk(int dtype, const void* x, const void* w, const void* bias,
+                                    int n_rows, int d, int tot, int k, void* logits, int64_t* idx,
+                                    void* prob, cudaStream_t stream);
+// Backward of the fused gate.  dl_scratch: fp32 [n_rows, tot]; dx (optional) [n_rows, d];
+// dw fp32 [tot, d] and db fp32 [tot] (optional) must be zero on entry (accumulated with
+// atomics).  The weight gradient kernel covers tot <= 16: pass dw = nullptr above that and
+// form dW = dl^T x from dl_scratch with a library GEMM.
+cudaError_t launch_gate_bwd(int dtype, const void* dprob, const int64_t* idx, const void* prob,
+                            const void* dlogits_in, const void* x, const void* w, int n_rows, int d,
+                            int tot, int k, float* dl_scratch, void* dx, float* dw, float* db,
+                            cudaStream_t stream);
+
 // Reference-precision grouped GEMM for fp32 / fp64 and for shapes the tensor-core kernel
 // does not take (elem: 0 bf16, 1 f16, 2 f32, 3 f64).  Same modes as the tcgen05 kernel.
 cudaError_t launch_simt_grouped_gemm(int mode, int elem, int num_groups, long rows_cap, int m, int n,

@@ -10,7 +10,8 @@ class NaiveGate(BaseGate):
     r"""``Linear(d_model → tot_expert)``, top-k of the logits, softmax over the k selected logits.
 
     State-dict keys: ``gate.weight [tot_expert, d_model]``, ``gate.bias [tot_expert]``.
-    On a GPU the top-k + softmax (and their backward) are one kernel.
+    On a GPU with 16-bit parameters and at most 64 experts the linear layer, the top-k and the
+    softmax are one kernel (two in backward); otherwise the top-k + softmax are.
     """
 
     def __init__(self, d_model, num_expert, world_size, top_k=2, gate_bias=True):
@@ -19,8 +20,9 @@ class NaiveGate(BaseGate):
         self.top_k = top_k
 
     def forward(self, inp, return_all_scores=False):
-        logits = self.gate(inp)
-        idx, score = gating.topk_softmax(logits.view(-1, self.tot_expert), self.top_k)
+        logits, idx, score = gating.linear_topk_softmax(
+            inp.reshape(-1, inp.shape[-1]), self.gate.weight, self.gate.bias, self.top_k)
+        logits = logits.view(*inp.shape[:-1], self.tot_expert)
         # The reference installs a zero "dummy" loss so that callers can always add it.
         self.set_loss(torch.zeros(1, device=inp.device, requires_grad=True))
         if return_all_scores:

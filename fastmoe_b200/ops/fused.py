@@ -100,11 +100,9 @@ class _ExpertMLP(Function):
         xs, w1, w2, offs, pre, a = ctx.saved_tensors
         groups = w1.shape[0]
         dys = dys.contiguous()
-        db2 = gg.bias_grad(dys, offs)
-        dw2 = gg.wgrad(dys, a, offs, groups)
+        dw2, db2 = gg.wgrad(dys, a, offs, groups, with_bias_grad=True)
         da = gg.dgrad(dys, w2, offs, pre=pre, act=ctx.act)
-        db1 = gg.bias_grad(da, offs)
-        dw1 = gg.wgrad(da, xs, offs, groups)
+        dw1, db1 = gg.wgrad(da, xs, offs, groups, with_bias_grad=True)
         dxs = gg.dgrad(da, w1, offs) if ctx.needs_input_grad[0] else None
         return dxs, dw1, db1, dw2, db2, None, None
 
@@ -122,8 +120,7 @@ class _GroupedLinear(Function):
     def backward(ctx, dys):
         xs, w, offs = ctx.saved_tensors
         dys = dys.contiguous()
-        db = gg.bias_grad(dys, offs)
-        dw = gg.wgrad(dys, xs, offs, w.shape[0])
+        dw, db = gg.wgrad(dys, xs, offs, w.shape[0], with_bias_grad=True)
         dxs = gg.dgrad(dys, w, offs) if ctx.needs_input_grad[0] else None
         return dxs, dw, db, None
 

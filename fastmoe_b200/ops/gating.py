@@ -5,6 +5,12 @@ Parity: the ``topk`` → ``softmax`` sequence of ``fmoe/gates/naive_gate.py:31-3
 in the reference).  On a GPU one kernel reads each logits row once, keeps the k largest in
 registers, writes ids and probabilities, and a second small kernel applies the softmax
 Jacobian in backward and scatters the result into the dense logits gradient.
+
+``linear_topk_softmax`` goes one step further for the plain linear gate
+(``fmoe/gates/naive_gate.py:24-38``: ``nn.Linear`` → ``topk`` → ``softmax``): with at most 64
+experts the logits of a token fit in registers, so one kernel reads the token once and writes
+logits, ids and probabilities, and the backward is two kernels (softmax Jacobian + ``dx``;
+``dW`` and ``db``) instead of the six of the ATen sequence.
 """
 import torch
 from torch.autograd import Function
@@ -13,6 +19,7 @@ from . import native
 
 MAX_FUSED_K = 8
 MAX_FUSED_EXPERTS = 4096
+MAX_SINGLE_PASS_EXPERTS = 8
 
 
 def _topk_softmax_torch(logits, k):
@@ -43,3 +50,49 @@ def topk_softmax(logits, k):
             and logits.dtype in (torch.float32, torch.bfloat16, torch.float16)):
         return _TopkSoftmax.apply(logits, k)
     return _topk_softmax_torch(logits, k)
+
+
+class _LinearTopkSoftmax(Function):
+    r"""``logits = x W^T + b``, top-k ids and softmax of the selected logits as one op."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, k):
+        logits, idx, prob = native.get().gate_linear_topk(x, weight, bias, int(k))
+        ctx.save_for_backward(x, weight, idx, prob)
+        ctx.has_bias = bias is not None
+        ctx.mark_non_differentiable(idx)
+        ctx.set_materialize_grads(False)
+        return logits, idx, prob
+
+    @staticmethod
+    def backward(ctx, grad_logits, _grad_idx, grad_prob):
+        x, weight, idx, prob = ctx.saved_tensors
+        if grad_logits is None and grad_prob is None:
+            return None, None, None, None
+        dx, dw, db, _dl = native.get().gate_linear_topk_bwd(
+            None if grad_prob is None else grad_prob.contiguous(), idx, prob,
+            None if grad_logits is None else grad_logits.contiguous(), x, weight,
+            ctx.needs_input_grad[0], ctx.has_bias and ctx.needs_input_grad[2])
+        return (dx if ctx.needs_input_grad[0] else None, dw if ctx.needs_input_grad[1] else None,
+                db if ctx.has_bias and ctx.needs_input_grad[2] else None, None)
+
+
+def linear_topk_softmax(x, weight, bias, k):
+    r"""``(logits [B,E], idx int64 [B,k], prob [B,k])`` of a linear gate over 2-D ``x``.
+
+    Uses the single-pass kernel when the shape allows it (16-bit types on a GPU, ``d_model`` a
+    multiple of 8) and the expert count is small enough for its one-warp-per-token SIMT dot
+    products to beat a library GEMM (measured on B200 with 4096 tokens, ``d_model`` 1024:
+    30.6 vs 35.5 µs forward + backward at 2 experts, 52 vs 37 µs at 16); otherwise the
+    ``linear`` → :func:`topk_softmax` sequence runs.
+    """
+    if (x.is_cuda and x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16)
+            and weight.shape[0] <= MAX_SINGLE_PASS_EXPERTS
+            and weight.dtype == x.dtype and (bias is None or bias.dtype == x.dtype)
+            and not torch.is_autocast_enabled()
+            and native.get().gate_fused_supported(weight.shape[0], x.shape[1], k)):
+        xc = x if x.is_contiguous() else x.contiguous()
+        return _LinearTopkSoftmax.apply(xc, weight.contiguous(), bias, k)
+    logits = torch.nn.functional.linear(x, weight, bias)
+    idx, prob = topk_softmax(logits, k)
+    return logits, idx, prob

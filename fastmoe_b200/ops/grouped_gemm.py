@@ -86,15 +86,25 @@ def dgrad(dy, weight, offs, pre=None, act=None):
     return out
 
 
-def wgrad(dy, x, offs, groups, out=None, accumulate=False):
-    r"""``dW[e] = dy[rows_e]^T x[rows_e]`` → ``[E, dy.shape[1], x.shape[1]]``; empty experts give zeros."""
+def wgrad(dy, x, offs, groups, out=None, accumulate=False, with_bias_grad=False):
+    r"""``dW[e] = dy[rows_e]^T x[rows_e]`` → ``[E, dy.shape[1], x.shape[1]]``; empty experts give zeros.
+
+    With ``with_bias_grad`` the per-expert column sums of ``dy`` (the bias gradient of the same
+    grouped linear, ``[E, dy.shape[1]]``) are returned as well: ``(dW, db)``.  The tensor-core
+    kernel produces them from the ``dy`` tiles it stages in shared memory anyway, so they cost
+    no extra pass over ``dy`` and no extra launch.
+    """
     nat = native.get()
     m, n = dy.shape[1], x.shape[1]
     if out is None:
         out = torch.empty(groups, m, n, dtype=dy.dtype, device=dy.device)
         accumulate = False
+    db = None
     if _tc_ok(dy, MODE_WGRAD, m, n, 0, groups) and out.data_ptr() % 32 == 0:
-        nat.grouped_gemm(MODE_WGRAD, _aligned(dy), _aligned(x), offs, out, None, None, None, 0, 0, accumulate)
+        if with_bias_grad:
+            db = torch.empty(groups, m, dtype=dy.dtype, device=dy.device)
+        nat.grouped_gemm(MODE_WGRAD, _aligned(dy), _aligned(x), offs, out, None, None, None, 0, 0,
+                         accumulate, db)
     else:
         tmp = torch.empty(groups, m, n, dtype=dy.dtype, device=dy.device)
         nat.simt_grouped_gemm(MODE_WGRAD, dy, x, offs, tmp, None)
@@ -102,7 +112,9 @@ def wgrad(dy, x, offs, groups, out=None, accumulate=False):
             out += tmp
         else:
             out.copy_(tmp)
-    return out
+        if with_bias_grad:
+            db = bias_grad(dy, offs)
+    return (out, db) if with_bias_grad else out
 
 
 def bias_grad(dy, offs, dtype=None):
@@ -157,6 +169,9 @@ def linear_backward_host_counts(grad_out, inp, expert_count_cpu, weight, bias=No
     offs = offsets_from_counts(expert_count_cpu, inp.device)
     grad_out = grad_out.contiguous()
     grad_in = dgrad(grad_out, weight.contiguous(), offs)
-    grad_w = wgrad(grad_out, inp.contiguous(), offs, weight.shape[0])
-    grad_b = bias_grad(grad_out, offs, bias.dtype) if bias is not None else None
+    if bias is not None:
+        grad_w, grad_b = wgrad(grad_out, inp.contiguous(), offs, weight.shape[0], with_bias_grad=True)
+        grad_b = grad_b.to(bias.dtype)
+    else:
+        grad_w, grad_b = wgrad(grad_out, inp.contiguous(), offs, weight.shape[0]), None
     return grad_in, grad_w, grad_b

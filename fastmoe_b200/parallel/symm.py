@@ -278,11 +278,9 @@ class _FusedEPMLP(Function):
         dys = torch.empty(capacity, d, dtype=dout.dtype, device=dout.device)
         ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, None, total, dys, None)
 
-        db2 = gg.bias_grad(dys, expert_offs)
-        dw2 = gg.wgrad(dys, a, expert_offs, n_expert)
+        dw2, db2 = gg.wgrad(dys, a, expert_offs, n_expert, with_bias_grad=True)
         da = gg.dgrad(dys, w2, expert_offs, pre=pre, act=act)
-        db1 = gg.bias_grad(da, expert_offs)
-        dw1 = gg.wgrad(da, xs, expert_offs, n_expert)
+        dw1, db1 = gg.wgrad(da, xs, expert_offs, n_expert, with_bias_grad=True)
         dx = None
         if ctx.needs_input_grad[0]:
             stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * dout.element_size())

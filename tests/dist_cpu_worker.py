@@ -1,6 +1,7 @@
 r"""Worker of the CPU multi-process tests (gloo): one process per emulated rank."""
 import os
 import sys
+import time
 
 import torch
 import torch.distributed as dist
@@ -288,4 +289,10 @@ if __name__ == "__main__":
     globals()["case_" + case]()
     if case != "rank_failure":
         dist.barrier()
-        dist.destroy_process_group()
+        # Leave without running the process-group and interpreter destructors: with the gloo
+        # backend a rank whose peers have already closed their sockets occasionally aborts in
+        # a background thread during teardown, after the case itself has passed.
+        sys.stdout.flush()
+        sys.stderr.flush()
+        time.sleep(0.2)
+        os._exit(0)

@@ -106,6 +106,17 @@ def test_grouped_gemm_wgrad(dtype, counts, m, n):
     for e, lo, hi in _segments(counts):
         ref = dy[lo:hi].float().sum(0)
         assert torch.allclose(bg[e].float(), ref, atol=0.3, rtol=2e-2)
+    # the same sums produced inside the weight-gradient kernel, with and without accumulation
+    out2, bg2 = gg.wgrad(dy, x, offs, len(counts), with_bias_grad=True)
+    assert torch.equal(out2, out)
+    for e, lo, hi in _segments(counts):
+        ref = dy[lo:hi].float().sum(0)
+        assert torch.allclose(bg2[e].float(), ref, atol=0.3, rtol=2e-2), e
+    if gg._tc_ok(dy, gg.MODE_WGRAD, m, n, 0, len(counts)):
+        acc_w = out.clone()
+        acc_b = bg2.clone()
+        _native().grouped_gemm(gg.MODE_WGRAD, dy, x, offs, acc_w, None, None, None, 0, 0, True, acc_b)
+        assert torch.allclose(acc_b.float(), 2 * bg2.float(), atol=0.6, rtol=3e-2)
     assert _native().read_status(0) == 0
 
 
@@ -212,3 +223,55 @@ def test_gate_topk_softmax(dtype, n_exp, k):
     prob.backward(g)
     rp.backward(g.float())
     assert torch.allclose(logits.grad.float(), ref_l.grad, atol=2e-2 if dtype != torch.float32 else 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n_exp,k,d,bias", [(4, 2, 64, True), (16, 2, 1024, True), (13, 3, 200, False),
+                                            (32, 1, 512, True), (64, 4, 256, True)])
+def test_gate_linear_topk_softmax(dtype, n_exp, k, d, bias):
+    r"""Single-pass linear gate against fp32 ``linear`` → ``topk`` → ``softmax``, forward and backward,
+    with gradients arriving through the probabilities and through the logits."""
+    from fastmoe_b200.ops import gating
+    torch.manual_seed(11)
+    n = 777
+    x = torch.randn(n, d, device=DEV, dtype=dtype).requires_grad_(True)
+    w = (torch.randn(n_exp, d, device=DEV) / d ** 0.5).to(dtype).requires_grad_(True)
+    b = (torch.randn(n_exp, device=DEV) * 0.1).to(dtype).requires_grad_(True) if bias else None
+    # the autograd function directly: the public wrapper only picks it for small expert counts
+    logits, idx, prob = gating._LinearTopkSoftmax.apply(x, w, b, k)
+    assert logits.dtype == dtype and idx.dtype == torch.int64 and prob.shape == (n, k)
+
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    br = b.detach().float().requires_grad_(True) if bias else None
+    lr = torch.nn.functional.linear(xr, wr, br)
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    assert torch.allclose(logits.float(), lr, atol=tol, rtol=tol)
+    # the selection is made on the rounded logits the kernel returns
+    rv, _ = torch.topk(logits.detach().float(), k, dim=-1)
+    assert torch.equal(torch.gather(logits.detach().float(), 1, idx), rv)
+    rp = torch.softmax(torch.gather(lr, 1, idx), -1)
+    assert torch.allclose(prob.float(), rp, atol=tol)
+
+    gp = torch.randn_like(prob)
+    gl = torch.randn_like(logits) * 0.1
+    torch.autograd.backward([prob, logits], [gp, gl])
+    torch.autograd.backward([rp, lr], [gp.float(), gl.float()])
+
+    def close(a, r):
+        scale = r.abs().max().item() + 1e-6
+        return (a.float() - r).abs().max().item() <= 2e-2 * scale
+
+    assert close(x.grad, xr.grad)
+    assert close(w.grad, wr.grad)
+    if bias:
+        assert close(b.grad, br.grad)
+
+    # gradient through the probabilities only (the plain top-k gate)
+    x2 = x.detach().clone().requires_grad_(True)
+    _, _, p2 = gating._LinearTopkSoftmax.apply(x2, w.detach(), None if b is None else b.detach(), k)
+    p2.backward(gp)
+    xr2 = x.detach().float().requires_grad_(True)
+    lr2 = torch.nn.functional.linear(xr2, wr.detach(), None if br is None else br.detach())
+    torch.softmax(torch.gather(lr2, 1, idx), -1).backward(gp.float())
+    assert close(x2.grad, xr2.grad)
