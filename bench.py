@@ -198,7 +198,19 @@ def main():
         raise
 
     graphed = args.impl == "ours" and os.environ.get("FMOE_BENCH_GRAPH", "1") == "1"
-    opt = torch.optim.Adam(layer.parameters(), lr=1e-4, fused=True, capturable=graphed)
+    overlap = args.impl == "ours" and world > 1 and os.environ.get("FMOE_BENCH_OVERLAP", "1") == "1"
+    if overlap:
+        # Same Adam over the same parameters, as two optimizer objects: the expert parameters
+        # need no gradient reduction, so their update runs while the gate gradients are being
+        # all-reduced on the wrapper's side stream.
+        local_params = [p for p in layer.parameters() if getattr(p, "dp_comm", "dp") == "none"]
+        local_ids = {id(p) for p in local_params}
+        synced_params = [p for p in layer.parameters() if id(p) not in local_ids]
+        opt_local = torch.optim.Adam(local_params, lr=1e-4, fused=True, capturable=graphed)
+        opt = torch.optim.Adam(synced_params, lr=1e-4, fused=True, capturable=graphed)
+    else:
+        opt_local = None
+        opt = torch.optim.Adam(layer.parameters(), lr=1e-4, fused=True, capturable=graphed)
     n_inputs = 4
     gen = torch.Generator(device="cpu").manual_seed(99 + rank)
     host_inputs = [torch.randn(TOKENS_PER_GPU, D_MODEL, generator=gen).to(torch.bfloat16).pin_memory()
@@ -208,13 +220,19 @@ def main():
 
     def step(x):
         opt.zero_grad(set_to_none=True)
+        if opt_local is not None:
+            opt_local.zero_grad(set_to_none=True)
         x = x.detach().requires_grad_(True)
         y = model(x)
         loss = y.sum()
         if layer.gate.has_loss:
             loss = loss + layer.gate.get_loss().sum().to(loss.dtype)
         loss.backward()
-        if world > 1:
+        if opt_local is not None:
+            pending = model.allreduce_params(async_op=True)
+            opt_local.step()
+            pending.wait()
+        elif world > 1:
             model.allreduce_params()
         opt.step()
         return loss

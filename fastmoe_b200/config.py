@@ -114,3 +114,10 @@ def recv_capacity_factor():
     overflow into a reported error.
     """
     return float_from_env("FMOE_RECV_CAPACITY_FACTOR", 0.0)
+
+
+def push_before_wgrad():
+    r"""``FMOE_PUSH_BEFORE_WGRAD`` (default on): in the fused expert-parallel backward, queue the
+    input-gradient GEMM whose epilogue returns rows to their sources before the two weight
+    gradients, so that the flight time of the remote stores is covered by local GEMMs."""
+    return switch_from_env("FMOE_PUSH_BEFORE_WGRAD", True)

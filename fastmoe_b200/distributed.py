@@ -29,6 +29,18 @@ def _bucket_params(params, need_grad):
     return buckets
 
 
+class _ReduceHandle:
+    r"""Returned by ``allreduce_gradients(async_op=True)``."""
+
+    def __init__(self, stream):
+        self._stream = stream
+
+    def wait(self):
+        if self._stream is not None:
+            torch.cuda.current_stream().wait_stream(self._stream)
+            self._stream = None
+
+
 class DistributedGroupedDataParallel(nn.Module):
     r"""Wraps ``module``; call :meth:`allreduce_params` after backward.
 
@@ -41,6 +53,7 @@ class DistributedGroupedDataParallel(nn.Module):
         super().__init__()
         self.module = module
         self.comms = {}
+        self._side_stream = None
         for name, group in kwargs.items():
             if name.endswith("_group"):
                 self.comms[name[:-len("_group")]] = group
@@ -51,8 +64,27 @@ class DistributedGroupedDataParallel(nn.Module):
             self._sync_params()
 
     # -------------------------------------------------------------- gradient reduction
-    def allreduce_gradients(self, no_scale=False, reduce_after=False, fp32_allreduce=False):
-        r"""Average (or sum, with ``no_scale``) gradients inside each parameter's group."""
+    def allreduce_gradients(self, no_scale=False, reduce_after=False, fp32_allreduce=False,
+                            async_op=False):
+        r"""Average (or sum, with ``no_scale``) gradients inside each parameter's group.
+
+        ``async_op=True`` (CUDA only; not in the reference) issues the reductions on a side
+        stream behind everything already queued on the current stream and returns a handle;
+        ``handle.wait()`` makes the current stream wait for them.  Work that does not touch
+        the reduced gradients — typically the optimizer step of the expert parameters, which
+        are not reduced under expert parallelism — can be queued in between and overlaps the
+        latency-bound all-reduce.  ``wait()`` must come before the next forward of the model.
+        The fork and the join are stream dependencies, so they can be captured in a CUDA graph.
+        """
+        if async_op and torch.cuda.is_available():
+            main = torch.cuda.current_stream()
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream()
+            side = self._side_stream
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                self.allreduce_gradients(no_scale, reduce_after, fp32_allreduce)
+            return _ReduceHandle(side)
         from .ops import allreduce as _ar
         for (dp_comm, dtype), group_params in _bucket_params(self.module.parameters(), True).items():
             if dp_comm not in self.comms:

@@ -278,13 +278,30 @@ class _FusedEPMLP(Function):
         dys = torch.empty(capacity, d, dtype=dout.dtype, device=dout.device)
         ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, None, total, dys, None)
 
-        dw2, db2 = gg.wgrad(dys, a, expert_offs, n_expert, with_bias_grad=True)
+        # By default the input-gradient chain goes first and its last GEMM pushes the rows home
+        # from its epilogue; both weight gradients are queued behind it, so the flight time of
+        # the last remote stores and the arrival handshake are covered by local tensor-core
+        # work before the combine waits for them.
+        push_first = config.push_before_wgrad()
+        need_dx = ctx.needs_input_grad[0]
+        dw2 = db2 = None
+        if not push_first:
+            dw2, db2 = gg.wgrad(dys, a, expert_offs, n_expert, with_bias_grad=True)
         da = gg.dgrad(dys, w2, expert_offs, pre=pre, act=act)
-        dw1, db1 = gg.wgrad(da, xs, expert_offs, n_expert, with_bias_grad=True)
         dx = None
-        if ctx.needs_input_grad[0]:
-            stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * dout.element_size())
+
+        def push():
+            stage, ret_ptrs = ws.buffer("ret", idx.numel() * d * dout.element_size())
             ws.ctx.gemm_push(gg.MODE_NN, da, w1, expert_offs, None, meta, ret_ptrs)
+            return stage
+
+        stage_ret = push() if (need_dx and push_first) else None
+        if push_first:
+            dw2, db2 = gg.wgrad(dys, a, expert_offs, n_expert, with_bias_grad=True)
+        dw1, db1 = gg.wgrad(da, xs, expert_offs, n_expert, with_bias_grad=True)
+        if need_dx:
+            if stage_ret is None:
+                stage_ret = push()
             dx = torch.empty(n_tok, d, dtype=dout.dtype, device=dout.device)
             ws.ctx.wait_combine(stage_ret, idx, None, k, dx, None)
         return (dx, dscore, dw1, db1, dw2, db2) + (None,) * 8

@@ -100,6 +100,14 @@ def case_grouped_ddp():
     dist.all_reduce(ref)
     assert torch.allclose(layer.gate.gate.weight.grad.float(), ref / world, atol=1e-2, rtol=2e-2)
     assert torch.equal(layer.experts.htoh4.weight.grad, expert_before)
+    # the same reduction issued on the side stream, with unrelated work queued in between
+    layer.gate.gate.weight.grad.copy_(local.to(layer.gate.gate.weight.grad.dtype))
+    pending = model.allreduce_params(async_op=True)
+    busy = expert_before.float().square().sum()
+    pending.wait()
+    torch.cuda.synchronize()
+    assert torch.allclose(layer.gate.gate.weight.grad.float(), ref / world, atol=1e-2, rtol=2e-2)
+    assert torch.isfinite(busy)
 
 
 def case_wait_timeout():
