@@ -417,6 +417,78 @@ __global__ void allreduce_kernel(ExchangeCtx c, PeerPtrs bufs, T* __restrict__ o
   }
 }
 
+// Two-shot: rank r owns the r-th slice of the vectors.  It sums that slice over all peers'
+// buffers (rank order, fp32), scales, and stores the result into the same slice of EVERY
+// peer's buffer (nobody else reads or writes slice r); after all ranks have published "my
+// slices are written", each rank copies its own, now fully reduced, buffer to `out`.  Per GPU
+// (W - 1) / W of the bytes are read and as many written over NVLink, against (W - 1) times the
+// bytes for the one-shot kernel, so this is the kernel for large buckets.  The buffer must
+// hold the element count rounded up to a whole vector.
+template <typename T, typename Vec, int PER>
+__global__ void allreduce_two_shot_kernel(ExchangeCtx c, PeerPtrs bufs, T* __restrict__ out, long n,
+                                          float scale) {
+  const int target_ready = 2 * c.epoch[0];
+  if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(c, kChanReduce, target_ready);
+  block_wait_all(c, kChanReduce, target_ready);
+  const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  const long nvec = (n + PER - 1) / PER;
+  const long per_rank = (nvec + c.world - 1) / c.world;
+  const long lo = per_rank * c.me;
+  const long hi = (lo + per_rank < nvec) ? lo + per_rank : nvec;
+  for (long i = lo + tid; i < hi; i += stride) {
+    float acc[PER];
+#pragma unroll
+    for (int q = 0; q < PER; ++q) acc[q] = 0.f;
+    for (int p = 0; p < c.world; ++p) {
+      Vec v = __ldcg(reinterpret_cast<const Vec*>(bufs.p[p]) + i);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int q = 0; q < PER; ++q) acc[q] += as_float(e[q]);
+    }
+    Vec r;
+    T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+    for (int q = 0; q < PER; ++q) e[q] = from_float<T>(acc[q] * scale);
+    for (int p = 0; p < c.world; ++p) reinterpret_cast<Vec*>(bufs.p[p])[i] = r;
+  }
+  if (last_block(c.epoch + 3)) {
+    if (threadIdx.x == 0) signal_all(c, kChanReduce, target_ready + 1);
+  }
+  block_wait_all(c, kChanReduce, target_ready + 1);
+  const Vec* mine = reinterpret_cast<const Vec*>(bufs.p[c.me]);
+  const long nfull = n / PER;
+  for (long i = tid; i < nfull; i += stride) reinterpret_cast<Vec*>(out)[i] = __ldcg(mine + i);
+  for (long i = nfull * PER + tid; i < n; i += stride) {
+    out[i] = *(reinterpret_cast<const volatile T*>(bufs.p[c.me]) + i);
+  }
+}
+
+// All-gather of equal slices: every rank stores its slice at offset `me` of every peer's
+// symmetric buffer, publishes, waits for all peers and copies the assembled buffer out.
+// The first handshake makes sure no peer is still reading its buffer from an earlier call.
+__global__ void allgather_kernel(ExchangeCtx c, const uint4* __restrict__ src, PeerPtrs bufs,
+                                 uint4* __restrict__ out, long nvec) {
+  const int target_ready = 2 * c.epoch[0];
+  if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(c, kChanReduce, target_ready);
+  block_wait_all(c, kChanReduce, target_ready);
+  const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i = tid; i < nvec; i += stride) {
+    const uint4 v = __ldg(src + i);
+    for (int p = 0; p < c.world; ++p) {
+      reinterpret_cast<uint4*>(bufs.p[p])[static_cast<long>(c.me) * nvec + i] = v;
+    }
+  }
+  if (last_block(c.epoch + 3)) {
+    if (threadIdx.x == 0) signal_all(c, kChanReduce, target_ready + 1);
+  }
+  block_wait_all(c, kChanReduce, target_ready + 1);
+  const uint4* mine = reinterpret_cast<const uint4*>(bufs.p[c.me]);
+  const long total = nvec * c.world;
+  for (long i = tid; i < total; i += stride) out[i] = __ldcg(mine + i);
+}
+
 __global__ void wait_only_kernel(ExchangeCtx c, int channel) {
   // Waits for an epoch nobody will publish: exercises the time-out path.
   block_wait_all(c, channel, c.epoch[0] + 1000000);
@@ -530,6 +602,41 @@ cudaError_t launch_allreduce(const ExchangeCtx& ctx, int dtype, const PeerPtrs& 
   } else {
     return cudaErrorInvalidValue;
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_allreduce_two_shot(const ExchangeCtx& ctx, int dtype, const PeerPtrs& bufs,
+                                      void* out, long n, float scale, cudaStream_t stream) {
+  // Every block waits for the peers in the middle of the kernel, so the whole grid must be
+  // resident at once: at most two 256-thread blocks per SM.
+  long blocks = (n / 8 / ctx.world + 255) / 256;
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks < 1) blocks = 1;
+  const int grid = static_cast<int>(blocks);
+  if (dtype == 0) {
+    allreduce_two_shot_kernel<__nv_bfloat16, uint4, 8><<<grid, 256, 0, stream>>>(
+        ctx, bufs, static_cast<__nv_bfloat16*>(out), n, scale);
+  } else if (dtype == 1) {
+    allreduce_two_shot_kernel<__half, uint4, 8><<<grid, 256, 0, stream>>>(
+        ctx, bufs, static_cast<__half*>(out), n, scale);
+  } else if (dtype == 2) {
+    allreduce_two_shot_kernel<float, uint4, 4><<<grid, 256, 0, stream>>>(
+        ctx, bufs, static_cast<float*>(out), n, scale);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_allgather(const ExchangeCtx& ctx, const void* src, const PeerPtrs& bufs,
+                             void* out, long bytes_per_rank, cudaStream_t stream) {
+  if (bytes_per_rank % 16 != 0) return cudaErrorInvalidValue;
+  const long nvec = bytes_per_rank / 16;
+  long blocks = (nvec * ctx.world + 255) / 256;  // the copy-out is the larger loop
+  if (blocks > 148 * 2) blocks = 148 * 2;        // whole grid resident: every block waits mid-kernel
+  if (blocks < 1) blocks = 1;
+  allgather_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+      ctx, static_cast<const uint4*>(src), bufs, static_cast<uint4*>(out), nvec);
   return cudaGetLastError();
 }
 

@@ -86,6 +86,16 @@ cudaError_t launch_slot_dot(int dtype, const void* dout, const void* y, const in
 cudaError_t launch_allreduce(const ExchangeCtx& ctx, int dtype, const PeerPtrs& bufs, void* out,
                              long n, float scale, cudaStream_t stream);
 
+// Same result for large buckets (two-shot: reduce-scatter into every peer's buffer, then a
+// local copy-out).  The symmetric buffers must hold `n` rounded up to 16 bytes.
+cudaError_t launch_allreduce_two_shot(const ExchangeCtx& ctx, int dtype, const PeerPtrs& bufs,
+                                      void* out, long n, float scale, cudaStream_t stream);
+
+// All-gather of equal slices (`bytes_per_rank` a multiple of 16) through symmetric buffers of
+// at least world * bytes_per_rank bytes: out = [slice of rank 0, slice of rank 1, ...].
+cudaError_t launch_allgather(const ExchangeCtx& ctx, const void* src, const PeerPtrs& bufs,
+                             void* out, long bytes_per_rank, cudaStream_t stream);
+
 // Test hook: waits on `channel` for flags that nothing sets, with the given limit; the
 // kernel returns and leaves kStatusPeerTimeout in the status word.
 cudaError_t launch_wait_only(const ExchangeCtx& ctx, int channel, cudaStream_t stream);

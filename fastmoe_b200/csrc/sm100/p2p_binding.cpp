@@ -112,7 +112,8 @@ class ExchangeContext {
                                              stream()));
   }
 
-  void allreduce(std::vector<int64_t> buf_ptrs, torch::Tensor out, int64_t n, double scale) {
+  void allreduce(std::vector<int64_t> buf_ptrs, torch::Tensor out, int64_t n, double scale,
+                 bool two_shot) {
     c10::cuda::CUDAGuard guard(out.device());
     int code;
     switch (out.scalar_type()) {
@@ -122,8 +123,27 @@ class ExchangeContext {
       default: TORCH_CHECK(false, "allreduce: bf16, fp16 or fp32"); code = -1;
     }
     FMOE_P2P_CHECK(fmoe::launch_begin_epoch(ctx_, stream()));
-    FMOE_P2P_CHECK(fmoe::launch_allreduce(ctx_, code, to_ptrs(buf_ptrs), out.data_ptr(), n,
-                                          static_cast<float>(scale), stream()));
+    if (two_shot) {
+      FMOE_P2P_CHECK(fmoe::launch_allreduce_two_shot(ctx_, code, to_ptrs(buf_ptrs), out.data_ptr(),
+                                                     n, static_cast<float>(scale), stream()));
+    } else {
+      FMOE_P2P_CHECK(fmoe::launch_allreduce(ctx_, code, to_ptrs(buf_ptrs), out.data_ptr(), n,
+                                            static_cast<float>(scale), stream()));
+    }
+  }
+
+  // out[r * n : (r + 1) * n] = rank r's `src` (flat bytes; src.nbytes a multiple of 16).
+  void allgather(torch::Tensor src, std::vector<int64_t> buf_ptrs, torch::Tensor out) {
+    TORCH_CHECK(src.is_cuda() && src.is_contiguous() && out.is_contiguous(), "allgather operands");
+    const int64_t bytes = src.numel() * src.element_size();
+    TORCH_CHECK(out.numel() * out.element_size() == bytes * ctx_.world, "allgather out size");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(src.data_ptr()) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0,
+                "allgather operands must be 16-byte aligned");
+    c10::cuda::CUDAGuard guard(out.device());
+    FMOE_P2P_CHECK(fmoe::launch_begin_epoch(ctx_, stream()));
+    FMOE_P2P_CHECK(fmoe::launch_allgather(ctx_, src.data_ptr(), to_ptrs(buf_ptrs), out.data_ptr(),
+                                          bytes, stream()));
   }
 
   // Grouped GEMM (forward mode 0 or input-gradient mode 1) whose epilogue stores each result
@@ -201,7 +221,9 @@ void bind_p2p(pybind11::module& m) {
       .def("wait_copy", &ExchangeContext::wait_copy)
       .def("return_push", &ExchangeContext::return_push)
       .def("wait_combine", &ExchangeContext::wait_combine)
-      .def("allreduce", &ExchangeContext::allreduce)
+      .def("allgather", &ExchangeContext::allgather)
+      .def("allreduce", &ExchangeContext::allreduce, py::arg("buf_ptrs"), py::arg("out"),
+           py::arg("n"), py::arg("scale"), py::arg("two_shot") = false)
       .def("gemm_push", &ExchangeContext::gemm_push)
       .def("wait_only", &ExchangeContext::wait_only);
   m.def("slot_dot", &slot_dot);

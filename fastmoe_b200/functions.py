@@ -127,9 +127,13 @@ class AllGather(Function):
     @staticmethod
     def forward(ctx, inp, rank, world_size, group):
         inp = inp.contiguous()
-        out = inp.new_empty((world_size * inp.shape[0],) + tuple(inp.shape[1:]))
-        dist.all_gather_into_tensor(out, inp, group=group) if inp.is_cuda else \
-            _all_gather_cat(out, inp, world_size, group)
+        out = _p2p_allgather(inp, group)
+        if out is None:
+            out = inp.new_empty((world_size * inp.shape[0],) + tuple(inp.shape[1:]))
+            if inp.is_cuda:
+                dist.all_gather_into_tensor(out, inp, group=group)
+            else:
+                _all_gather_cat(out, inp, world_size, group)
         ctx.args = rank, inp.shape[0]
         return out
 
@@ -137,6 +141,14 @@ class AllGather(Function):
     def backward(ctx, grad_out):
         rank, n = ctx.args
         return grad_out[rank * n:(rank + 1) * n], None, None, None
+
+
+def _p2p_allgather(inp, group, out=None):
+    r"""Peer-to-peer all-gather on GPUs with a symmetric workspace, else ``None``."""
+    if not inp.is_cuda:
+        return None
+    from .parallel import symm
+    return symm.allgather_rows(inp, group, out)
 
 
 def _all_gather_cat(out, inp, world_size, group):
@@ -162,7 +174,9 @@ class Slice(Function):
         grad_out = grad_out.contiguous()
         out = grad_out.new_zeros((full,) + tuple(grad_out.shape[1:]))
         covered = out[:world_size * grad_out.shape[0]]
-        if grad_out.is_cuda:
+        if _p2p_allgather(grad_out, group, out=covered) is not None:
+            pass
+        elif grad_out.is_cuda:
             dist.all_gather_into_tensor(covered, grad_out, group=group)
         else:
             _all_gather_cat(covered, grad_out, world_size, group)

@@ -334,7 +334,18 @@ def moe_mlp_forward(layer, x, gate_idx, gate_score):
 # Gradient all-reduce of replicated parameters
 # ------------------------------------------------------------------------------------------
 _AR_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
-_AR_MAX_BYTES = 64 * 1024 * 1024
+_AR_MAX_BYTES = 1024 * 1024 * 1024
+# Above this size the two-shot kernel (each rank reduces one slice and writes it to all peers)
+# moves fewer bytes over NVLink than the one-shot kernel (each rank reads every peer in full).
+_AR_TWO_SHOT_BYTES = 512 * 1024
+
+
+def _ar_buffer_bytes(nbytes):
+    return (nbytes + 15) // 16 * 16
+
+
+def _two_shot(nbytes, world):
+    return world > 2 and nbytes >= _AR_TWO_SHOT_BYTES or nbytes >= 8 * _AR_TWO_SHOT_BYTES
 
 
 def allreduce_grads(grads, comm, scale, fp32_accumulate=False):  # pylint: disable=unused-argument
@@ -356,8 +367,9 @@ def allreduce_grads(grads, comm, scale, fp32_accumulate=False):  # pylint: disab
     ws = get_workspace(comm, grads[0].device)
     if ws is None:
         return False
-    buf, ptrs = ws.buffer("allreduce", n * grads[0].element_size())
-    flat = buf[:n * grads[0].element_size()].view(dtype)
+    nbytes = n * grads[0].element_size()
+    buf, ptrs = ws.buffer("allreduce", _ar_buffer_bytes(nbytes))
+    flat = buf[:nbytes].view(dtype)
     views = []
     offset = 0
     for g in grads:
@@ -365,7 +377,7 @@ def allreduce_grads(grads, comm, scale, fp32_accumulate=False):  # pylint: disab
         offset += g.numel()
     torch._foreach_copy_(views, grads)  # pylint: disable=protected-access
     out = torch.empty(n, dtype=dtype, device=grads[0].device)
-    ws.ctx.allreduce(ptrs, out, n, float(scale))
+    ws.ctx.allreduce(ptrs, out, n, float(scale), _two_shot(nbytes, ws.world))
     outs = []
     offset = 0
     for g in grads:
@@ -393,8 +405,37 @@ def allreduce_flat(flat, comm, scale=1.0):
     if ws is None:
         return None
     n = flat.numel()
-    buf, ptrs = ws.buffer("allreduce", n * flat.element_size())
-    buf[:n * flat.element_size()].view(flat.dtype).copy_(flat.reshape(-1))
+    nbytes = n * flat.element_size()
+    buf, ptrs = ws.buffer("allreduce", _ar_buffer_bytes(nbytes))
+    buf[:nbytes].view(flat.dtype).copy_(flat.reshape(-1))
     out = torch.empty(n, dtype=flat.dtype, device=flat.device)
-    ws.ctx.allreduce(ptrs, out, n, float(scale))
+    ws.ctx.allreduce(ptrs, out, n, float(scale), _two_shot(nbytes, ws.world))
+    return out
+
+
+def allgather_rows(inp, comm, out=None):
+    r"""``out = cat([inp of rank 0, inp of rank 1, ...])`` with peer-to-peer stores, or ``None``
+    when that path is not available (caller uses the collective library).
+
+    Parity: the all-gather of ``fmoe/functions.py:308-329`` (``AllGather.forward``,
+    ``Slice.backward``), which the reference follows with a device synchronisation.
+    """
+    if not inp.is_cuda or not config.fused_enabled():
+        return None
+    if comm is None:
+        comm = dist.group.WORLD
+    nbytes = inp.numel() * inp.element_size()
+    if (dist.get_backend(comm) != "nccl" or nbytes == 0 or nbytes % 16 != 0
+            or nbytes * dist.get_world_size(comm) > _AR_MAX_BYTES):
+        return None
+    ws = get_workspace(comm, inp.device)
+    if ws is None:
+        return None
+    inp = inp.contiguous()
+    if inp.data_ptr() % 16 != 0:
+        inp = inp.clone()
+    _buf, ptrs = ws.buffer("allgather", nbytes * ws.world)
+    if out is None:
+        out = inp.new_empty((ws.world * inp.shape[0],) + tuple(inp.shape[1:]))
+    ws.ctx.allgather(inp, ptrs, out)
     return out

@@ -84,6 +84,23 @@ def case_allreduce():
         other = mine.clone()
         dist.broadcast(other, 0)
         assert torch.equal(mine, other)
+    # a bucket large enough for the two-shot kernel, with a ragged element count
+    for dtype in (torch.bfloat16, torch.float32):
+        torch.manual_seed(100 + rank)
+        grads = [torch.randn(2048, 1537, device=_dev()).to(dtype), torch.randn(3, device=_dev()).to(dtype)]
+        nbytes = sum(g.numel() for g in grads) * grads[0].element_size()
+        assert symm._two_shot(nbytes, world)  # pylint: disable=protected-access
+        ref = [g.float().clone() for g in grads]
+        for r in ref:
+            dist.all_reduce(r)
+        assert symm.allreduce_grads(grads, dist.group.WORLD, 1.0 / world)
+        for g, r in zip(grads, ref):
+            assert torch.allclose(g.float(), r / world, atol=2e-2, rtol=2e-2)
+        mine = grads[0].float()
+        other = mine.clone()
+        dist.broadcast(other, 0)
+        assert torch.equal(mine, other)
+        assert native.get().read_status(_dev().index) == 0
 
 
 def case_grouped_ddp():
@@ -108,6 +125,43 @@ def case_grouped_ddp():
     torch.cuda.synchronize()
     assert torch.allclose(layer.gate.gate.weight.grad.float(), ref / world, atol=1e-2, rtol=2e-2)
     assert torch.isfinite(busy)
+
+
+def case_slice_group():
+    r"""Peer-to-peer all-gather (rows of every rank in rank order), then a layer with
+    ``slice_group``: ranks share the input, each routes its slice, outputs are all-gathered."""
+    from fastmoe_b200.functions import AllGather, Slice
+    rank, world = dist.get_rank(), dist.get_world_size()
+    for rows, cols, dtype in ((5, 24, torch.bfloat16), (300, 256, torch.float32)):
+        torch.manual_seed(3 + rank)
+        mine = torch.randn(rows, cols, device=_dev()).to(dtype)
+        got = symm.allgather_rows(mine, dist.group.WORLD)
+        assert got is not None
+        ref = torch.empty(world * rows, cols, device=_dev(), dtype=dtype)
+        dist.all_gather_into_tensor(ref, mine)
+        assert torch.equal(got, ref)
+    # differentiable wrappers: AllGather backward keeps the own slice, Slice backward gathers
+    torch.manual_seed(8)
+    full = torch.randn(8 * world, 16, device=_dev(), requires_grad=True)
+    part = Slice.apply(full, rank, world, dist.group.WORLD)
+    back = AllGather.apply(part * (rank + 1.0), rank, world, dist.group.WORLD)
+    scale = torch.arange(1, world + 1, device=_dev(), dtype=torch.float32).repeat_interleave(8)[:, None]
+    assert torch.allclose(back, full.detach() * scale)
+    back.sum().backward()
+    assert torch.allclose(full.grad, torch.ones_like(full) * scale)
+    torch.manual_seed(9)
+    moe = FMoETransformerMLP(num_expert=2, d_model=256, d_hidden=512, world_size=1, top_k=2,
+                             slice_group=dist.group.WORLD).to(_dev()).to(torch.bfloat16)
+    ref_layer = FMoETransformerMLP(num_expert=2, d_model=256, d_hidden=512, world_size=1,
+                                   top_k=2).to(_dev()).to(torch.bfloat16)
+    ref_layer.load_state_dict(moe.state_dict())
+    x = torch.randn(64 * world, 256, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    y = moe(x)
+    ref = ref_layer(x.detach())
+    assert torch.allclose(y.float(), ref.float(), atol=3e-2, rtol=3e-2)
+    y.float().sum().backward()
+    assert x.grad.shape == x.shape
+    assert native.get().read_status(_dev().index) == 0
 
 
 def case_wait_timeout():
