@@ -187,6 +187,50 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return w;
 }
 
+// Capacity grants in one exchange.  Every rank writes its per-expert request counts and its
+// own per-expert capacities into every peer's matrix; with the full matrix on every rank the
+// rank-ordered grants (`grant[w][g] = min(request[w][g], what ranks < w left of cap[g])`) are
+// computed locally by everybody, so the second all-to-all of the reference
+// (fmoe/gates/utils.py:19-24: grants travel back to the requesters) is not needed.
+// Matrix row of rank w: [tot request counts | n_expert capacities]; two matrices alternate
+// with the epoch so that a fast rank cannot overwrite a matrix a slow rank still reads.
+__global__ void __launch_bounds__(1024, 1)
+capacity_grant_kernel(ExchangeCtx c, const int* __restrict__ lec, const int* __restrict__ cap,
+                      PeerPtrs cnt, int n_expert, int64_t* __restrict__ new_lec,
+                      int64_t* __restrict__ new_gec) {
+  extern __shared__ int sh[];
+  const int tot = n_expert * c.world;
+  const int width = tot + n_expert;
+  const int epoch = c.epoch[0];
+  const long half = static_cast<long>(epoch & 1) * c.world * width;
+  for (int g = threadIdx.x; g < width; g += blockDim.x) {
+    const int v = g < tot ? lec[g] : cap[g - tot];
+    for (int p = 0; p < c.world; ++p) static_cast<int*>(cnt.p[p])[half + c.me * width + g] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < c.world) {
+    st_release_sys(flag_of(c.flags.p[threadIdx.x], kChanCounts, c.me), epoch);
+  }
+  block_wait_all(c, kChanCounts, epoch);
+  const volatile int* mine = static_cast<const volatile int*>(cnt.p[c.me]) + half;
+  for (int i = threadIdx.x; i < c.world * width; i += blockDim.x) sh[i] = mine[i];
+  __syncthreads();
+  for (int g = threadIdx.x; g < tot; g += blockDim.x) {
+    const int owner = g / n_expert;
+    const int e = g - owner * n_expert;
+    int remaining = sh[owner * width + tot + e];
+    for (int w = 0; w < c.world; ++w) {
+      const int want = sh[w * width + g];
+      const int grant = want < remaining ? want : remaining;
+      remaining -= grant;
+      if (w == c.me) new_lec[g] = grant;
+      if (owner == c.me) new_gec[w * n_expert + e] = grant;
+    }
+  }
+}
+
+
 // ------------------------------------------------------------------------------ dispatch
 // One warp per slot, persistent grid.  Stores go to the owner's staging buffer over NVLink.
 template <typename T>
@@ -520,6 +564,21 @@ cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const 
   }
   count_exchange_kernel<<<1, 1024, smem, stream>>>(ctx, lec, cnt, n_expert, capacity_rows, dst_base,
                                                    expert_offs, total_rows);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_capacity_grant(const ExchangeCtx& ctx, const int* lec, const int* cap,
+                                  const PeerPtrs& cnt, int n_expert, int64_t* new_lec,
+                                  int64_t* new_gec, cudaStream_t stream) {
+  const int width = n_expert * ctx.world + n_expert;
+  const size_t smem = static_cast<size_t>(ctx.world) * width * sizeof(int);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(capacity_grant_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+  }
+  capacity_grant_kernel<<<1, 1024, smem, stream>>>(ctx, lec, cap, cnt, n_expert, new_lec, new_gec);
   return cudaGetLastError();
 }
 

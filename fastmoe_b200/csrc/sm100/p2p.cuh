@@ -96,6 +96,15 @@ cudaError_t launch_allreduce_two_shot(const ExchangeCtx& ctx, int dtype, const P
 cudaError_t launch_allgather(const ExchangeCtx& ctx, const void* src, const PeerPtrs& bufs,
                              void* out, long bytes_per_rank, cudaStream_t stream);
 
+// Rank-ordered capacity grants from one exchange of request counts and capacities.
+// lec: int32 [world * n_expert] requests of this rank; cap: int32 [n_expert] capacities of this
+// rank's experts; cnt: symmetric int32 buffers of 2 * world * (world + 1) * n_expert entries.
+// new_lec[g]: what this rank may send to global expert g; new_gec[w * n_expert + e]: what rank
+// w may send to local expert e.  Call launch_begin_epoch right before.
+cudaError_t launch_capacity_grant(const ExchangeCtx& ctx, const int* lec, const int* cap,
+                                  const PeerPtrs& cnt, int n_expert, int64_t* new_lec,
+                                  int64_t* new_gec, cudaStream_t stream);
+
 // Test hook: waits on `channel` for flags that nothing sets, with the given limit; the
 // kernel returns and leaves kStatusPeerTimeout in the status word.
 cudaError_t launch_wait_only(const ExchangeCtx& ctx, int channel, cudaStream_t stream);

@@ -60,6 +60,24 @@ class ExchangeContext {
         total_rows.data_ptr<int>(), stream()));
   }
 
+  std::vector<torch::Tensor> capacity_grant(torch::Tensor lec, torch::Tensor cap,
+                                            std::vector<int64_t> cnt_ptrs, int64_t n_expert) {
+    TORCH_CHECK(lec.scalar_type() == torch::kInt && cap.scalar_type() == torch::kInt,
+                "capacity_grant: int32 counts and capacities");
+    TORCH_CHECK(lec.numel() == n_expert * ctx_.world && cap.numel() == n_expert,
+                "capacity_grant: shapes");
+    c10::cuda::CUDAGuard guard(lec.device());
+    auto opts = torch::dtype(torch::kLong).device(lec.device());
+    auto new_lec = torch::empty({lec.numel()}, opts);
+    auto new_gec = torch::empty({lec.numel()}, opts);
+    FMOE_P2P_CHECK(fmoe::launch_begin_epoch(ctx_, stream()));
+    FMOE_P2P_CHECK(fmoe::launch_capacity_grant(ctx_, lec.data_ptr<int>(), cap.data_ptr<int>(),
+                                               to_ptrs(cnt_ptrs), static_cast<int>(n_expert),
+                                               new_lec.data_ptr<int64_t>(),
+                                               new_gec.data_ptr<int64_t>(), stream()));
+    return {new_lec, new_gec};
+  }
+
   void begin_epoch() {
     c10::cuda::CUDAGuard guard(epoch_.device());
     FMOE_P2P_CHECK(fmoe::launch_begin_epoch(ctx_, stream()));
@@ -216,6 +234,7 @@ void bind_p2p(pybind11::module& m) {
       .def(py::init<std::vector<int64_t>, torch::Tensor, int64_t, int64_t, torch::Tensor, double>())
       .def("set_timeout_ms", &ExchangeContext::set_timeout_ms)
       .def("count_exchange", &ExchangeContext::count_exchange)
+      .def("capacity_grant", &ExchangeContext::capacity_grant)
       .def("begin_epoch", &ExchangeContext::begin_epoch)
       .def("dispatch_push", &ExchangeContext::dispatch_push)
       .def("wait_copy", &ExchangeContext::wait_copy)

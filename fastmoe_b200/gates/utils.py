@@ -13,6 +13,17 @@ def limit_by_capacity(topk_idx, num_expert, world_size, capacity):
     """
     with torch.no_grad():
         cap = torch.full((num_expert,), int(capacity), dtype=torch.int32, device=topk_idx.device)
+        if world_size > 1 and topk_idx.is_cuda:
+            # One peer-to-peer exchange of requests and capacities; every rank derives all
+            # grants from the full matrix, so nothing has to travel back.
+            from ..parallel import comm as _comm, symm as _symm
+            counts, _rank = _ops.route(topk_idx, num_expert * world_size)
+            fused = _symm.capacity_grant(counts, cap, num_expert, _comm._group(None))  # pylint: disable=protected-access
+            if fused is not None:
+                new_lec, new_gec = fused
+                topk_idx = _ops.prune_gate_by_capacity(
+                    topk_idx, new_lec.to(torch.int32), num_expert, world_size)
+                return new_lec, new_gec, topk_idx
         _, _lec, gec = count_by_gate(topk_idx, num_expert, world_size, require_pos=False)
         new_gec = _ops.limit_by_capacity(gec, cap, num_expert, world_size)
         if world_size > 1:

@@ -439,3 +439,29 @@ def allgather_rows(inp, comm, out=None):
         out = inp.new_empty((ws.world * inp.shape[0],) + tuple(inp.shape[1:]))
     ws.ctx.allgather(inp, ptrs, out)
     return out
+
+
+def capacity_grant(lec, cap, n_expert, comm=None):
+    r"""``(new_lec, new_gec)`` (int64) of a global capacity limit with ONE peer-to-peer exchange,
+    or ``None`` when that path is not available.
+
+    ``lec``: int32 ``[world * n_expert]`` slots this rank wants to send to every global expert;
+    ``cap``: int32 ``[n_expert]`` capacities of this rank's experts.  Parity: the count
+    all-to-all → ``limit_by_capacity`` → grant all-to-all sequence of
+    ``fmoe/gates/utils.py:9-26``; grants are handed out in rank order, as there.
+    """
+    if not lec.is_cuda or not config.fused_enabled():
+        return None
+    if comm is None:
+        comm = dist.group.WORLD
+    if dist.get_backend(comm) != "nccl":
+        return None
+    ws = get_workspace(comm, lec.device)
+    if ws is None:
+        return None
+    width = (ws.world + 1) * n_expert
+    if ws.world * width * 4 > 200 * 1024:
+        return None
+    _buf, ptrs = ws.buffer("capacity", 2 * ws.world * width * 4)
+    new_lec, new_gec = ws.ctx.capacity_grant(lec.contiguous(), cap.contiguous(), ptrs, n_expert)
+    return new_lec, new_gec

@@ -164,6 +164,30 @@ def case_slice_group():
     assert native.get().read_status(_dev().index) == 0
 
 
+def case_capacity():
+    r"""Global capacity limit: the single-exchange grant kernel against the two all-to-alls of
+    the collective-library path, including per-rank capacities that differ."""
+    from fastmoe_b200.functions import ensure_comm
+    from fastmoe_b200.gates.utils import limit_by_capacity
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ensure_comm(torch.zeros(1, device=_dev()), None)
+    n_expert = 3
+    for trial in range(3):
+        torch.manual_seed(40 + 7 * trial + rank)
+        idx = torch.randint(0, n_expert * world, (257 + 13 * rank, 2), device=_dev())
+        capacity = 40 + 5 * trial + (3 * rank if trial == 2 else 0)
+        os.environ["FMOE_FUSED"] = "1"
+        a_lec, a_gec, a_idx = limit_by_capacity(idx.clone(), n_expert, world, capacity)
+        os.environ["FMOE_FUSED"] = "0"
+        b_lec, b_gec, b_idx = limit_by_capacity(idx.clone(), n_expert, world, capacity)
+        os.environ["FMOE_FUSED"] = "1"
+        assert torch.equal(a_lec.long(), b_lec.long()), (a_lec, b_lec)
+        assert torch.equal(a_gec.long(), b_gec.long())
+        assert torch.equal(a_idx, b_idx)
+        assert int(a_gec.view(world, n_expert).sum(0).max()) <= capacity
+    assert native.get().read_status(_dev().index) == 0
+
+
 def case_wait_timeout():
     r"""A device wait on a flag that nothing sets returns after its limit with a status code;
     the context stays usable."""

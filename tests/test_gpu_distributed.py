@@ -22,14 +22,14 @@ def _need(world):
 
 
 @pytest.mark.parametrize("case", ["fused_vs_general", "allreduce", "grouped_ddp", "wait_timeout",
-                                  "graph_step", "smart_schedule", "slice_group"])
+                                  "graph_step", "smart_schedule", "slice_group", "capacity"])
 def test_two_ranks(case):
     _need(2)
     codes = run_ranks("dist_gpu_worker.py", case, 2, timeout=300, extra_env=ENV)
     assert codes == [0, 0], codes
 
 
-@pytest.mark.parametrize("case", ["fused_vs_general", "allreduce", "slice_group"])
+@pytest.mark.parametrize("case", ["fused_vs_general", "allreduce", "slice_group", "capacity"])
 def test_many_ranks(case):
     world = int(os.environ.get("FMOE_TEST_WORLD", "4"))
     _need(world)
