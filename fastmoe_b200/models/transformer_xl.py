@@ -15,6 +15,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..transformer import FMoETransformerMLP
+from .adaptive import AdaptiveEmbedding, ProjectedAdaptiveLogSoftmax
 
 
 class PositionalEmbedding(nn.Module):
@@ -128,18 +129,29 @@ class MemTransformerLM(nn.Module):
     Keyword arguments follow the example model: ``n_token, n_layer, n_head, d_model, d_head,
     d_inner, dropout, dropatt, tie_weight, pre_lnorm, tgt_len, ext_len, mem_len, same_length,
     clamp_len, moe, moe_num_expert, moe_top_k`` plus ``world_size`` / ``moe_group`` / ``gate``.
+    ``d_embed`` / ``cutoffs`` / ``div_val`` / ``tie_projs`` select the adaptive embedding and
+    adaptive softmax used for large vocabularies (``--adaptive`` in the training script); with
+    no cut-offs and ``d_embed == d_model`` a plain embedding and a plain (tied) output layer
+    are used.
     """
 
     def __init__(self, n_token, n_layer, n_head, d_model, d_head, d_inner, dropout=0.1, dropatt=0.0,
                  tie_weight=True, pre_lnorm=False, tgt_len=512, ext_len=0, mem_len=512,
                  same_length=False, clamp_len=-1, moe=False, moe_num_expert=64, moe_top_k=2,
-                 world_size=1, moe_group=None, gate=None):
+                 world_size=1, moe_group=None, gate=None, d_embed=None, cutoffs=(), div_val=1,
+                 tie_projs=()):
         super().__init__()
         self.n_token, self.n_layer, self.d_model = n_token, n_layer, d_model
+        d_embed = d_model if d_embed is None or d_embed <= 0 else d_embed
+        self.adaptive = bool(cutoffs) or d_embed != d_model or div_val != 1
         self.tgt_len, self.ext_len, self.mem_len = tgt_len, ext_len, mem_len
         self.same_length, self.clamp_len = same_length, clamp_len
-        self.word_emb = nn.Embedding(n_token, d_model)
-        self.emb_scale = d_model ** 0.5
+        if self.adaptive:
+            self.word_emb = AdaptiveEmbedding(n_token, d_embed, d_model, cutoffs, div_val)
+            self.emb_scale = 1.0   # the adaptive embedding applies sqrt(d_model) itself
+        else:
+            self.word_emb = nn.Embedding(n_token, d_model)
+            self.emb_scale = d_model ** 0.5
         self.drop = nn.Dropout(dropout)
         self.pos_emb = PositionalEmbedding(d_model)
         self.r_w_bias = nn.Parameter(torch.zeros(n_head, d_head))
@@ -149,10 +161,18 @@ class MemTransformerLM(nn.Module):
         self.layers = nn.ModuleList([
             DecoderLayer(n_head, d_model, d_head, d_inner, dropout, dropatt, pre_lnorm, moe, moe_kwargs)
             for _ in range(n_layer)])
-        self.out_layer = nn.Linear(d_model, n_token)
-        if tie_weight:
-            self.out_layer.weight = self.word_emb.weight
+        if self.adaptive:
+            self.crit = ProjectedAdaptiveLogSoftmax(n_token, d_embed, d_model, cutoffs, div_val)
+            self.out_layer = None
+        else:
+            self.crit = None
+            self.out_layer = nn.Linear(d_model, n_token)
         self.apply(self._init)
+        if tie_weight:
+            if self.adaptive:
+                self.crit.tie_weights(self.word_emb, tie_projs)
+            else:
+                self.out_layer.weight = self.word_emb.weight
 
     @staticmethod
     def _init(m):
@@ -169,7 +189,7 @@ class MemTransformerLM(nn.Module):
     def init_mems(self, device=None, dtype=None):
         if self.mem_len <= 0:
             return []
-        p = self.word_emb.weight
+        p = self.r_w_bias
         return [torch.empty(0, dtype=dtype or p.dtype, device=device or p.device)
                 for _ in range(self.n_layer + 1)]
 
@@ -206,9 +226,13 @@ class MemTransformerLM(nn.Module):
         mems = list(mems) if mems else self.init_mems(device=data.device)
         hidden, new_mems = self._forward(data, mems)
         tgt_len = target.shape[0]
-        logits = self.out_layer(hidden[-tgt_len:])
-        loss = F.cross_entropy(logits.float().view(-1, self.n_token), target.reshape(-1),
-                               reduction="none").view(tgt_len, -1)
+        pred = hidden[-tgt_len:]
+        if self.adaptive:
+            loss = self.crit(pred.reshape(-1, pred.shape[-1]), target.reshape(-1)).view(tgt_len, -1)
+        else:
+            logits = self.out_layer(pred)
+            loss = F.cross_entropy(logits.float().view(-1, self.n_token), target.reshape(-1),
+                                   reduction="none").view(tgt_len, -1)
         return [loss] + new_mems
 
     def balance_losses(self):
