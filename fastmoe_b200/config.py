@@ -93,7 +93,16 @@ def wait_timeout_ms():
 
 
 def debug_bounds():
+    r"""``FMOE_DEBUG_BOUNDS=1``: the fused paths validate the routing tables on the host
+    (expert ids in range, slot ranks consistent with the counts, offsets monotone and inside
+    the buffers) before launching; costs a device synchronisation per layer call."""
     return switch_from_env("FMOE_DEBUG_BOUNDS", False)
+
+
+def nvtx_enabled():
+    r"""``FMOE_NVTX=1``: NVTX ranges around the fused paths (forward, backward, exchange,
+    gradient all-reduce) for timeline tools."""
+    return switch_from_env("FMOE_NVTX", False)
 
 
 def use_nvls():

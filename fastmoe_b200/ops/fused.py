@@ -21,7 +21,9 @@ from torch.autograd import Function
 
 from . import grouped_gemm as gg
 from . import native
+from .. import config
 from ..transformer import activation_kind
+from ..utils.profiling import check_routing, fused_range
 
 _TC = (torch.bfloat16, torch.float16)
 
@@ -146,7 +148,13 @@ def moe_mlp_forward(layer, x, gate_idx, gate_score):
     k = gate_idx.shape[1]
     idx = gate_idx.contiguous().view(-1)
     score = gate_score.reshape(-1).to(x.dtype)
-    _counts, rank, offs = nat.route_offs(idx, layer.num_expert)
-    xs = _Dispatch.apply(x.contiguous(), idx, rank, offs, k)
-    ys = expert_mlp(layer, xs, offs)
-    return _Combine.apply(ys, score, idx, rank, offs, k)
+    with fused_range("route"):
+        counts, rank, offs = nat.route_offs(idx, layer.num_expert)
+    if config.debug_bounds():
+        check_routing(idx, rank, counts, layer.num_expert, offs, idx.numel())
+    with fused_range("dispatch"):
+        xs = _Dispatch.apply(x.contiguous(), idx, rank, offs, k)
+    with fused_range("experts"):
+        ys = expert_mlp(layer, xs, offs)
+    with fused_range("combine"):
+        return _Combine.apply(ys, score, idx, rank, offs, k)

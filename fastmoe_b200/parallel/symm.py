@@ -35,6 +35,7 @@ from torch.autograd import Function
 
 from .. import config
 from ..ops import native
+from ..utils.profiling import fused_range
 
 _WORKSPACES = {}
 _FAILED = set()
@@ -237,21 +238,25 @@ class _FusedEPMLP(Function):
         dst_base = torch.empty(tot, dtype=torch.int32, device=dev)
         expert_offs = torch.empty(n_expert + 1, dtype=torch.int32, device=dev)
         total = torch.empty(1, dtype=torch.int32, device=dev)
-        ws.ctx.count_exchange(lec, ws.cnt_ptrs, n_expert, capacity, dst_base, expert_offs, total)
-        stage_rows, rows_ptrs = ws.buffer("rows", capacity * d * x.element_size())
-        stage_meta, meta_ptrs = ws.buffer("meta", capacity * 8)
-        ws.ctx.dispatch_push(x, idx, rank, dst_base, None, rows_ptrs, meta_ptrs, n_expert, k, capacity)
-        xs = torch.empty(capacity, d, dtype=x.dtype, device=dev)
-        meta = torch.empty(capacity, dtype=torch.int64, device=dev)
-        ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, stage_meta.view(torch.int64), total, xs, meta)
+        with fused_range("ep.counts"):
+            ws.ctx.count_exchange(lec, ws.cnt_ptrs, n_expert, capacity, dst_base, expert_offs, total)
+        with fused_range("ep.dispatch"):
+            stage_rows, rows_ptrs = ws.buffer("rows", capacity * d * x.element_size())
+            stage_meta, meta_ptrs = ws.buffer("meta", capacity * 8)
+            ws.ctx.dispatch_push(x, idx, rank, dst_base, None, rows_ptrs, meta_ptrs, n_expert, k, capacity)
+            xs = torch.empty(capacity, d, dtype=x.dtype, device=dev)
+            meta = torch.empty(capacity, dtype=torch.int64, device=dev)
+            ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, stage_meta.view(torch.int64), total, xs, meta)
 
-        a, pre = gg.forward(xs, w1, expert_offs, b1, act=act, want_pre=True)
-        stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * x.element_size())
-        ws.ctx.gemm_push(gg.MODE_NT, a, w2, expert_offs, b2, meta, ret_ptrs)
-        n_tok = x.shape[0]
-        out = torch.empty(n_tok, d, dtype=x.dtype, device=dev)
-        y_slots = torch.empty(idx.numel(), d, dtype=x.dtype, device=dev)
-        ws.ctx.wait_combine(stage_ret, idx, score, k, out, y_slots)
+        with fused_range("ep.gemm1"):
+            a, pre = gg.forward(xs, w1, expert_offs, b1, act=act, want_pre=True)
+        with fused_range("ep.gemm2_push_combine"):
+            stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * x.element_size())
+            ws.ctx.gemm_push(gg.MODE_NT, a, w2, expert_offs, b2, meta, ret_ptrs)
+            n_tok = x.shape[0]
+            out = torch.empty(n_tok, d, dtype=x.dtype, device=dev)
+            y_slots = torch.empty(idx.numel(), d, dtype=x.dtype, device=dev)
+            ws.ctx.wait_combine(stage_ret, idx, score, k, out, y_slots)
 
         ctx.ws = ws
         ctx.args = n_expert, k, capacity, act, n_tok
@@ -318,6 +323,9 @@ def moe_mlp_forward(layer, x, gate_idx, gate_score):
     idx = gate_idx.contiguous().view(-1)
     score = gate_score.reshape(-1).to(x.dtype)
     lec, rank = nat.route(idx, n_expert * ws.world)
+    if config.debug_bounds():
+        from ..utils.profiling import check_routing
+        check_routing(idx, rank, lec, n_expert * ws.world)
     capacity = receive_capacity(x.shape[0], k, ws.world)
     act = activation_kind(layer.experts.activation)
     if act is not None:
@@ -368,6 +376,11 @@ def allreduce_grads(grads, comm, scale, fp32_accumulate=False):  # pylint: disab
     if ws is None:
         return False
     nbytes = n * grads[0].element_size()
+    with fused_range("allreduce"):
+        return _allreduce_grads(ws, grads, n, nbytes, dtype, scale)
+
+
+def _allreduce_grads(ws, grads, n, nbytes, dtype, scale):
     buf, ptrs = ws.buffer("allreduce", _ar_buffer_bytes(nbytes))
     flat = buf[:nbytes].view(dtype)
     views = []

@@ -28,6 +28,49 @@ def nvtx_range(name):
         yield
 
 
+@contextlib.contextmanager
+def fused_range(name):
+    r"""NVTX range used inside the framework's fused paths; active only with ``FMOE_NVTX=1``
+    so that the default path pays one environment lookup."""
+    from .. import config
+    if config.nvtx_enabled():
+        with nvtx_range("fmoe:" + name):
+            yield
+    else:
+        yield
+
+
+def check_routing(idx, rank, counts, tot_expert, offs=None, capacity=None):
+    r"""Host-side validation of a routing table (``FMOE_DEBUG_BOUNDS=1``); raises ``ValueError``.
+
+    ``idx``: expert id per slot (``-1`` = dropped); ``rank``: rank of the slot inside its
+    expert; ``counts[e]``: slots kept for expert ``e``; ``offs``: exclusive prefix of the
+    counts (optional); ``capacity``: rows of the buffer the offsets index (optional).
+    """
+    idx = idx.reshape(-1).long().cpu()
+    rank = rank.reshape(-1).long().cpu()
+    counts = counts.reshape(-1).long().cpu()
+    if idx.numel() and (int(idx.min()) < -1 or int(idx.max()) >= tot_expert):
+        raise ValueError("expert id out of range [-1, %d): min %d max %d" %
+                         (tot_expert, int(idx.min()), int(idx.max())))
+    kept = idx >= 0
+    want = torch.bincount(idx[kept], minlength=tot_expert)[:tot_expert]
+    if not torch.equal(want, counts[:tot_expert]):
+        raise ValueError("expert counts do not match the expert ids")
+    if kept.any():
+        if int(rank[kept].min()) < 0 or bool((rank[kept] >= counts[idx[kept]]).any()):
+            raise ValueError("slot rank outside [0, count of its expert)")
+        key = idx[kept] * (int(rank.max()) + 1) + rank[kept]
+        if key.unique().numel() != key.numel():
+            raise ValueError("two slots of one expert share a rank")
+    if offs is not None:
+        offs = offs.reshape(-1).long().cpu()
+        if bool((offs[1:] < offs[:-1]).any()) or int(offs[0]) != 0:
+            raise ValueError("expert offsets are not a monotone prefix starting at 0")
+        if capacity is not None and int(offs[-1]) > capacity:
+            raise ValueError("expert offsets exceed the buffer: %d > %d" % (int(offs[-1]), capacity))
+
+
 class EventTimer:
     r"""Accumulates CUDA-event durations of named regions on the current stream.
 
