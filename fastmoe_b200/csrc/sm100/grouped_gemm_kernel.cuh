@@ -503,7 +503,8 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, const EpiTi
 template <int MODE, typename T, int ACT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
-                    const __grid_constant__ CUtensorMap tm_b, const KernelParams p) {
+                    const __grid_constant__ CUtensorMap tm_b,
+                    const __grid_constant__ KernelParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
