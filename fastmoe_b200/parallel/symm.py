@@ -283,10 +283,9 @@ class _FusedEPMLP(Function):
         dys = torch.empty(capacity, d, dtype=dout.dtype, device=dout.device)
         ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, None, total, dys, None)
 
-        # By default the input-gradient chain goes first and its last GEMM pushes the rows home
-        # from its epilogue; both weight gradients are queued behind it, so the flight time of
-        # the last remote stores and the arrival handshake are covered by local tensor-core
-        # work before the combine waits for them.
+        # Order of the four GEMMs: weight gradients between the two input-gradient GEMMs by
+        # default; `FMOE_PUSH_BEFORE_WGRAD` runs the input-gradient chain (whose last GEMM
+        # pushes the rows home from its epilogue) first.
         push_first = config.push_before_wgrad()
         need_dx = ctx.needs_input_grad[0]
         dw2 = db2 = None
