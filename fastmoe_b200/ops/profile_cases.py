@@ -33,8 +33,8 @@ def gemm_case(repeats=2):
         gg.forward(hid, w2, offs, None)                          # GEMM 2: NT plain
         gg.dgrad(x, w2, offs, pre=hid, act="gelu")               # dgrad 2: NN + GELU derivative
         gg.dgrad(hid, w1, offs)                                  # dgrad 1: NN plain
-        gg.wgrad(hid, x, offs, n_exp)                            # wgrad 1
-        gg.wgrad(x, hid, offs, n_exp)                            # wgrad 2
+        gg.wgrad(hid, x, offs, n_exp, with_bias_grad=True)       # wgrad 1 (+ bias gradient)
+        gg.wgrad(x, hid, offs, n_exp, with_bias_grad=True)       # wgrad 2 (+ bias gradient)
     torch.cuda.synchronize()
     assert native.get().read_status(0) == 0
 
