@@ -31,6 +31,13 @@ namespace {
 // Number of kernels of this library launched by this process (benchmarks report it).
 std::atomic<int64_t> g_launches{0};
 
+}  // namespace
+
+// Called by the exchange bindings (other translation unit) for every kernel they launch.
+void fmoe_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+namespace {
+
 cudaStream_t cur_stream() {
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return at::cuda::getCurrentCUDAStream().stream();

@@ -8,6 +8,8 @@
 #include "grouped_gemm.cuh"
 #include "p2p.cuh"
 
+void fmoe_count_launch();  // binding.cpp: the library's launch counter
+
 namespace {
 
 #define FMOE_P2P_CHECK(expr)                                                        \
@@ -210,7 +212,11 @@ class ExchangeContext {
   }
 
  private:
-  cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+  // One call per kernel launch: also feeds the library's launch counter.
+  cudaStream_t stream() {
+    fmoe_count_launch();
+    return at::cuda::getCurrentCUDAStream().stream();
+  }
   fmoe::ExchangeCtx ctx_;
   torch::Tensor epoch_;
   torch::Tensor status_;
@@ -219,6 +225,7 @@ class ExchangeContext {
 void slot_dot(torch::Tensor dout, torch::Tensor y, torch::Tensor idx, int64_t k,
               torch::Tensor dscore) {
   c10::cuda::CUDAGuard guard(dout.device());
+  fmoe_count_launch();
   FMOE_P2P_CHECK(fmoe::launch_slot_dot(dtype16(dout), dout.data_ptr(), y.data_ptr(),
                                        idx.data_ptr<int64_t>(), static_cast<int>(idx.numel()),
                                        static_cast<int>(k), static_cast<int>(dout.size(1)),
