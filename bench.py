@@ -296,24 +296,26 @@ def main():
 
     # ------------------------------------------------ end-to-end region (H2D inputs, D2H loss)
     # One timed region around all K steps.  Inside it, every step: the pinned host batch is
-    # copied to the device (on a copy stream, one step ahead of its use: a plain input
+    # copied to the device (on a copy stream, up to three steps ahead of its use: a plain input
     # pipeline, the same for both arms), the step runs through the framework's public call,
-    # and the loss is read back to the host (asynchronously into pinned memory, the value is
-    # consumed one step later).  An L2 flush (160 MiB fill) also runs between the steps,
+    # and the loss is read back to the host (asynchronously into pinned memory; the host consumes
+    # the value three steps later, so that a scheduling hiccup of one of the N host processes
+    # does not stall the N GPUs that wait for each other on the device).  An L2 flush (160 MiB fill) also runs between the steps,
     # inside the region.
     main = torch.cuda.current_stream()
     copy_stream = torch.cuda.Stream()
-    stage = [torch.empty_like(dev_inputs[0]) for _ in range(2)]
-    ready = [torch.cuda.Event() for _ in range(2)]
-    consumed = [torch.cuda.Event() for _ in range(2)]
-    loss_pinned = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
-    loss_done = [torch.cuda.Event() for _ in range(2)]
+    depth = 4   # input copies run up to `depth - 1` steps ahead; a loss is consumed `depth - 1` steps late
+    stage = [torch.empty_like(dev_inputs[0]) for _ in range(depth)]
+    ready = [torch.cuda.Event() for _ in range(depth)]
+    consumed = [torch.cuda.Event() for _ in range(depth)]
+    loss_pinned = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(depth)]
+    loss_done = [torch.cuda.Event() for _ in range(depth)]
     small_flush = flush[:160 * 1024 * 1024 // 4]
 
     def issue_copy(i):
-        j = i % 2
+        j = i % depth
         with torch.cuda.stream(copy_stream):
-            if i >= 2:
+            if i >= depth:
                 copy_stream.wait_event(consumed[j])
             stage[j].copy_(host_inputs[i % n_inputs], non_blocking=True)
             ready[j].record(copy_stream)
@@ -324,21 +326,24 @@ def main():
     e_ev = torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     s_ev.record()
-    issue_copy(0)
+    for i in range(min(depth - 1, args.steps)):
+        issue_copy(i)
     for i in range(args.steps):
-        if i + 1 < args.steps:
-            issue_copy(i + 1)
+        if i + depth - 1 < args.steps:
+            issue_copy(i + depth - 1)
         small_flush.fill_(float(i))
-        main.wait_event(ready[i % 2])
-        loss = stepper(stage[i % 2]) if graphed else step(stage[i % 2])
-        consumed[i % 2].record(main)
-        loss_pinned[i % 2].copy_(loss.detach().float().reshape(1), non_blocking=True)
-        loss_done[i % 2].record(main)
-        if i >= 1:
-            loss_done[(i - 1) % 2].synchronize()
-            loss_host = float(loss_pinned[(i - 1) % 2])   # the previous step's result, on the host
-    loss_done[(args.steps - 1) % 2].synchronize()
-    loss_host = float(loss_pinned[(args.steps - 1) % 2])
+        main.wait_event(ready[i % depth])
+        loss = stepper(stage[i % depth]) if graphed else step(stage[i % depth])
+        consumed[i % depth].record(main)
+        loss_pinned[i % depth].copy_(loss.detach().float().reshape(1), non_blocking=True)
+        loss_done[i % depth].record(main)
+        if i >= depth - 1:
+            # the result of an earlier step, on the host (every step's loss is read exactly once)
+            loss_done[(i - depth + 1) % depth].synchronize()
+            loss_host = float(loss_pinned[(i - depth + 1) % depth])
+    for i in range(max(0, args.steps - depth + 1), args.steps):
+        loss_done[i % depth].synchronize()
+        loss_host = float(loss_pinned[i % depth])
     e_ev.record()
     torch.cuda.synchronize()
     wall = (time.perf_counter() - t0) * 1e3

@@ -85,6 +85,10 @@ class DistributedGroupedDataParallel(nn.Module):
             with torch.cuda.stream(side):
                 self.allreduce_gradients(no_scale, reduce_after, fp32_allreduce)
             return _ReduceHandle(side)
+        if async_op:
+            # no GPU: reduce now and hand back a handle whose wait() has nothing left to do
+            self.allreduce_gradients(no_scale, reduce_after, fp32_allreduce)
+            return _ReduceHandle(None)
         from .ops import allreduce as _ar
         for (dp_comm, dtype), group_params in _bucket_params(self.module.parameters(), True).items():
             if dp_comm not in self.comms:

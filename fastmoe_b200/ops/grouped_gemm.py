@@ -134,8 +134,11 @@ def bias_grad(dy, offs, dtype=None):
 
 
 def _zero_tail(out, offs):
-    # The SIMT kernel leaves rows past the last expert segment unwritten.
-    pass
+    r"""The SIMT kernel leaves rows past the last expert segment unwritten (the buffer comes from
+    ``torch.empty``): zero them, without a host read, so that an activation applied to the whole
+    buffer never meets NaN bit patterns."""
+    rows = torch.arange(out.shape[0], device=out.device)
+    out.masked_fill_((rows >= offs[-1])[:, None], 0)
 
 
 def _torch_act(x, act):

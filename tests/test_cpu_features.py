@@ -311,3 +311,28 @@ def test_debug_routing_check_and_nvtx_switch(monkeypatch):
         pass
     monkeypatch.setenv("FMOE_DEBUG_BOUNDS", "1")
     assert config.debug_bounds()
+
+
+def test_async_gradient_allreduce_handle_without_gpu():
+    r"""``allreduce_gradients(async_op=True)`` returns a handle on every device; without CUDA the
+    reduction has already happened when it returns."""
+    import torch.distributed as dist
+    from fastmoe_b200 import DistributedGroupedDataParallel
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29611")
+        dist.init_process_group("gloo", rank=0, world_size=1)
+        created = True
+    else:
+        created = False
+    try:
+        layer = FMoETransformerMLP(num_expert=2, d_model=8, d_hidden=16, world_size=1, top_k=2)
+        model = DistributedGroupedDataParallel(layer)
+        model(torch.randn(5, 8)).sum().backward()
+        before = layer.gate.gate.weight.grad.clone()
+        handle = model.allreduce_params(async_op=True)
+        handle.wait()
+        assert torch.allclose(layer.gate.gate.weight.grad, before)
+    finally:
+        if created:
+            dist.destroy_process_group()
