@@ -75,12 +75,12 @@ __device__ __forceinline__ void signal_all(const ExchangeCtx& c, int channel, in
 // Grid-wide "I am the last CTA" test on a counter in local memory (reset for the next use).
 __device__ __forceinline__ bool last_block(int* counter) {
   __shared__ int is_last;
-  // The CTA barrier orders every thread's stores before thread 0's system-scope fence, which
-  // is cumulative: one fence per block instead of one per thread (a system-scope fence is
-  // the expensive part of this test when a thousand blocks run it).
+  // Every thread orders its own stores at system scope before the barrier; thread 0 then
+  // counts the block.  (One fence by thread 0 behind the barrier would be enough by the
+  // memory model's cumulativity, and was not measurably faster.)
+  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
     const int prev = atomicAdd(counter, 1);
     is_last = (prev == static_cast<int>(gridDim.x) - 1);
     if (is_last) *counter = 0;
@@ -541,6 +541,13 @@ __global__ void allgather_kernel(const __grid_constant__ ExchangeCtx c, const ui
   for (long i = tid; i < total; i += stride) out[i] = __ldcg(mine + i);
 }
 
+// Waits until every peer has published the current epoch on `channel` (its rows have landed in
+// this rank's staging buffer); the kernels behind it in the stream may then read the buffer in
+// place.
+__global__ void wait_arrival_kernel(const __grid_constant__ ExchangeCtx c, int channel) {
+  block_wait_all(c, channel, c.epoch[0]);
+}
+
 __global__ void wait_only_kernel(const __grid_constant__ ExchangeCtx c, int channel) {
   // Waits for an epoch nobody will publish: exercises the time-out path.
   block_wait_all(c, channel, c.epoch[0] + 1000000);
@@ -711,6 +718,11 @@ cudaError_t launch_allgather(const ExchangeCtx& ctx, const void* src, const Peer
   if (blocks < 1) blocks = 1;
   allgather_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
       ctx, static_cast<const uint4*>(src), bufs, static_cast<uint4*>(out), nvec);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_arrival(const ExchangeCtx& ctx, int channel, cudaStream_t stream) {
+  wait_arrival_kernel<<<1, 32, 0, stream>>>(ctx, channel);
   return cudaGetLastError();
 }
 

@@ -105,6 +105,9 @@ cudaError_t launch_capacity_grant(const ExchangeCtx& ctx, const int* lec, const 
                                   const PeerPtrs& cnt, int n_expert, int64_t* new_lec,
                                   int64_t* new_gec, cudaStream_t stream);
 
+// Waits (bounded) for all peers' current-epoch flags on `channel` without touching any data.
+cudaError_t launch_wait_arrival(const ExchangeCtx& ctx, int channel, cudaStream_t stream);
+
 // Test hook: waits on `channel` for flags that nothing sets, with the given limit; the
 // kernel returns and leaves kStatusPeerTimeout in the status word.
 cudaError_t launch_wait_only(const ExchangeCtx& ctx, int channel, cudaStream_t stream);

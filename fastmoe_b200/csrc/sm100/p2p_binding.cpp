@@ -111,6 +111,11 @@ class ExchangeContext {
         with_meta ? out_meta->data_ptr<int64_t>() : nullptr, stream()));
   }
 
+  void wait_arrival(int64_t channel) {
+    c10::cuda::CUDAGuard guard(epoch_.device());
+    FMOE_P2P_CHECK(fmoe::launch_wait_arrival(ctx_, static_cast<int>(channel), stream()));
+  }
+
   void return_push(torch::Tensor rows, torch::Tensor meta, torch::Tensor total_rows,
                    std::vector<int64_t> ret_ptrs) {
     c10::cuda::CUDAGuard guard(rows.device());
@@ -245,6 +250,7 @@ void bind_p2p(pybind11::module& m) {
       .def("begin_epoch", &ExchangeContext::begin_epoch)
       .def("dispatch_push", &ExchangeContext::dispatch_push)
       .def("wait_copy", &ExchangeContext::wait_copy)
+      .def("wait_arrival", &ExchangeContext::wait_arrival)
       .def("return_push", &ExchangeContext::return_push)
       .def("wait_combine", &ExchangeContext::wait_combine)
       .def("allgather", &ExchangeContext::allgather)

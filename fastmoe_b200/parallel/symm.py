@@ -280,14 +280,22 @@ class _FusedEPMLP(Function):
         stage_rows, rows_ptrs = ws.buffer("rows", capacity * d * dout.element_size())
         ws.ctx.dispatch_push(dout, idx, rank, dst_base, score, rows_ptrs, [0] * ws.world,
                              n_expert, k, capacity)
-        dys = torch.empty(capacity, d, dtype=dout.dtype, device=dout.device)
-        ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, None, total, dys, None)
+        push_first = config.push_before_wgrad()
+        need_dx = ctx.needs_input_grad[0]
+        if push_first or not need_dx:
+            dys = torch.empty(capacity, d, dtype=dout.dtype, device=dout.device)
+            ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, None, total, dys, None)
+        else:
+            # The received gradient rows are only read by the next two GEMMs, and no peer can
+            # write this staging buffer again before it has combined what this rank pushes at
+            # the very end of this backward (that push exists because dx is wanted, and it comes
+            # last in the default order): use the rows in place, no copy.
+            ws.ctx.wait_arrival(nat.P2P_CHAN_DISPATCH)
+            dys = stage_rows[:capacity * d * dout.element_size()].view(dout.dtype).view(capacity, d)
 
         # Order of the four GEMMs: weight gradients between the two input-gradient GEMMs by
         # default; `FMOE_PUSH_BEFORE_WGRAD` runs the input-gradient chain (whose last GEMM
         # pushes the rows home from its epilogue) first.
-        push_first = config.push_before_wgrad()
-        need_dx = ctx.needs_input_grad[0]
         dw2 = db2 = None
         if not push_first:
             dw2, db2 = gg.wgrad(dys, a, expert_offs, n_expert, with_bias_grad=True)

@@ -14,6 +14,8 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 # NVLS is switched off for these runs: no kernel here uses multimem, and a rank that died
 # while bound to a multicast object could disturb the other GPUs.
 ENV = {"NCCL_NVLS_ENABLE": "0"}
+# Seconds a case may take before its ranks are killed (by pid).
+TIMEOUT = int(os.environ.get("FMOE_TEST_TIMEOUT", "300"))
 
 
 def _need(world):
@@ -25,7 +27,7 @@ def _need(world):
                                   "graph_step", "smart_schedule", "slice_group", "capacity"])
 def test_two_ranks(case):
     _need(2)
-    codes = run_ranks("dist_gpu_worker.py", case, 2, timeout=300, extra_env=ENV)
+    codes = run_ranks("dist_gpu_worker.py", case, 2, timeout=TIMEOUT, extra_env=ENV)
     assert codes == [0, 0], codes
 
 
@@ -33,7 +35,7 @@ def test_two_ranks(case):
 def test_many_ranks(case):
     world = int(os.environ.get("FMOE_TEST_WORLD", "4"))
     _need(world)
-    codes = run_ranks("dist_gpu_worker.py", case, world, timeout=300, extra_env=ENV)
+    codes = run_ranks("dist_gpu_worker.py", case, world, timeout=TIMEOUT, extra_env=ENV)
     assert codes == [0] * world, codes
 
 
