@@ -8,6 +8,7 @@ import os
 import socket
 import subprocess
 import sys
+import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -18,8 +19,9 @@ def free_port():
         return s.getsockname()[1]
 
 
-def run_ranks(script, case, world_size, timeout=300, extra_env=None):
-    r"""Returns the list of exit codes; children are killed (by pid) when `timeout` expires."""
+def run_ranks(script, case, world_size, timeout=300, extra_env=None, stop_on_failure=True):
+    r"""Returns the list of exit codes; children are killed (by pid) when `timeout` expires, and
+    — unless `stop_on_failure` is off — a few seconds after the first rank has failed."""
     port = free_port()
     procs = []
     for rank in range(world_size):
@@ -29,11 +31,29 @@ def run_ranks(script, case, world_size, timeout=300, extra_env=None):
         if extra_env:
             env.update(extra_env)
         procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, script), case], env=env))
-    codes = []
-    for p in procs:
-        try:
-            codes.append(p.wait(timeout=timeout))
-        except subprocess.TimeoutExpired:
-            p.kill()
-            codes.append(-9)
+    # Poll all ranks: when one fails, the others would wait for it in their next collective
+    # until `timeout`, so they are stopped (by pid) right away and reported as -9.
+    deadline = time.monotonic() + timeout
+    codes = [None] * world_size
+    while any(c is None for c in codes):
+        for i, p in enumerate(procs):
+            if codes[i] is None:
+                rc = p.poll()
+                if rc is not None:
+                    codes[i] = rc
+        failed = stop_on_failure and any(c not in (None, 0) for c in codes)
+        if failed or time.monotonic() > deadline:
+            grace = time.monotonic() + (3.0 if failed else 0.0)
+            while time.monotonic() < grace and any(p.poll() is None for p in procs):
+                time.sleep(0.1)
+            for i, p in enumerate(procs):
+                if codes[i] is None:
+                    rc = p.poll()
+                    if rc is None:
+                        p.kill()
+                        p.wait()
+                        rc = -9
+                    codes[i] = rc
+            break
+        time.sleep(0.05)
     return codes

@@ -16,7 +16,7 @@ def test_cpu_ranks(case, world):
 
 def test_rank_failure_is_detected():
     r"""Rank 1 exits before the collective; rank 0 must come back with an error, not hang."""
-    codes = run_ranks("dist_cpu_worker.py", "rank_failure", 2, timeout=120)
+    codes = run_ranks("dist_cpu_worker.py", "rank_failure", 2, timeout=120, stop_on_failure=False)
     assert codes[1] == 3
     assert codes[0] == 0, codes
 
