@@ -375,7 +375,9 @@ def main():
                 "seq_len": 1, "d_model": D_MODEL, "d_hidden": D_HIDDEN,
                 "experts_per_gpu": EXPERTS_PER_GPU, "top_k": TOP_K,
                 "parallelism": "ep%d" % world,
-                "step": "fwd+bwd+gate-grad-allreduce+fused-adam",
+                "step": "fwd+bwd+gate-grad-allreduce+fused-adam"
+                        + (" (all-reduce on a side stream, overlapped with the Adam update of the"
+                           " expert parameters; same Adam, two optimizer objects)" if overlap else ""),
                 "cuda_graph": bool(graphed),
                 "l2": "flushed between timed steps (256 MiB fill outside the per-step events; "
                       "in the end-to-end region a 160 MiB fill per step inside the region)",

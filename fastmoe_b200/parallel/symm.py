@@ -14,11 +14,16 @@ One layer call is, per rank and without any host read:
     route → count_exchange (counts to all peers; offsets from the full matrix)
           → dispatch_push (rows + (source, slot) words into the owners' staging buffers)
           → wait_copy     (arrival flags, rows into the tensor kept for backward)
-          → grouped GEMM 1 / activation / grouped GEMM 2 on the received rows
-          → return_push   (output rows back into the sources' slot-indexed staging buffer)
+          → grouped GEMM 1 (+ bias, activation) on the received rows
+          → grouped GEMM 2 whose epilogue stores every output row straight into its source
+            rank's slot-indexed staging buffer (`gemm_push`; `return_push` is the separate
+            kernel used when the second linear is not a plain grouped GEMM)
           → wait_combine  (arrival flags, gate-weighted sum over the k slots of a token)
 
-Backward runs the same two exchanges with gradient rows.  Staging buffers are shared by all
+Backward runs the same two exchanges with gradient rows; the received gradient rows are read
+in place (no copy out of staging) and the last input-gradient GEMM pushes from its epilogue.
+The module also holds the other peer-to-peer collectives: gradient all-reduce (one- and
+two-shot), all-gather of slice groups, capacity grants.  Staging buffers are shared by all
 layers: a rank can only start the next exchange after it has seen every peer's flags of the
 current one, and a peer only raises them after it is done reading, so no buffer is
 overwritten early.
@@ -364,10 +369,11 @@ def _two_shot(nbytes, world):
 
 
 def allreduce_grads(grads, comm, scale, fp32_accumulate=False):  # pylint: disable=unused-argument
-    r"""Sum ``grads`` over ``comm`` in place with the one-shot peer-to-peer kernel.
+    r"""Sum ``grads`` over ``comm`` in place with the peer-to-peer kernels (one-shot for small
+    buckets, two-shot from 512 KiB).
 
-    Every rank reads all peers' copies in rank order and accumulates in fp32, so the result is
-    bit-identical on all ranks and ``fp32_accumulate`` is implied.  Returns ``False`` (caller
+    Sums are formed in rank order with fp32 accumulation, so the result is bit-identical on
+    all ranks and ``fp32_accumulate`` is implied.  Returns ``False`` (caller
     falls back to the collective library) for unsupported dtypes, very large buckets or when
     no symmetric workspace exists for the group.
     """
@@ -408,7 +414,7 @@ def _allreduce_grads(ws, grads, n, nbytes, dtype, scale):
 
 
 def allreduce_flat(flat, comm, scale=1.0):
-    r"""Sum of a 1-D tensor over ``comm`` with the one-shot peer-to-peer kernel, or ``None`` when
+    r"""Sum of a 1-D tensor over ``comm`` with the peer-to-peer all-reduce kernels, or ``None`` when
     that path is not available (caller falls back to the collective library).
 
     Used for the shadow-expert traffic: a parameter *broadcast* is the sum of the owner's values
