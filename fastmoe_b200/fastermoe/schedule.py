@@ -174,9 +174,16 @@ def smart_schedule_forward(expert_fn, experts, inp, pos_s, pos_g, lec, gec, stor
         outputs[g] = _run_shadow_expert(experts, flat, rows)  # also with zero rows: keeps the graph uniform
 
     # ------------------------------------------------------------------ pipelined exchange
+    # Three passes over the steps.  (1) All dispatch exchanges are queued on the side stream
+    # at once, so the rows of step s + 1 travel while the experts work on step s.  (2) Per
+    # step: wait for that step's rows, run the experts, queue the return exchange on the side
+    # stream behind an event, and go on with the next step's experts while it travels.
+    # (3) Collect the returned rows.  Every rank issues the collectives in the same order:
+    # dispatch 0 .. n-1, return 0 .. n-1.
     gsz = _group_size(world_size)
     n_steps = world_size // gsz
     my_group = me // gsz
+    plans = []
     for step in range(n_steps):
         to_group = (my_group + step) % n_steps
         from_group = (my_group - step) % n_steps
@@ -192,18 +199,39 @@ def smart_schedule_forward(expert_fn, experts, inp, pos_s, pos_g, lec, gec, stor
                 if not stored[me * num_expert + e]:
                     recv_sizes[src] += gec_l[src * num_expert + e]
         send_buf = torch.cat(send_pieces) if send_pieces else local_input[:0]
+        plans.append((to_group, from_group, send_buf, send_sizes, recv_sizes))
 
+    def exchange(buf, out_sizes, in_sizes, after=None):
+        r"""One chunk all-to-all, on the side stream when there is one.  Returns the received
+        buffer and the event that marks its arrival (None on the caller's stream)."""
+        if comm is None:
+            return _ChunkAllToAll.apply(buf, anchor, out_sizes, in_sizes, group), None
+        if after is not None:
+            comm.wait_event(after)
+        with torch.cuda.stream(comm):
+            got = _ChunkAllToAll.apply(buf, anchor, out_sizes, in_sizes, group)
+            done = torch.cuda.Event()
+            done.record(comm)
+        buf.record_stream(comm)
+        got.record_stream(main)
+        return got, done
+
+    received = []
+    if world_size > 1:
+        if comm is not None:
+            comm.wait_stream(main)        # the send buffers were assembled on the caller's stream
+        for _to, _from, send_buf, send_sizes, recv_sizes in plans:
+            received.append(exchange(send_buf, send_sizes, recv_sizes))
+    else:
+        received = [(plan[2], None) for plan in plans]
+
+    returned = []
+    for step, (to_group, from_group, _send_buf, send_sizes, recv_sizes) in enumerate(plans):
+        recv_buf, arrived = received[step]
+        if arrived is not None:
+            main.wait_event(arrived)
         if world_size > 1:
-            if comm is not None:
-                comm.wait_stream(main)
-                with torch.cuda.stream(comm):
-                    recv_buf = _ChunkAllToAll.apply(send_buf, anchor, send_sizes, recv_sizes, group)
-                main.wait_stream(comm)
-            else:
-                recv_buf = _ChunkAllToAll.apply(send_buf, anchor, send_sizes, recv_sizes, group)
             ties.append(recv_buf[:0])
-        else:
-            recv_buf = send_buf
 
         # received layout: source rank outer, local expert inner
         pieces, cursor = {}, 0
@@ -237,24 +265,24 @@ def smart_schedule_forward(expert_fn, experts, inp, pos_s, pos_g, lec, gec, stor
         if back:
             back_buf = torch.cat(back)
         else:
-            back_buf = None
+            # nothing was computed here in this step, but peers may still expect the call
+            back_buf = local_input.new_zeros((0, _feature_width(experts, local_input)))
 
         if world_size > 1:
-            if back_buf is None:
-                # nothing was computed here in this step, but peers may still expect the call
-                width = _feature_width(experts, local_input)
-                back_buf = local_input.new_zeros((0, width))
+            computed = None
             if comm is not None:
-                comm.wait_stream(main)
-                with torch.cuda.stream(comm):
-                    ret_buf = _ChunkAllToAll.apply(back_buf, anchor, recv_sizes, send_sizes, group)
-                main.wait_stream(comm)
-            else:
-                ret_buf = _ChunkAllToAll.apply(back_buf, anchor, recv_sizes, send_sizes, group)
-            ties.append(ret_buf[:0])
+                computed = torch.cuda.Event()
+                computed.record(main)
+            returned.append(exchange(back_buf, recv_sizes, send_sizes, after=computed))
         else:
-            ret_buf = back_buf if back_buf is not None else local_input[:0]
+            returned.append((back_buf, None))
 
+    for step, (to_group, _from, _send_buf, _send_sizes, _recv_sizes) in enumerate(plans):
+        ret_buf, arrived = returned[step]
+        if arrived is not None:
+            main.wait_event(arrived)
+        if world_size > 1:
+            ties.append(ret_buf[:0])
         cursor = 0
         for p in range(to_group * gsz, (to_group + 1) * gsz):
             for e in range(num_expert):
