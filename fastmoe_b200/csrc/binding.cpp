@@ -480,5 +480,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cpu_linear_forward", &fmoe::cpu::linear_forward);
   m.def("cpu_linear_backward", &fmoe::cpu::linear_backward);
   m.def("cpu_swipe_plan", &fmoe::cpu::swipe_plan);
+  m.def("cpu_smart_schedule_plan", &fmoe::cpu::smart_schedule_plan);
   bind_p2p(m);
 }

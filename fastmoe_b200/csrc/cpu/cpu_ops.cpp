@@ -129,5 +129,71 @@ std::vector<torch::Tensor> swipe_plan(torch::Tensor want, torch::Tensor cap) {
   return {accepted, left};
 }
 
+// Chunk plan of the group-wise pipelined exchange (the host-side bookkeeping the reference
+// does in `computePtrs` / the step loops of cuda/fastermoe/smart_schedule.h:48-80,105-261).
+// Ranks form groups of `group_size`; in step s rank `me` sends to group (mine + s) and receives
+// from group (mine - s).  Shadowed experts (`stored`) take no part in the exchange.
+//   send_sizes, recv_sizes : [steps, world]  rows to / from every rank in that step
+//   send_experts, send_offsets : global expert ids whose row segments make up the send buffer
+//                                of step s, in order: send_experts[send_offsets[s] : send_offsets[s+1]]
+//   recv_cursor, recv_count : [steps, group_size, num_expert]  where the rows of (source rank of
+//                             the step's group, local expert) start in the received buffer and
+//                             how many there are (cursor -1 for shadowed experts)
+std::vector<torch::Tensor> smart_schedule_plan(torch::Tensor lec, torch::Tensor gec,
+                                               torch::Tensor stored, int64_t num_expert,
+                                               int64_t world_size, int64_t me, int64_t group_size) {
+  auto l = lec.to(torch::kLong).contiguous().cpu();
+  auto g = gec.to(torch::kLong).contiguous().cpu();
+  auto st = stored.to(torch::kBool).contiguous().cpu();
+  const int64_t tot = num_expert * world_size;
+  TORCH_CHECK(l.numel() == tot && g.numel() == tot && st.numel() == tot, "plan: count shapes");
+  TORCH_CHECK(group_size >= 1 && world_size % group_size == 0, "plan: group size");
+  const int64_t steps = world_size / group_size;
+  const int64_t my_group = me / group_size;
+  const int64_t* lp = l.data_ptr<int64_t>();
+  const int64_t* gp = g.data_ptr<int64_t>();
+  const bool* sp = st.data_ptr<bool>();
+  auto send_sizes = torch::zeros({steps, world_size}, torch::kLong);
+  auto recv_sizes = torch::zeros({steps, world_size}, torch::kLong);
+  auto recv_cursor = torch::full({steps, group_size, num_expert}, -1, torch::kLong);
+  auto recv_count = torch::zeros({steps, group_size, num_expert}, torch::kLong);
+  auto send_offsets = torch::zeros({steps + 1}, torch::kLong);
+  std::vector<int64_t> experts;
+  int64_t* ss = send_sizes.data_ptr<int64_t>();
+  int64_t* rs = recv_sizes.data_ptr<int64_t>();
+  int64_t* rc = recv_cursor.data_ptr<int64_t>();
+  int64_t* rn = recv_count.data_ptr<int64_t>();
+  int64_t* so = send_offsets.data_ptr<int64_t>();
+  for (int64_t s = 0; s < steps; ++s) {
+    const int64_t to_group = (my_group + s) % steps;
+    const int64_t from_group = ((my_group - s) % steps + steps) % steps;
+    for (int64_t p = to_group * group_size; p < (to_group + 1) * group_size; ++p) {
+      for (int64_t e = 0; e < num_expert; ++e) {
+        const int64_t id = p * num_expert + e;
+        if (!sp[id] && lp[id] > 0) {
+          experts.push_back(id);
+          ss[s * world_size + p] += lp[id];
+        }
+      }
+    }
+    so[s + 1] = static_cast<int64_t>(experts.size());
+    int64_t cursor = 0;
+    for (int64_t i = 0; i < group_size; ++i) {
+      const int64_t src = from_group * group_size + i;
+      for (int64_t e = 0; e < num_expert; ++e) {
+        if (sp[me * num_expert + e]) continue;
+        const int64_t n = gp[src * num_expert + e];
+        rs[s * world_size + src] += n;
+        rc[(s * group_size + i) * num_expert + e] = cursor;
+        rn[(s * group_size + i) * num_expert + e] = n;
+        cursor += n;
+      }
+    }
+  }
+  auto send_experts = torch::empty({static_cast<int64_t>(experts.size())}, torch::kLong);
+  std::copy(experts.begin(), experts.end(), send_experts.data_ptr<int64_t>());
+  return {send_sizes, recv_sizes, send_experts, send_offsets, recv_cursor, recv_count};
+}
+
 }  // namespace cpu
 }  // namespace fmoe

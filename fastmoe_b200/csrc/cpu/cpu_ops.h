@@ -30,5 +30,10 @@ std::vector<torch::Tensor> linear_backward(torch::Tensor grad_out, torch::Tensor
 // Returns (accepted [n, n] int64, cap_left [n] int64).
 std::vector<torch::Tensor> swipe_plan(torch::Tensor want, torch::Tensor cap);
 
+// Per-step split sizes and buffer layouts of the FasterMoE group-wise exchange (see the .cpp).
+std::vector<torch::Tensor> smart_schedule_plan(torch::Tensor lec, torch::Tensor gec,
+                                               torch::Tensor stored, int64_t num_expert,
+                                               int64_t world_size, int64_t me, int64_t group_size);
+
 }  // namespace cpu
 }  // namespace fmoe

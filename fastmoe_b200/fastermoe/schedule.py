@@ -134,6 +134,66 @@ def _group_size(world_size):
     return max(g, 1)
 
 
+def _plan_steps_python(lec_l, gec_l, stored, num_expert, world_size, me, gsz):
+    r"""PyTorch-free restatement of the native chunk planner (same return layout, as lists)."""
+    n_steps = world_size // gsz
+    my_group = me // gsz
+    send_sizes, recv_sizes, send_experts, recv_layout = [], [], [], []
+    for step in range(n_steps):
+        to_group = (my_group + step) % n_steps
+        from_group = (my_group - step) % n_steps
+        ss, rs, ids = [0] * world_size, [0] * world_size, []
+        for p in range(to_group * gsz, (to_group + 1) * gsz):
+            for e in range(num_expert):
+                g = p * num_expert + e
+                if not stored[g] and lec_l[g] > 0:
+                    ids.append(g)
+                    ss[p] += lec_l[g]
+        layout, cursor = {}, 0
+        for src in range(from_group * gsz, (from_group + 1) * gsz):
+            for e in range(num_expert):
+                if stored[me * num_expert + e]:
+                    continue
+                n = gec_l[src * num_expert + e]
+                rs[src] += n
+                layout[(src, e)] = (cursor, n)
+                cursor += n
+        send_sizes.append(ss)
+        recv_sizes.append(rs)
+        send_experts.append(ids)
+        recv_layout.append(layout)
+    return send_sizes, recv_sizes, send_experts, recv_layout
+
+
+def plan_steps(lec, gec, stored_models, num_expert, world_size, me, gsz):
+    r"""Per step of the group-wise exchange: split sizes, the expert segments that make up the
+    send buffer, and where each (source rank, local expert) block sits in the received buffer.
+
+    Computed by the native planner (``csrc/cpu/cpu_ops.cpp::smart_schedule_plan``, the
+    counterpart of the pointer bookkeeping in ``cuda/fastermoe/smart_schedule.h:48-80``) when
+    the extension is loaded, by :func:`_plan_steps_python` otherwise.
+    """
+    from ..ops import native
+    if native.available():
+        ss, rs, ids, offs, cur, cnt = native.get().cpu_smart_schedule_plan(
+            lec.reshape(-1).cpu(), gec.reshape(-1).cpu(), stored_models.reshape(-1).cpu(),
+            num_expert, world_size, me, gsz)
+        n_steps = world_size // gsz
+        my_group = me // gsz
+        ids, offs = ids.tolist(), offs.tolist()
+        cur, cnt = cur.tolist(), cnt.tolist()
+        layouts = []
+        for step in range(n_steps):
+            from_group = (my_group - step) % n_steps
+            layouts.append({(from_group * gsz + i, e): (cur[step][i][e], cnt[step][i][e])
+                            for i in range(gsz) for e in range(num_expert) if cur[step][i][e] >= 0})
+        return (ss.tolist(), rs.tolist(), [ids[offs[s]:offs[s + 1]] for s in range(n_steps)], layouts)
+    stored = [bool(v) for v in stored_models.reshape(-1).tolist()]
+    return _plan_steps_python([int(v) for v in lec.reshape(-1).tolist()],
+                              [int(v) for v in gec.reshape(-1).tolist()], stored, num_expert,
+                              world_size, me, gsz)
+
+
 def smart_schedule_forward(expert_fn, experts, inp, pos_s, pos_g, lec, gec, stored_models,
                            fwd_batch_size, out_batch_size, num_expert, world_size):
     r"""Body of :class:`MoEForward`; all arguments as in the reference's ``MoEForward.forward``."""
@@ -183,23 +243,15 @@ def smart_schedule_forward(expert_fn, experts, inp, pos_s, pos_g, lec, gec, stor
     gsz = _group_size(world_size)
     n_steps = world_size // gsz
     my_group = me // gsz
+    all_send, all_recv, all_ids, all_layouts = plan_steps(lec, gec, stored_models, num_expert,
+                                                         world_size, me, gsz)
     plans = []
     for step in range(n_steps):
         to_group = (my_group + step) % n_steps
         from_group = (my_group - step) % n_steps
-        send_pieces, send_sizes, recv_sizes = [], [0] * world_size, [0] * world_size
-        for p in range(to_group * gsz, (to_group + 1) * gsz):
-            for e in range(num_expert):
-                g = p * num_expert + e
-                if not stored[g] and lec_l[g] > 0:
-                    send_pieces.append(local_input[seg_start[g]:seg_start[g + 1]])
-                    send_sizes[p] += lec_l[g]
-        for src in range(from_group * gsz, (from_group + 1) * gsz):
-            for e in range(num_expert):
-                if not stored[me * num_expert + e]:
-                    recv_sizes[src] += gec_l[src * num_expert + e]
+        send_pieces = [local_input[seg_start[g]:seg_start[g + 1]] for g in all_ids[step]]
         send_buf = torch.cat(send_pieces) if send_pieces else local_input[:0]
-        plans.append((to_group, from_group, send_buf, send_sizes, recv_sizes))
+        plans.append((to_group, from_group, send_buf, all_send[step], all_recv[step]))
 
     def exchange(buf, out_sizes, in_sizes, after=None):
         r"""One chunk all-to-all, on the side stream when there is one.  Returns the received
@@ -234,14 +286,7 @@ def smart_schedule_forward(expert_fn, experts, inp, pos_s, pos_g, lec, gec, stor
             ties.append(recv_buf[:0])
 
         # received layout: source rank outer, local expert inner
-        pieces, cursor = {}, 0
-        for src in range(from_group * gsz, (from_group + 1) * gsz):
-            for e in range(num_expert):
-                if stored[me * num_expert + e]:
-                    continue
-                n = gec_l[src * num_expert + e]
-                pieces[(src, e)] = (cursor, n)
-                cursor += n
+        pieces = all_layouts[step]
         result = {}
         for e in range(num_expert):
             if stored[me * num_expert + e]:

@@ -336,3 +336,23 @@ def test_async_gradient_allreduce_handle_without_gpu():
     finally:
         if created:
             dist.destroy_process_group()
+
+
+def test_native_smart_schedule_planner_matches_python():
+    r"""The C++ chunk planner of the group-wise exchange and its Python restatement agree."""
+    from fastmoe_b200.fastermoe import schedule
+    from fastmoe_b200.ops import native
+    if not native.available():
+        pytest.skip("native extension not built")
+    gen = torch.Generator().manual_seed(5)
+    for world, n_exp, gsz in ((4, 2, 2), (8, 3, 4), (4, 1, 1), (2, 2, 2), (6, 2, 3)):
+        for me in range(world):
+            tot = world * n_exp
+            lec = torch.randint(0, 7, (tot,), generator=gen)
+            gec = torch.randint(0, 7, (tot,), generator=gen)
+            stored = torch.rand(tot, generator=gen) < 0.3
+            got = schedule.plan_steps(lec, gec, stored, n_exp, world, me, gsz)
+            want = schedule._plan_steps_python(lec.tolist(), gec.tolist(), stored.tolist(), n_exp,
+                                               world, me, gsz)
+            assert got[0] == want[0] and got[1] == want[1] and got[2] == want[2]
+            assert got[3] == want[3], (world, n_exp, gsz, me)
