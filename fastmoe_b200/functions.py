@@ -17,7 +17,6 @@ import torch.distributed as dist
 from torch.autograd import Function
 
 from .ops import api as _ops
-from .parallel import comm as _comm
 from .parallel.comm import ensure_comm, get_moe_group  # noqa: F401  (re-exported)
 
 

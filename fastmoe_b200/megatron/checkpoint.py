@@ -14,7 +14,6 @@ shard on rank 0's file (``merge_state_dict``).  Interleaved pipeline stages are 
 """
 import os
 import random
-import sys
 from collections import OrderedDict
 
 import numpy as np

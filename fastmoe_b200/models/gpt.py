@@ -8,7 +8,6 @@ Megatron's ``ParallelMLP``, and the model offers ``state_dict_for_save_checkpoin
 ``set_input_tensor``.  Attention uses ``scaled_dot_product_attention``; it is outside the MoE
 paths this project rewrites.
 """
-import math
 from dataclasses import dataclass
 
 import torch

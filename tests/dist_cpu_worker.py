@@ -177,7 +177,6 @@ def case_shadow_policy():
 def case_megatron_checkpoint():
     r"""Megatron adapter under expert parallelism: fmoefy, grouped DDP with a gate group, and
     sharded save / load (rank 0 full file, other ranks expert shards) giving identical models."""
-    import tempfile
     import types
     from fastmoe_b200.megatron import stub
     from fastmoe_b200.models import GPTConfig, GPTModel
