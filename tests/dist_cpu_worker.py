@@ -123,6 +123,17 @@ def case_slice_group():
     assert torch.allclose(y, ref, atol=1e-5)
     y.sum().backward()
     assert x.grad.shape == x.shape
+    # Remainder rows (batch not divisible by the group size) are not routed, as in the
+    # reference: Slice keeps B // W rows per rank and its backward leaves the tail at zero.
+    from fastmoe_b200.functions import AllGather, Slice
+    full = torch.arange((4 * world + 1) * 3, dtype=torch.float32).view(4 * world + 1, 3).requires_grad_(True)
+    part = Slice.apply(full, rank, world, dist.group.WORLD)
+    assert part.shape[0] == 4 and torch.equal(part, full.detach()[4 * rank:4 * rank + 4])
+    gathered = AllGather.apply(part * 2.0, rank, world, dist.group.WORLD)
+    assert torch.equal(gathered, 2.0 * full.detach()[:4 * world])
+    gathered.sum().backward()
+    assert torch.equal(full.grad[:4 * world], torch.full((4 * world, 3), 2.0))
+    assert float(full.grad[4 * world:].abs().sum()) == 0.0
 
 
 def case_smart_schedule():

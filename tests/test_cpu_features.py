@@ -356,3 +356,31 @@ def test_native_smart_schedule_planner_matches_python():
                                                world, me, gsz)
             assert got[0] == want[0] and got[1] == want[1] and got[2] == want[2]
             assert got[3] == want[3], (world, n_exp, gsz, me)
+
+
+def test_scatter_gather_rows_and_gradients():
+    r"""``MOEScatter`` puts row ``pos // k`` of the input at every kept slot (dropped slots, id -1,
+    are skipped), ``MOEGather`` is its transpose, and both pass a numerical gradient check."""
+    from fastmoe_b200.functions import MOEGather, MOEScatter, prepare_forward
+    torch.manual_seed(12)
+    k, n_tok, n_exp, d = 2, 6, 3, 4
+    gate = torch.randint(0, n_exp, (n_tok, k))
+    gate[1, 0] = -1
+    gate[4, 1] = -1
+    pos, lec, gec, _cnt, fwd = prepare_forward(gate, n_exp, 1)
+    assert fwd == n_tok * k - 2 and pos.numel() == fwd
+    x = torch.randn(n_tok, d, dtype=torch.float64, requires_grad=True)
+    token_of_slot = torch.div(pos, k, rounding_mode="floor")
+    rows = MOEScatter.apply(x, token_of_slot, lec, gec, fwd, 1)
+    assert torch.equal(rows, x.detach()[token_of_slot])
+    # rows arrive grouped by ascending expert id
+    experts_of_rows = gate.reshape(-1)[pos]
+    assert torch.equal(experts_of_rows, experts_of_rows.sort().values)
+    assert torch.autograd.gradcheck(
+        lambda t: MOEScatter.apply(t, token_of_slot, lec, gec, fwd, 1), (x,))
+    y = torch.randn(fwd, d, dtype=torch.float64, requires_grad=True)
+    back = MOEGather.apply(y, pos, lec, gec, n_tok * k, 1)
+    assert back.shape == (n_tok * k, d)
+    assert torch.equal(back[pos], y.detach()) and float(back[1 * k + 0].abs().sum()) == 0.0
+    assert torch.autograd.gradcheck(
+        lambda t: MOEGather.apply(t, pos, lec, gec, n_tok * k, 1), (y,))
