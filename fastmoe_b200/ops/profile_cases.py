@@ -4,6 +4,7 @@ Small, self-terminating workloads for profiling single kernels under ``ncu``.
     python -m fastmoe_b200.ops.profile_cases gemm      # the six grouped-GEMM variants of one MoE layer
     python -m fastmoe_b200.ops.profile_cases rows      # routing / scatter / combine kernels
     python -m fastmoe_b200.ops.profile_cases push      # exchange kernels on one GPU (one-rank group)
+    python -m fastmoe_b200.ops.profile_cases push_gemm # GEMM 2 with the return push in its epilogue (one-rank group)
     python -m fastmoe_b200.ops.profile_cases gate      # single-pass linear gate, forward and backward
 
 Each case touches more than the 126 MB L2 in total but holds well under 1 GB on the device and
@@ -104,6 +105,59 @@ def push_case(repeats=3):
     dist.destroy_process_group()
 
 
+def push_gemm_case(repeats=3):
+    r"""The fused combine on one GPU: the second expert GEMM whose epilogue stores every output
+    row into the slot-indexed return buffer (here this rank's own symmetric buffer, reached
+    through the same peer table, completion counter and flags as on several GPUs), followed by
+    the gate-weighted combine.  Checked against the plain GEMM + local combine."""
+    import os
+    import torch.distributed as dist
+    from ..parallel import symm
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29578")
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    nat = native.get()
+    ws = symm.get_workspace(dist.group.WORLD, dev)
+    assert ws is not None, "symmetric memory is not available"
+    n_tok, k, d, h, n_exp = 4096, 2, 1024, 4096, 2
+    x = torch.randn(n_tok, d, device=dev, dtype=torch.bfloat16)
+    idx = torch.randint(0, n_exp, (n_tok * k,), device=dev)
+    score = torch.rand(n_tok * k, device=dev).to(torch.bfloat16)
+    w2 = (torch.randn(n_exp, d, h, device=dev) * 0.02).to(torch.bfloat16)
+    b2 = (torch.randn(n_exp, d, device=dev) * 0.1).to(torch.bfloat16)
+    capacity = symm.receive_capacity(n_tok, k, 1)
+    act = torch.randn(capacity, h, device=dev, dtype=torch.bfloat16)
+    rows_buf, rows_ptrs = ws.buffer("rows", capacity * d * 2)
+    meta_buf, meta_ptrs = ws.buffer("meta", capacity * 8)
+    ret_buf, ret_ptrs = ws.buffer("ret", n_tok * k * d * 2)
+    lec, rnk = nat.route(idx, n_exp)
+    dst_base = torch.empty(n_exp, dtype=torch.int32, device=dev)
+    offs = torch.empty(n_exp + 1, dtype=torch.int32, device=dev)
+    total = torch.empty(1, dtype=torch.int32, device=dev)
+    xs = torch.empty(capacity, d, device=dev, dtype=torch.bfloat16)
+    meta = torch.empty(capacity, dtype=torch.int64, device=dev)
+    out = torch.empty(n_tok, d, device=dev, dtype=torch.bfloat16)
+    keep = torch.empty(n_tok * k, d, device=dev, dtype=torch.bfloat16)
+    for _ in range(repeats):
+        ws.ctx.count_exchange(lec, ws.cnt_ptrs, n_exp, capacity, dst_base, offs, total)
+        ws.ctx.begin_epoch()
+        ws.ctx.dispatch_push(x, idx, rnk, dst_base, None, rows_ptrs, meta_ptrs, n_exp, k, capacity)
+        ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, rows_buf, meta_buf.view(torch.int64), total, xs, meta)
+        ws.ctx.gemm_push(gg.MODE_NT, act, w2, offs, b2, meta, ret_ptrs)
+        ws.ctx.wait_combine(ret_buf, idx, score, k, out, keep)
+    torch.cuda.synchronize()
+    assert nat.read_status(0) == 0
+    ys = gg.forward(act, w2, offs, b2)
+    want = torch.empty_like(out)
+    nat.gather_combine(ys, idx, rnk, offs[:n_exp].contiguous(), score, k, want)
+    assert torch.allclose(out.float(), want.float(), atol=0.05, rtol=0.05)
+    dist.destroy_process_group()
+
+
 def gate_case(repeats=3):
     from . import gating
     dev = "cuda"
@@ -119,6 +173,6 @@ def gate_case(repeats=3):
 
 
 if __name__ == "__main__":
-    {"gemm": gemm_case, "rows": rows_case, "push": push_case,
+    {"gemm": gemm_case, "rows": rows_case, "push": push_case, "push_gemm": push_gemm_case,
      "gate": gate_case}[sys.argv[1] if len(sys.argv) > 1 else "gemm"]()
     print("done")
