@@ -1,0 +1,96 @@
+r"""The C++ CPU ops of the extension against their PyTorch restatements (`ops/torch_impl.py`),
+on randomly generated routing tables: both are oracles for the CUDA kernels, so they have to
+agree with each other first.  Skipped when the extension has not been built."""
+import pytest
+import torch
+from hypothesis import given, settings, strategies as st
+
+from fastmoe_b200.ops import native, torch_impl
+
+pytestmark = pytest.mark.skipif(not native.available(), reason="native extension not built")
+
+
+def _routing(draw, tot):
+    n = draw(st.integers(min_value=0, max_value=60))
+    ids = draw(st.lists(st.integers(min_value=-1, max_value=tot - 1), min_size=n, max_size=n))
+    return torch.tensor(ids, dtype=torch.int64)
+
+
+@st.composite
+def routing_case(draw):
+    n_expert = draw(st.integers(min_value=1, max_value=5))
+    n_worker = draw(st.integers(min_value=1, max_value=4))
+    return n_expert, n_worker, _routing(draw, n_expert * n_worker)
+
+
+@settings(max_examples=60, deadline=None)
+@given(routing_case())
+def test_route_matches_restatement(case):
+    n_expert, n_worker, idx = case
+    tot = n_expert * n_worker
+    counts, rank = native.get().cpu_route(idx, tot)
+    assert torch.equal(counts.long(), torch_impl.expert_count(idx, tot).long())
+    assert torch.equal(rank.long(), torch_impl.slot_rank(idx, tot).reshape(-1).long())
+    # the positions implied by (count prefix, rank) are a permutation of the kept slots
+    pos = torch_impl.assign_pos(idx, tot)
+    assert sorted(pos.tolist()) == [s for s, e in enumerate(idx.tolist()) if e >= 0]
+    assert idx[pos].tolist() == sorted(e for e in idx.tolist() if e >= 0)
+
+
+@settings(max_examples=60, deadline=None)
+@given(routing_case(), st.integers(min_value=0, max_value=12))
+def test_capacity_limit_and_prune_match_restatement(case, capacity):
+    n_expert, n_worker, idx = case
+    tot = n_expert * n_worker
+    gen = torch.Generator().manual_seed(int(idx.sum()) % 1000 + capacity)
+    proposals = torch.randint(0, 9, (tot,), generator=gen)
+    cap_a = torch.full((n_expert,), capacity, dtype=torch.int32)
+    cap_b = cap_a.clone()
+    got = native.get().cpu_limit_by_capacity(proposals.clone(), cap_a, n_expert, n_worker)
+    want = torch_impl.limit_by_capacity(proposals.clone(), cap_b, n_expert, n_worker)
+    assert torch.equal(got, want) and torch.equal(cap_a, cap_b)
+    # grants never exceed the capacity of an expert and are handed out in worker order
+    per_expert = got.view(n_worker, n_expert)
+    assert bool((per_expert.sum(0) <= capacity).all())
+    budget = torch.randint(0, 6, (tot,), generator=gen).to(torch.int32)
+    budget_a, budget_b = budget.clone(), budget.clone()
+    pruned = native.get().cpu_prune_gate_by_capacity(idx.clone(), budget_a, n_expert, n_worker)
+    ref = torch_impl.prune_gate_by_capacity(idx.clone(), budget_b, n_expert, n_worker)
+    assert torch.equal(pruned, ref)
+    # an expert keeps at most what it was asked for and at most its budget
+    kept = torch_impl.expert_count(pruned, tot).long()
+    assert bool((kept <= torch_impl.expert_count(idx, tot).long()).all())
+    assert bool((kept <= budget.long()).all())
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(min_value=1, max_value=5), st.integers(min_value=0, max_value=10_000))
+def test_swipe_plan_matches_restatement_and_conserves_tokens(n_worker, seed):
+    gen = torch.Generator().manual_seed(seed)
+    want = torch.randint(0, 20, (n_worker, n_worker), generator=gen)
+    cap = torch.randint(0, 40, (n_worker,), generator=gen)
+    accepted, left = native.get().cpu_swipe_plan(want, cap)
+    ref_accepted, ref_left = torch_impl.swipe_plan(want.tolist(), cap.tolist(), n_worker)
+    assert accepted.tolist() == ref_accepted and left.tolist() == ref_left
+    # nobody receives more than its capacity; tokens are only lost when all capacity is used up
+    assert bool((accepted.sum(0) <= cap).all())
+    lost = int(want.sum()) - int(accepted.sum())
+    assert lost >= 0 and (lost == 0 or int(left.sum()) == 0)
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.integers(min_value=1, max_value=4), st.integers(min_value=0, max_value=1000))
+def test_grouped_linear_matches_restatement(n_expert, seed):
+    gen = torch.Generator().manual_seed(seed)
+    counts = torch.randint(0, 6, (n_expert,), generator=gen)
+    rows, d_in, d_out = int(counts.sum()), 5, 3
+    x = torch.randn(rows, d_in, generator=gen, dtype=torch.float64)
+    w = torch.randn(n_expert, d_out, d_in, generator=gen, dtype=torch.float64)
+    b = torch.randn(n_expert, d_out, generator=gen, dtype=torch.float64)
+    nat = native.get()
+    y = nat.cpu_linear_forward(x, counts, w, b)
+    assert torch.allclose(y, torch_impl.linear_forward(x, counts, w, b))
+    gy = torch.randn(rows, d_out, generator=gen, dtype=torch.float64)
+    gx, gw, gb = nat.cpu_linear_backward(gy, x, counts, w, b)
+    rx, rw, rb = torch_impl.linear_backward(gy, x, counts, w, b)
+    assert torch.allclose(gx, rx) and torch.allclose(gw, rw) and torch.allclose(gb, rb)
