@@ -186,3 +186,51 @@ def swipe_reassign(gate_idx, accepted_row, n_expert, bias):
             new_ids = targets * n_expert + bias
         idx[moved] = new_ids
     return idx.view_as(gate_idx)
+
+
+# ----------------------------------------------------------------------------------
+# Expert-parallel exchange bookkeeping (restatement of the device-side arithmetic)
+# ----------------------------------------------------------------------------------
+def exchange_offsets(count_matrix, me, n_expert, capacity_rows=None):
+    r"""What ``count_exchange_kernel`` derives on rank ``me`` from the full count matrix.
+
+    ``count_matrix[w, g]``: slots rank ``w`` routes to global expert ``g`` (``g = owner * E + e``).
+    Receive layout on every rank: local expert outer, source rank inner.  Returns
+
+    * ``dst_base[g]``: row in the owner's receive buffer where this rank's rows for ``g`` start,
+    * ``expert_offs[e]`` (``E + 1`` entries): row ranges of this rank's local experts,
+    * ``total``: rows this rank receives (clamped to ``capacity_rows`` when given),
+    * ``overflow``: whether any rank receives more than ``capacity_rows``.
+    """
+    mat = torch.as_tensor(count_matrix, dtype=torch.int64)
+    world, tot = mat.shape
+    assert tot == world * n_expert
+    col = mat.sum(0)
+    dst_base = torch.zeros(tot, dtype=torch.int64)
+    for g in range(tot):
+        owner, e = divmod(g, n_expert)
+        dst_base[g] = col[owner * n_expert:owner * n_expert + e].sum() + mat[:me, g].sum()
+    mine = col[me * n_expert:(me + 1) * n_expert]
+    expert_offs = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(mine, 0)])
+    per_rank = col.view(world, n_expert).sum(1)
+    overflow = capacity_rows is not None and bool((per_rank > capacity_rows).any())
+    if capacity_rows is not None:
+        expert_offs = expert_offs.clamp(max=capacity_rows)
+    return dst_base, expert_offs, int(expert_offs[-1]), overflow
+
+
+def capacity_grants(count_matrix, capacities, n_expert):
+    r"""What ``capacity_grant_kernel`` derives on every rank: ``grant[w, g]``, handed out in rank
+    order from the capacity of ``g``'s owner (``capacities[owner, e]``)."""
+    mat = torch.as_tensor(count_matrix, dtype=torch.int64)
+    caps = torch.as_tensor(capacities, dtype=torch.int64)
+    world, tot = mat.shape
+    grant = torch.zeros_like(mat)
+    for g in range(tot):
+        owner, e = divmod(g, n_expert)
+        left = int(caps[owner, e])
+        for w in range(world):
+            take = min(int(mat[w, g]), max(left, 0))
+            grant[w, g] = take
+            left -= take
+    return grant

@@ -94,3 +94,45 @@ def test_grouped_linear_matches_restatement(n_expert, seed):
     gx, gw, gb = nat.cpu_linear_backward(gy, x, counts, w, b)
     rx, rw, rb = torch_impl.linear_backward(gy, x, counts, w, b)
     assert torch.allclose(gx, rx) and torch.allclose(gw, rw) and torch.allclose(gb, rb)
+
+
+@settings(max_examples=50, deadline=None)
+@given(st.integers(min_value=1, max_value=8), st.integers(min_value=1, max_value=4),
+       st.integers(min_value=0, max_value=10_000))
+def test_exchange_offsets_tile_every_receive_buffer_exactly(world, n_expert, seed):
+    r"""The offsets every rank derives from the shared count matrix are consistent: on each
+    receiving rank the row ranges of all (source, expert) pairs are disjoint, ordered by local
+    expert then source rank, and cover ``[0, total)``; grants obey the capacities and equal the
+    two-step exchange of the collective-library path."""
+    gen = torch.Generator().manual_seed(seed)
+    tot = world * n_expert
+    mat = torch.randint(0, 7, (world, tot), generator=gen)
+    views = [torch_impl.exchange_offsets(mat, me, n_expert) for me in range(world)]
+    for owner in range(world):
+        _base, offs, total, overflow = views[owner]
+        assert not overflow and total == int(mat[:, owner * n_expert:(owner + 1) * n_expert].sum())
+        covered = []
+        for e in range(n_expert):
+            g = owner * n_expert + e
+            for src in range(world):
+                start = int(views[src][0][g])
+                n = int(mat[src, g])
+                assert int(offs[e]) <= start and start + n <= int(offs[e + 1])
+                covered.append((start, start + n))
+        covered = [c for c in covered if c[1] > c[0]]
+        covered.sort()
+        assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+        if covered:
+            assert covered[0][0] == 0 and covered[-1][1] == total
+    # a bounded receive buffer: totals are clamped and the overflow is flagged on every rank
+    small = max(0, int(mat.sum()) // (2 * world))
+    flags = [torch_impl.exchange_offsets(mat, me, n_expert, small)[3] for me in range(world)]
+    assert len(set(flags)) == 1
+    caps = torch.randint(0, 12, (world, n_expert), generator=gen)
+    grant = torch_impl.capacity_grants(mat, caps, n_expert)
+    for owner in range(world):
+        cap = caps[owner].to(torch.int32).clone()
+        proposals = mat[:, owner * n_expert:(owner + 1) * n_expert].reshape(-1).clone()
+        two_step = torch_impl.limit_by_capacity(proposals, cap, n_expert, world).view(world, n_expert)
+        assert torch.equal(grant[:, owner * n_expert:(owner + 1) * n_expert], two_step)
+        assert bool((two_step.sum(0) <= caps[owner]).all())
