@@ -136,6 +136,89 @@ def case_slice_group():
     assert float(full.grad[4 * world:].abs().sum()) == 0.0
 
 
+def case_pipeline_hybrid():
+    r"""Pipeline x expert parallelism (2 stages x 2 ranks): the 1F1B runner with MoE stages gives
+    the loss and the gradients of the same model run in one process; expert gradients are summed
+    over the data-parallel chains, shared ones averaged; the balance loss of every stage is
+    back-propagated with weight / n_stages."""
+    from fastmoe_b200.parallel.pipeline import PipelineRunner, build_stage_groups
+    rank, world = dist.get_rank(), dist.get_world_size()
+    n_stages, n_micro, tokens, d, h, n_exp, blocks_per_stage = 2, 3, 6, 8, 16, 2, 2
+    stage, group, prev_rank, next_rank = build_stage_groups(n_stages)
+    ssize = world // n_stages
+    chain = rank % ssize
+
+    class Block(nn.Module):
+        def __init__(self, num_expert, world_size, moe_group, gate):
+            super().__init__()
+            self.lin = nn.Linear(d, d)
+            self.moe = FMoETransformerMLP(num_expert=num_expert, d_model=d, d_hidden=h, top_k=2,
+                                          world_size=world_size, moe_group=moe_group, gate=gate)
+
+        def forward(self, x):
+            return x + self.moe(torch.tanh(self.lin(x)))
+
+    def data(j):
+        gen = torch.Generator().manual_seed(300 + j)
+        xs = [torch.randn(tokens, d, generator=gen) for _ in range(n_micro)]
+        ts = [torch.randn(tokens, d, generator=gen) for _ in range(n_micro)]
+        return xs, ts
+
+    def mse(out, target):
+        return (out - target).pow(2).mean()
+
+    gate_grads = {}
+    for gate_cls, weight in ((gates.NaiveGate, 0.0), (gates.GShardGate, 0.0), (gates.GShardGate, 0.5),
+                             (gates.GShardGate, 1.0)):
+        torch.manual_seed(17)
+        full = nn.Sequential(*[Block(n_exp * ssize, 1, None, gate_cls)
+                               for _ in range(n_stages * blocks_per_stage)])
+        mine = nn.Sequential(*[Block(n_exp, ssize, group, gate_cls) for _ in range(blocks_per_stage)])
+        refs = list(full)[stage * blocks_per_stage:(stage + 1) * blocks_per_stage]
+        lo, hi = chain * n_exp, (chain + 1) * n_exp
+        for b, ref in zip(mine, refs):
+            b.lin.load_state_dict(ref.lin.state_dict())
+            b.moe.gate.load_state_dict(ref.moe.gate.state_dict())
+            with torch.no_grad():
+                for name in ("htoh4", "h4toh"):
+                    getattr(b.moe.experts, name).weight.copy_(getattr(ref.moe.experts, name).weight[lo:hi])
+                    getattr(b.moe.experts, name).bias.copy_(getattr(ref.moe.experts, name).bias[lo:hi])
+        model = DistributedGroupedDataParallel(mine, dp_group=group, gate_group=group, moe_group=group,
+                                               need_sync=False)
+        xs, ts = data(chain)
+        runner = PipelineRunner(mine, stage, n_stages, prev_rank, next_rank, (tokens, d), torch.float32,
+                                loss_fn=mse, balance_weight=weight)
+        torch.manual_seed(23)          # GShard's random second-expert routing: same draws in every run
+        loss = runner.run(micro_batches=xs if stage == 0 else None,
+                          targets=ts if stage == n_stages - 1 else None, n_micro=n_micro)
+        model.allreduce_params()
+
+        if gate_cls is gates.NaiveGate:
+            # single-process reference over the data of both chains
+            total = 0.0
+            for j in range(ssize):
+                xj, tj = data(j)
+                for x, t in zip(xj, tj):
+                    total = total + mse(full(x), t) / (n_micro * ssize)
+            total.backward()
+            if stage == n_stages - 1:
+                mean = loss.clone()
+                dist.all_reduce(mean, group=group)
+                assert torch.allclose(mean / ssize, total.detach(), atol=1e-5), (mean / ssize, total)
+            for b, ref in zip(mine, refs):
+                assert torch.allclose(b.lin.weight.grad, ref.lin.weight.grad, atol=1e-5)
+                assert torch.allclose(b.moe.gate.gate.weight.grad, ref.moe.gate.gate.weight.grad, atol=1e-5)
+                want = ref.moe.experts.htoh4.weight.grad[lo:hi] * ssize
+                assert torch.allclose(b.moe.experts.htoh4.weight.grad, want, atol=1e-5)
+        else:
+            gate_grads[weight] = torch.cat([b.moe.gate.gate.weight.grad.reshape(-1) for b in mine]).clone()
+    # Every stage back-propagates weight / n_stages times its own balance loss: the gate
+    # gradients are affine in the weight, and the balance term is not zero on any stage.
+    g0, g1, g2 = gate_grads[0.0], gate_grads[0.5], gate_grads[1.0]
+    assert torch.allclose(g2 - g1, g1 - g0, atol=1e-5), float(((g2 - g1) - (g1 - g0)).abs().max())
+    assert float((g1 - g0).abs().max()) > 1e-6, "the balance loss did not reach the gates of stage %d" % stage
+
+
 def case_smart_schedule():
     r"""Smart schedule (all group sizes, with and without shadow experts) == general path."""
     from fastmoe_b200.fastermoe import schedule

@@ -14,6 +14,12 @@ def test_cpu_ranks(case, world):
     assert codes == [0] * world, codes
 
 
+def test_pipeline_times_expert_parallelism():
+    r"""2 pipeline stages x 2 expert-parallel ranks over gloo."""
+    codes = run_ranks("dist_cpu_worker.py", "pipeline_hybrid", 4, timeout=240)
+    assert codes == [0] * 4, codes
+
+
 def test_rank_failure_is_detected():
     r"""Rank 1 exits before the collective; rank 0 must come back with an error, not hang."""
     codes = run_ranks("dist_cpu_worker.py", "rank_failure", 2, timeout=120, stop_on_failure=False)
