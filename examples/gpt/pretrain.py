@@ -10,6 +10,12 @@ checkpoints are sharded per data-parallel rank.  ``FMOE_FASTER_SCHEDULE_ENABLE=1
 ``FMOE_FASTER_SHADOW_ENABLE=1`` turn on the smart schedule and shadow experts.  Tokens are
 uniform over the vocabulary (synthetic).
 
+``--pipeline-model-parallel-size P`` splits the layers over ``P`` stages (ranks ``s * world/P ..``
+form stage ``s``; experts are spread over the ranks of a stage) and runs ``--num-microbatches``
+micro-batches per iteration through the 1F1B runner of :mod:`fastmoe_b200.parallel.pipeline`,
+every stage back-propagating ``balance_loss_weight / P`` times the balance loss of its own
+gates.  The output embedding of the last stage is not tied to the input embedding of the first.
+
     torchrun --nproc-per-node 8 --master-addr 127.0.0.1 examples/gpt/pretrain.py --fmoefy \
         --num-layers 24 --hidden-size 1024 --num-attention-heads 16 --seq-length 1024 \
         --micro-batch-size 8 --num-experts 2 --top-k 1 --balance-strategy switch --train-iters 20
@@ -46,6 +52,8 @@ def get_args():
     p.add_argument("--load", default=None)
     p.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
     p.add_argument("--zipf", type=float, default=0.0, help="skew of the gate bias (0 = none)")
+    p.add_argument("--pipeline-model-parallel-size", type=int, default=1)
+    p.add_argument("--num-microbatches", type=int, default=1)
     add_fmoe_args(p)
     args = p.parse_args()
     if getattr(args, "num_experts", None) is not None:
@@ -56,12 +64,18 @@ def get_args():
 def main():
     args = get_args()
     rank, world, device = init_distributed()
+    pp = args.pipeline_model_parallel_size
+    assert world % pp == 0 and args.num_layers % pp == 0
     args.tensor_model_parallel_size = 1
-    args.pipeline_model_parallel_size = 1
-    args.data_parallel_size = world
-    args.distributed_experts = world > 1
+    args.data_parallel_size = world // pp
+    args.distributed_experts = args.data_parallel_size > 1
     args.fp16 = args.dtype == "fp16"
-    stub.install(args)
+    stage, stage_group, prev_rank, next_rank = 0, None, None, None
+    if pp > 1:
+        from fastmoe_b200.parallel.pipeline import PipelineRunner, build_stage_groups
+        stage, stage_group, prev_rank, next_rank = build_stage_groups(pp)
+    stub.install(args, data_parallel_group=stage_group, pipeline_rank=stage, pipeline_size=pp,
+                 num_microbatches=args.num_microbatches)
     from fastmoe_b200 import megatron as fmoe_megatron
 
     torch.manual_seed(1234)
@@ -73,8 +87,10 @@ def main():
                     vocab_size=args.vocab_size, max_position_embeddings=args.seq_length,
                     init_method_std=args.init_method_std)
 
-    def model_provider(pre_process=True, post_process=True):
-        return GPTModel(cfg, pre_process, post_process)
+    def model_provider(pre_process=None, post_process=None):
+        pre = stage == 0 if pre_process is None else pre_process
+        post = stage == pp - 1 if post_process is None else post_process
+        return GPTModel(cfg, pre, post, num_layers=args.num_layers // pp)
 
     if args.fmoefy:
         provider = fmoe_megatron.patch_model_provider(model_provider, Megatron_Version="v3.0.2")
@@ -84,9 +100,9 @@ def main():
                                          hidden_hidden_size=args.hidden_hidden_size, top_k=args.top_k,
                                          megatron_version="v3.0.2")
         else:
-            model = provider(True, True)
+            model = provider(stage == 0, stage == pp - 1)
         if args.zipf > 0:
-            tot = args.fmoe_num_experts * (world if args.distributed_experts else 1)
+            tot = args.fmoe_num_experts * (args.data_parallel_size if args.distributed_experts else 1)
             bias = -args.zipf * torch.log(torch.arange(1, tot + 1, dtype=torch.float32))
             for layer in model.language_model.encoder.layers:
                 gate = getattr(layer.mlp.gate, "gate", None)
@@ -98,6 +114,11 @@ def main():
     model = model.to(device).to(dtype)
     ddp = fmoe_megatron.DistributedDataParallel(model) if world > 1 else model
     opt = torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.01)
+
+    if pp > 1:
+        run_pipeline(args, model, ddp, opt, PipelineRunner, stage, pp, prev_rank, next_rank, rank, world,
+                     device, dtype, cfg, fmoe_megatron)
+        return
 
     gen = torch.Generator(device="cpu").manual_seed(4321 + rank)
     tokens_per_iter = args.micro_batch_size * args.seq_length * world
@@ -129,6 +150,65 @@ def main():
                                             hh if args.fmoefy else None) * tokens_per_iter
                 print("iteration {:6d} | ms/iter {:9.2f} | tokens/s {:12.0f} | model TFLOP/s {:8.1f} | lm loss {:7.4f}".format(
                     it, ms, tokens_per_iter / ms * 1e3, flops / ms / 1e9, float(lm_loss)), flush=True)
+            window = 0
+            watch.__enter__()
+    if args.save:
+        fmoe_megatron.save_checkpoint(args.train_iters, ddp, None, None)
+
+
+class _Stage(torch.nn.Module):
+    r"""A pipeline stage of the GPT: tokens or the previous stage's hidden states in, hidden
+    states (logits on the last stage) out."""
+
+    def __init__(self, model):
+        super().__init__()
+        self.model = model
+
+    def forward(self, x):
+        if self.model.pre_process:
+            return self.model(x)
+        self.model.set_input_tensor(x)
+        return self.model(None)
+
+
+def run_pipeline(args, model, ddp, opt, runner_cls, stage, pp, prev_rank, next_rank, rank, world,
+                 device, dtype, cfg, fmoe_megatron):
+    stage_size = world // pp
+    chain = rank % stage_size
+
+    def lm_loss(logits, labels):
+        return torch.nn.functional.cross_entropy(logits.float().reshape(-1, logits.shape[-1]),
+                                                 labels.reshape(-1))
+
+    weight = args.balance_loss_weight if (args.fmoefy and args.balance_strategy) else 0.0
+    runner = runner_cls(_Stage(model), stage, pp, prev_rank, next_rank,
+                        (args.seq_length, args.micro_batch_size, args.hidden_size), dtype,
+                        loss_fn=lm_loss, balance_weight=weight, device=device)
+    n_micro = args.num_microbatches
+    tokens_per_iter = args.micro_batch_size * args.seq_length * stage_size * n_micro
+    watch = Stopwatch(device)
+    watch.__enter__()
+    window = 0
+    for it in range(1, args.train_iters + 1):
+        # the first and the last stage of a chain draw the same batch
+        gen = torch.Generator(device="cpu").manual_seed(4321 + 1000 * it + chain)
+        blocks = [torch.randint(0, args.vocab_size, (args.micro_batch_size, args.seq_length + 1), generator=gen)
+                  for _ in range(n_micro)]
+        tokens = [b[:, :-1].to(device) for b in blocks] if stage == 0 else None
+        labels = [b[:, 1:].to(device) for b in blocks] if stage == pp - 1 else None
+        opt.zero_grad(set_to_none=True)
+        loss = runner.run(micro_batches=tokens, targets=labels, n_micro=n_micro)
+        if stage_size > 1:
+            ddp.allreduce_params()
+        clip_grad_norm_moe(model.parameters(), args.clip_grad)
+        opt.step()
+        window += 1
+        if it % args.log_interval == 0 or it == args.train_iters:
+            watch.__exit__()
+            ms = max_over_ranks(watch.ms, device) / window
+            if rank == world - 1:
+                print("iteration {:6d} | ms/iter {:9.2f} | tokens/s {:12.0f} | stages {} x {} | lm loss {:7.4f}".format(
+                    it, ms, tokens_per_iter / ms * 1e3, pp, stage_size, float(loss)), flush=True)
             window = 0
             watch.__enter__()
     if args.save:

@@ -19,9 +19,12 @@ def free_port():
         return s.getsockname()[1]
 
 
-def run_ranks(script, case, world_size, timeout=300, extra_env=None, stop_on_failure=True):
+def run_ranks(script, case, world_size, timeout=300, extra_env=None, stop_on_failure=True,
+              args=None):
     r"""Returns the list of exit codes; children are killed (by pid) when `timeout` expires, and
-    — unless `stop_on_failure` is off — a few seconds after the first rank has failed."""
+    — unless `stop_on_failure` is off — a few seconds after the first rank has failed.
+    `script` is relative to this directory (or absolute); `args` replaces `[case]` as the
+    script's command line."""
     port = free_port()
     procs = []
     for rank in range(world_size):
@@ -30,7 +33,8 @@ def run_ranks(script, case, world_size, timeout=300, extra_env=None, stop_on_fai
                     "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
         if extra_env:
             env.update(extra_env)
-        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, script), case], env=env))
+        cmd = [sys.executable, os.path.join(HERE, script)] + (list(args) if args is not None else [case])
+        procs.append(subprocess.Popen(cmd, env=env))
     # Poll all ranks: when one fails, the others would wait for it in their next collective
     # until `timeout`, so they are stopped (by pid) right away and reported as -9.
     deadline = time.monotonic() + timeout

@@ -20,6 +20,20 @@ def test_pipeline_times_expert_parallelism():
     assert codes == [0] * 4, codes
 
 
+def test_gpt_example_with_pipeline_stages():
+    r"""The fmoefy-ed GPT example as 2 pipeline stages x 2 expert-parallel ranks (gloo, tiny)."""
+    import os
+    script = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                          "examples", "gpt", "pretrain.py")
+    argv = ["--fmoefy", "--num-experts", "2", "--top-k", "2", "--balance-strategy", "gshard",
+            "--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "2",
+            "--seq-length", "16", "--vocab-size", "64", "--micro-batch-size", "2", "--train-iters", "2",
+            "--log-interval", "1", "--pipeline-model-parallel-size", "2", "--num-microbatches", "3",
+            "--dtype", "fp32"]
+    codes = run_ranks(script, None, 4, timeout=240, args=argv)
+    assert codes == [0] * 4, codes
+
+
 def test_rank_failure_is_detected():
     r"""Rank 1 exits before the collective; rank 0 must come back with an error, not hang."""
     codes = run_ranks("dist_cpu_worker.py", "rank_failure", 2, timeout=120, stop_on_failure=False)
