@@ -268,6 +268,54 @@ def case_shadow_policy():
     assert skew[0] and not any(skew[1:])
 
 
+def case_tensor_parallel():
+    r"""Megatron tensor parallelism of the experts: every rank of the tensor-parallel group holds a
+    slice of each expert's hidden dimension, the partial outputs are summed
+    (``reduce_from_tensor_model_parallel_region``); together they equal one layer whose expert
+    weights are the concatenation of the slices (and whose output bias is the sum of the ranks'
+    biases, a property of the reference's layout)."""
+    import types
+    from fastmoe_b200.megatron import stub
+    from fastmoe_b200.megatron.layers import MegatronMLP
+    rank, world = dist.get_rank(), dist.get_world_size()
+    d, hidden_per_rank, n_exp = 8, 6, 3
+    args = types.SimpleNamespace(hidden_size=d, num_layers=2, balance_strategy="naive", top_k=2,
+                                 init_method_std=0.05, fmoe_num_experts=n_exp, distributed_experts=False,
+                                 hidden_hidden_size=hidden_per_rank, tensor_model_parallel_size=world)
+    stub.install(args, tensor_parallel_group=dist.group.WORLD)
+    import numpy as np
+    torch.manual_seed(31)          # same gate on every rank
+    np.random.seed(40 + rank)      # different expert slices per rank
+    mlp = MegatronMLP(args, 0)
+    for p in mlp.experts.parameters():
+        with torch.no_grad():
+            p.add_(0.01 * (rank + 1))          # also give the biases rank-dependent values
+    x = torch.randn(11, d, generator=torch.Generator().manual_seed(5), requires_grad=True)
+    out, bias = mlp(x)
+    assert bias.shape == (d,) and float(bias.abs().sum()) == 0.0
+    out.pow(2).sum().backward()
+
+    full = FMoETransformerMLP(num_expert=n_exp, d_model=d, d_hidden=hidden_per_rank * world, top_k=2)
+    full.gate.load_state_dict(mlp.gate.state_dict())
+    w1 = torch.cat(_gather(mlp.experts.htoh4.weight.detach()), dim=1)     # [E, world*h, d]
+    b1 = torch.cat(_gather(mlp.experts.htoh4.bias.detach()), dim=1)
+    w2 = torch.cat(_gather(mlp.experts.h4toh.weight.detach()), dim=2)     # [E, d, world*h]
+    b2 = torch.stack(_gather(mlp.experts.h4toh.bias.detach())).sum(0)
+    with torch.no_grad():
+        full.experts.htoh4.weight.copy_(w1)
+        full.experts.htoh4.bias.copy_(b1)
+        full.experts.h4toh.weight.copy_(w2)
+        full.experts.h4toh.bias.copy_(b2)
+    xr = x.detach().clone().requires_grad_(True)
+    ref = full(xr)
+    assert torch.allclose(out, ref, atol=1e-5), float((out - ref).abs().max())
+    ref.pow(2).sum().backward()
+    lo, hi = rank * hidden_per_rank, (rank + 1) * hidden_per_rank
+    assert torch.allclose(mlp.experts.htoh4.weight.grad, full.experts.htoh4.weight.grad[:, lo:hi], atol=1e-4)
+    assert torch.allclose(mlp.experts.h4toh.weight.grad, full.experts.h4toh.weight.grad[:, :, lo:hi], atol=1e-4)
+    stub.uninstall()
+
+
 def case_megatron_checkpoint():
     r"""Megatron adapter under expert parallelism: fmoefy, grouped DDP with a gate group, and
     sharded save / load (rank 0 full file, other ranks expert shards) giving identical models."""

@@ -34,6 +34,11 @@ def test_gpt_example_with_pipeline_stages():
     assert codes == [0] * 4, codes
 
 
+def test_megatron_tensor_parallel_experts():
+    codes = run_ranks("dist_cpu_worker.py", "tensor_parallel", 2, timeout=240)
+    assert codes == [0, 0], codes
+
+
 def test_rank_failure_is_detected():
     r"""Rank 1 exits before the collective; rank 0 must come back with an error, not hang."""
     codes = run_ranks("dist_cpu_worker.py", "rank_failure", 2, timeout=120, stop_on_failure=False)
