@@ -108,6 +108,40 @@ def case_grouped_ddp():
     assert torch.equal(moe.experts.htoh4.weight.grad, local_exp)
 
 
+def case_hybrid_dp_ep():
+    r"""Hybrid data x expert parallelism on 4 ranks: ranks {0,1} and {2,3} are two expert-parallel
+    groups, the experts of rank r and rank r+2 are replicas (tag 'dp', reduced over {r, r+2}),
+    gates are reduced over all ranks.  After the reduction the replicas hold identical gradients
+    and they equal the average of the two groups' own gradients."""
+    rank, world = dist.get_rank(), dist.get_world_size()
+    assert world == 4
+    ep_groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]
+    dp_groups = [dist.new_group([0, 2]), dist.new_group([1, 3])]
+    ep_group, dp_group = ep_groups[rank // 2], dp_groups[rank % 2]
+    torch.manual_seed(70 + rank % 2)              # replicas start from the same experts
+    moe = FMoETransformerMLP(num_expert=2, d_model=8, d_hidden=16, world_size=2, moe_group=ep_group,
+                             top_k=2, expert_dp_comm="dp")
+    model = DistributedGroupedDataParallel(moe, dp_group=dp_group, moe_group=ep_group,
+                                           gate_group=dist.group.WORLD)
+    # construction synchronised every tag inside its group
+    rep = [torch.empty_like(moe.experts.htoh4.weight) for _ in range(2)]
+    dist.all_gather(rep, moe.experts.htoh4.weight.detach().contiguous(), group=dp_group)
+    assert torch.equal(rep[0], rep[1])
+    gates_all = _gather(moe.gate.gate.weight.detach())
+    assert all(torch.equal(gates_all[0], g) for g in gates_all)
+    for p in moe.experts.parameters():
+        assert p.dp_comm == "dp"
+    torch.manual_seed(90 + rank)                  # different data everywhere
+    model(torch.randn(10, 8)).pow(2).sum().backward()
+    own_expert = moe.experts.htoh4.weight.grad.clone()
+    own_gate = moe.gate.gate.weight.grad.clone()
+    model.allreduce_params()
+    pair = [torch.empty_like(own_expert) for _ in range(2)]
+    dist.all_gather(pair, own_expert, group=dp_group)
+    assert torch.allclose(moe.experts.htoh4.weight.grad, (pair[0] + pair[1]) / 2, atol=1e-6)
+    assert torch.allclose(moe.gate.gate.weight.grad, torch.stack(_gather(own_gate)).mean(0), atol=1e-6)
+
+
 def case_slice_group():
     r"""slice_group: ranks share the input, each routes its slice, outputs are all-gathered."""
     rank, world = dist.get_rank(), dist.get_world_size()

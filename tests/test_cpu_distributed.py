@@ -34,6 +34,11 @@ def test_gpt_example_with_pipeline_stages():
     assert codes == [0] * 4, codes
 
 
+def test_hybrid_data_and_expert_parallelism():
+    codes = run_ranks("dist_cpu_worker.py", "hybrid_dp_ep", 4, timeout=240)
+    assert codes == [0] * 4, codes
+
+
 def test_megatron_tensor_parallel_experts():
     codes = run_ranks("dist_cpu_worker.py", "tensor_parallel", 2, timeout=240)
     assert codes == [0, 0], codes
