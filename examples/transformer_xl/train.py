@@ -77,6 +77,10 @@ def get_args(argv=None):
     p.add_argument("--pre_lnorm", action="store_true")
     p.add_argument("--varlen", action="store_true")
     p.add_argument("--multi_gpu", action="store_true", help="nn.DataParallel in one process")
+    p.add_argument("--gpu0_bsz", type=int, default=-1,
+                   help="with --multi_gpu: sequences of a batch given to GPU 0 (it also gathers)")
+    p.add_argument("--sample_softmax", type=int, default=-1,
+                   help="train against this many log-uniform negatives instead of the full softmax")
     p.add_argument("--same_length", action="store_true")
     p.add_argument("--clamp_len", type=int, default=-1)
     p.add_argument("--log-interval", type=int, default=10)
@@ -103,7 +107,8 @@ def build_model(args, n_token, world, cutoffs):
         clamp_len=args.clamp_len, moe=args.moe, moe_num_expert=args.moe_num_expert,
         moe_top_k=args.moe_top_k, world_size=world if args.moe else 1,
         d_embed=args.d_embed, cutoffs=cutoffs if args.adaptive else (), div_val=args.div_val,
-        tie_projs=[False] + [True] * len(cutoffs) if args.adaptive else ())
+        tie_projs=[False] + [True] * len(cutoffs) if args.adaptive else (),
+        sample_softmax=args.sample_softmax)
 
 
 def build_optimizer(args, model):
@@ -168,7 +173,11 @@ def main(argv=None):
 
     model = build_model(args, n_token, world, cutoffs).to(device).to(dtype)
     if args.multi_gpu and world == 1 and torch.cuda.device_count() > 1:
-        para_model = nn.DataParallel(model, dim=1)       # batch is dimension 1 of [seq, batch]
+        if args.gpu0_bsz >= 0:
+            from exp_utils import BalancedDataParallel
+            para_model = BalancedDataParallel(args.gpu0_bsz // args.batch_chunk, model, dim=1)
+        else:
+            para_model = nn.DataParallel(model, dim=1)   # batch is dimension 1 of [seq, batch]
     elif world > 1:
         para_model = DistributedGroupedDataParallel(model)
     else:
@@ -180,11 +189,14 @@ def main(argv=None):
     if args.restart and restart_dir:
         loaded, _ = checkpoint.load(restart_dir, model, opt)
         step = loaded or 0
+    log = print
+    if rank == 0 and args.work_dir:
+        from exp_utils import create_exp_dir
+        log = create_exp_dir(args.work_dir, scripts_to_save=[os.path.abspath(__file__)])
     if rank == 0:
         n_all = sum(p.numel() for p in model.parameters())
         n_exp = sum(p.numel() for p in model.parameters() if getattr(p, "dp_comm", "dp") == "none")
-        print("| params/rank {:,} (experts {:,}) | vocab {} | ranks {}".format(n_all, n_exp, n_token, world),
-              flush=True)
+        log("| params/rank {:,} (experts {:,}) | vocab {} | ranks {}".format(n_all, n_exp, n_token, world))
 
     tokens_per_step = args.tgt_len * args.batch_size * world
     model.train()
@@ -228,16 +240,16 @@ def main(argv=None):
                     mean = window_loss / window
                     unit = "bpc {:6.4f}".format(mean / math.log(2)) if args.dataset in ("enwik8", "text8") \
                         else "ppl {:9.3f}".format(math.exp(min(mean, 20.0)))
-                    print("| step {:6d} | lr {:.3g} | ms/batch {:8.2f} | tokens/s {:12.0f} | loss {:5.3f} | {}".format(
-                        step, opt.param_groups[0]["lr"], ms, tokens_per_step / ms * 1e3, mean, unit), flush=True)
+                    log("| step {:6d} | lr {:.3g} | ms/batch {:8.2f} | tokens/s {:12.0f} | loss {:5.3f} | {}".format(
+                        step, opt.param_groups[0]["lr"], ms, tokens_per_step / ms * 1e3, mean, unit))
                 window, window_loss = 0, 0.0
                 watch.__enter__()
             if step % args.eval_interval == 0 or step == args.max_step:
                 val = evaluate(args, model, va_iter.get_fixlen_iter(), device, args.max_eval_steps)
                 val = max_over_ranks(val, device) if world > 1 else val
                 if rank == 0:
-                    print("| eval at step {:6d} | {:6.1f} s | valid loss {:5.3f}".format(
-                        step, time.time() - t_start, val), flush=True)
+                    log("| eval at step {:6d} | {:6.1f} s | valid loss {:5.3f}".format(
+                        step, time.time() - t_start, val))
                 if args.work_dir and (best_val is None or val < best_val):
                     checkpoint.save(args.work_dir, step, model, opt)
                     best_val = val

@@ -16,6 +16,7 @@ import torch.nn.functional as F
 
 from ..transformer import FMoETransformerMLP
 from .adaptive import AdaptiveEmbedding, ProjectedAdaptiveLogSoftmax
+from .sampled_softmax import LogUniformSampler, sampled_softmax_nll
 
 
 class PositionalEmbedding(nn.Module):
@@ -132,14 +133,15 @@ class MemTransformerLM(nn.Module):
     ``d_embed`` / ``cutoffs`` / ``div_val`` / ``tie_projs`` select the adaptive embedding and
     adaptive softmax used for large vocabularies (``--adaptive`` in the training script); with
     no cut-offs and ``d_embed == d_model`` a plain embedding and a plain (tied) output layer
-    are used.
+    are used.  ``sample_softmax=N`` trains against ``N`` log-uniform negatives
+    (:mod:`fastmoe_b200.models.sampled_softmax`); evaluation always uses the full softmax.
     """
 
     def __init__(self, n_token, n_layer, n_head, d_model, d_head, d_inner, dropout=0.1, dropatt=0.0,
                  tie_weight=True, pre_lnorm=False, tgt_len=512, ext_len=0, mem_len=512,
                  same_length=False, clamp_len=-1, moe=False, moe_num_expert=64, moe_top_k=2,
                  world_size=1, moe_group=None, gate=None, d_embed=None, cutoffs=(), div_val=1,
-                 tie_projs=()):
+                 tie_projs=(), sample_softmax=-1):
         super().__init__()
         self.n_token, self.n_layer, self.d_model = n_token, n_layer, d_model
         d_embed = d_model if d_embed is None or d_embed <= 0 else d_embed
@@ -168,6 +170,12 @@ class MemTransformerLM(nn.Module):
             self.crit = None
             self.out_layer = nn.Linear(d_model, n_token)
         self.apply(self._init)
+        # --sample_softmax N: train against N log-uniform negatives instead of the full softmax
+        self.sample_softmax = sample_softmax
+        self.sampler = None
+        if sample_softmax > 0:
+            assert not self.adaptive, "sampled softmax works on the plain output layer"
+            self.sampler = LogUniformSampler(n_token, sample_softmax)
         if tie_weight:
             if self.adaptive:
                 self.crit.tie_weights(self.word_emb, tie_projs)
@@ -229,6 +237,10 @@ class MemTransformerLM(nn.Module):
         pred = hidden[-tgt_len:]
         if self.adaptive:
             loss = self.crit(pred.reshape(-1, pred.shape[-1]), target.reshape(-1)).view(tgt_len, -1)
+        elif self.sampler is not None and self.training:
+            loss = sampled_softmax_nll(self.out_layer.weight, self.out_layer.bias,
+                                       pred.reshape(-1, pred.shape[-1]), target.reshape(-1),
+                                       self.sampler).view(tgt_len, -1)
         else:
             logits = self.out_layer(pred)
             loss = F.cross_entropy(logits.float().view(-1, self.n_token), target.reshape(-1),

@@ -112,3 +112,34 @@ def test_transformer_xl_training_script_learns_and_restarts(tmp_path, capsys):
     import eval as xl_eval
     loss = xl_eval.main(common + ["--split", "valid"])
     assert math.isfinite(loss)
+
+
+def test_log_uniform_sampler_and_sampled_softmax():
+    from fastmoe_b200.models.sampled_softmax import LogUniformSampler, sampled_softmax_nll
+    sampler = LogUniformSampler(500, 40, torch.Generator().manual_seed(1))
+    assert abs(float(sampler.prob.sum()) - 1.0) < 1e-9
+    assert bool((sampler.prob[:-1] >= sampler.prob[1:]).all())       # frequent classes first
+    labels = torch.randint(0, 500, (30,))
+    true_q, samp_q, negatives = sampler.sample(labels)
+    assert negatives.unique().numel() == negatives.numel() <= 80
+    assert true_q.shape == (30,) and samp_q.shape == negatives.shape
+    # with every class as a "negative" and no proposal correction the loss is the full softmax
+    class Everything:
+        def sample(self, lab):
+            return torch.zeros(lab.shape[0]), torch.zeros(500), torch.arange(500)
+    w, b, h = torch.randn(500, 8), torch.randn(500), torch.randn(30, 8)
+    nll = sampled_softmax_nll(w, b, h, labels, Everything())
+    ref = torch.nn.functional.cross_entropy(h @ w.t() + b, labels, reduction="none")
+    assert torch.allclose(nll, ref, atol=1e-4)
+
+
+def test_balanced_data_parallel_chunk_sizes(tmp_path):
+    from exp_utils import balanced_chunk_sizes, create_exp_dir
+    assert balanced_chunk_sizes(22, 4, 4) == [4, 6, 6, 6]
+    assert balanced_chunk_sizes(22, 4, 0) == [0, 8, 7, 7]
+    assert balanced_chunk_sizes(5, 4, 4) == [4, 1]
+    assert balanced_chunk_sizes(8, 1, 2) == [8]
+    log = create_exp_dir(str(tmp_path / "run"), scripts_to_save=[__file__])
+    log("hello", print_=False)
+    assert (tmp_path / "run" / "log.txt").read_text() == "hello\n"
+    assert (tmp_path / "run" / "scripts" / os.path.basename(__file__)).exists()
