@@ -29,8 +29,8 @@ from ..ops import grouped_gemm as gg
 from ..ops import native
 from . import symm
 
-LINK_BYTES_PER_S = 770e9       # measured peer-copy bandwidth per direction on this pool
-GEMM_FLOPS = 1643.7e12         # measured burst cuBLAS bf16 rate (MEASURED_PEAKS.json)
+LINK_BYTES_PER_S = 770e9       # measured peer-copy bandwidth per direction between two B200s (nominal 900e9)
+GEMM_FLOPS = 1643.7e12         # measured burst cuBLAS bf16 rate of one B200
 
 
 def main():
