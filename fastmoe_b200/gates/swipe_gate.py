@@ -1,38 +1,47 @@
-r"""SWIPE-balanced gate (parity: ``fmoe/gates/swipe_gate.py:15-49``)."""
+r"""
+SWIPE: a top-k gate whose training-time routing never overloads a worker.
+
+Parity: ``fmoe/gates/swipe_gate.py:15-49``.  Every worker can take ``B * top_k`` tokens per
+step.  The k choices of a token are balanced one rank of choice after the other: all first
+choices are offered to their workers, which accept them in rank order until full; the rejected
+tokens are "swiped" to workers that still have room (to their expert ``j % num_expert`` for the
+j-th choice); then the second choices go through the same procedure with the capacity that is
+left, and so on.  Scores are the softmax over the logits of the experts finally chosen.
+Evaluation keeps the plain top-k.  The expert-parallel group must exist (``ensure_comm``)
+before the first training call.
+"""
 import torch
-import torch.nn.functional as F
 
 from .naive_gate import NaiveGate
 from ..ops import api as _ops
+from ..ops import gating
 
 
 class SwipeGate(NaiveGate):
-    r"""Top-k gate whose training-time routing is re-balanced so that no worker receives more
-    than ``B·top_k`` tokens: overflow is swiped to expert ``j % num_expert`` of workers with room.
-    Evaluation is a plain top-k.  Needs the expert-parallel group (``ensure_comm``) first.
-    """
 
     def __init__(self, d_model, num_expert, world_size, top_k=2, gate_bias=True):
-        super().__init__(d_model, num_expert, world_size, top_k, gate_bias)
+        super().__init__(d_model, num_expert, world_size, top_k=top_k, gate_bias=gate_bias)
 
     def swipe_once(self, idx, capacity, bias):
+        r"""Balance one choice of every token; returns the new expert ids and what capacity is left."""
         with torch.no_grad():
-            new_idx, capacity = _ops.swipe_once(idx, capacity, self.num_expert, self.world_size, bias)
-        return new_idx.to(idx.device), capacity
+            moved, left = _ops.swipe_once(idx, capacity, self.num_expert, self.world_size, bias)
+        return moved.to(idx.device), left
+
+    def _balanced_choices(self, preferred):
+        r"""``preferred [B, k]`` (descending preference) → balanced ids ``[B, k]``."""
+        left = torch.scalar_tensor(preferred.shape[0] * self.top_k, dtype=torch.long)
+        columns = []
+        for choice in range(self.top_k):
+            ids, left = self.swipe_once(preferred[:, choice], left, choice % self.num_expert)
+            columns.append(ids)
+        return torch.stack(columns, dim=1)
 
     def forward(self, inp):
         logits = self.gate(inp)
-        top_val, top_idx = torch.topk(logits, k=self.top_k, dim=-1)
         if not self.training:
-            return top_idx, F.softmax(top_val, dim=-1)
-
-        capacity = torch.scalar_tensor(inp.shape[0] * self.top_k, dtype=torch.long)
-        rows = torch.arange(inp.shape[0], device=inp.device)
-        new_idx, new_val = [], []
-        for j in range(self.top_k):
-            idx_j, capacity = self.swipe_once(top_idx[:, j], capacity, j % self.num_expert)
-            new_idx.append(idx_j)
-            new_val.append(logits[rows, idx_j])
-        topk_idx = torch.stack(new_idx, dim=1)
-        topk_val = F.softmax(torch.stack(new_val, dim=1), dim=-1)
-        return topk_idx, topk_val
+            return gating.topk_softmax(logits, self.top_k)
+        preferred = torch.topk(logits, k=self.top_k, dim=-1).indices
+        chosen = self._balanced_choices(preferred)
+        scores = torch.softmax(torch.gather(logits, 1, chosen), dim=-1)
+        return chosen, scores

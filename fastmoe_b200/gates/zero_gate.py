@@ -1,22 +1,24 @@
-r"""Degenerate gate: every slot goes to global expert 0 (parity: ``fmoe/gates/zero_gate.py:11-30``)."""
+r"""
+A gate that sends everything to global expert 0.
+
+Useful for tests (all other experts receive zero tokens) and as the simplest possible routing
+policy.  Parity: ``fmoe/gates/zero_gate.py:11-30``: the first constructor argument (the model
+width) is ignored, ids come back flattened as ``[B * top_k]`` and scores as ``[B, 1, top_k]``
+with every slot weighted ``1 / top_k``; ``FMoE`` restores the ``[B, top_k]`` view of the ids.
+"""
 import torch
 
 from .base_gate import BaseGate
 
 
 class ZeroGate(BaseGate):
-    r"""Routes all ``top_k`` slots of every token to expert 0 with weight ``1/top_k``.
 
-    The ids are returned flattened (``[B·k]``) like the reference does; ``FMoE`` restores
-    the ``[B, k]`` view.
-    """
-
-    def __init__(self, _1, num_expert, world_size, top_k=2):
+    def __init__(self, _d_model, num_expert, world_size, top_k=2):
         super().__init__(num_expert, world_size)
         self.top_k = top_k
 
     def forward(self, inp):
-        n = inp.shape[0]
-        idx = inp.new_zeros(n * self.top_k, dtype=torch.int64)
-        score = torch.full((n, 1, self.top_k), 1.0 / self.top_k, device=inp.device)
-        return idx, score
+        n_slots = inp.shape[0] * self.top_k
+        expert_ids = torch.zeros(n_slots, dtype=torch.int64, device=inp.device)
+        weights = torch.full((inp.shape[0], 1, self.top_k), 1.0 / self.top_k, device=inp.device)
+        return expert_ids, weights

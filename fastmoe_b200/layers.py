@@ -155,65 +155,71 @@ class FMoE(nn.Module):
         r"""Hook for subclasses with a fully fused device path; ``None`` = use the general path."""
         return None
 
-    def forward(self, moe_inp):
-        sizes = [t.shape[0] for t in tree.flatten(moe_inp)]
-        assert all(s == sizes[0] for s in sizes), "MoE inputs must have the same batch size"
+    @staticmethod
+    def _check_batch(pytree, what):
+        rows = {t.shape[0] for t in tree.flatten(pytree)}
+        assert len(rows) <= 1, "MoE %s must have the same batch size" % what
 
+    def _route(self, moe_inp):
+        r"""Gate call, hook, and the ``[B, k]`` view of the expert ids."""
+        ids, scores = self.gate(moe_inp)
+        if self.gate_hook is not None:
+            self.gate_hook(ids, scores, None)
+        if ids.dim() == 1 and self.top_k > 1:
+            # Gates that return flattened ids (ZeroGate, NoisyGate in the reference) are
+            # given their [B, k] shape back; the reference would treat them as top-1.
+            ids = ids.view(-1, self.top_k)
+        return ids, scores
+
+    def _unmask(self, rows, mask):
+        r"""``[kept * k, d]`` expert outputs → ``[B, k, d]`` with the constant rows of
+        ``mask_dict`` at the masked tokens."""
+        width = rows.shape[-1]
+        full = torch.zeros(mask.shape[0], self.top_k, width, device=rows.device, dtype=rows.dtype)
+        full[mask == 0] = rows.view(-1, self.top_k, width)
+        for value, constant in self.mask_dict.items():
+            full[mask == value] = constant
+        return full
+
+    def _general_path(self, moe_inp, ids, scores):
+        r"""Arbitrary experts / pytrees / masks: scatter, experts, gather, weighted sum over k."""
+        mask = None
+        if self.mask is not None and self.mask_dict is not None:
+            mask = self.mask.view(-1)
+            routed = mask == 0
+            moe_inp = tree.map_structure(lambda t: t[routed, :], moe_inp)
+            ids = ids[routed, :]
+
+        run, per_expert = _general_forward_fn()
+        slots = run(moe_inp, ids, self.expert_fn_single if per_expert else self.expert_fn,
+                    self.num_expert, self.world_size, experts=getattr(self, "experts", None))
+        if mask is not None:
+            per_token = tree.map_structure(lambda t: self._unmask(t, mask), slots)
+        else:
+            per_token = tree.map_structure(lambda t: t.view(-1, self.top_k, t.shape[-1]), slots)
+
+        weights = scores.view(-1, 1, self.top_k)
+        return tree.map_structure(
+            lambda t: torch.bmm(weights.to(t.dtype), t).reshape(-1, t.shape[-1]), per_token)
+
+    def forward(self, moe_inp):
+        self._check_batch(moe_inp, "inputs")
         if self.world_size > 1:
             tree.map_structure(lambda t: ensure_comm(t, self.moe_group), moe_inp)
-        if self.slice_size > 1:
+        sliced = self.slice_size > 1
+        if sliced:
             moe_inp = tree.map_structure(
                 lambda t: Slice.apply(t, self.slice_rank, self.slice_size, self.slice_group), moe_inp)
 
-        gate_top_k_idx, gate_score = self.gate(moe_inp)
-        if self.gate_hook is not None:
-            self.gate_hook(gate_top_k_idx, gate_score, None)
-        if gate_top_k_idx.dim() == 1 and self.top_k > 1:
-            # Gates that return flattened ids (ZeroGate, NoisyGate in the reference) are
-            # given their [B, k] shape back; the reference would treat them as top-1.
-            gate_top_k_idx = gate_top_k_idx.view(-1, self.top_k)
+        ids, scores = self._route(moe_inp)
+        out = None
+        if self.mask is None or self.mask_dict is None:
+            out = self._fused_forward(moe_inp, ids, scores)
+        if out is None:
+            out = self._general_path(moe_inp, ids, scores)
 
-        use_mask = self.mask is not None and self.mask_dict is not None
-        moe_outp = None
-        if not use_mask:
-            moe_outp = self._fused_forward(moe_inp, gate_top_k_idx, gate_score)
-
-        if moe_outp is None:
-            mask = None
-            if use_mask:
-                mask = self.mask.view(-1)
-                moe_inp = tree.map_structure(lambda t: t[mask == 0, :], moe_inp)
-                gate_top_k_idx = gate_top_k_idx[mask == 0, :]
-
-            general_forward, per_expert = _general_forward_fn()
-            fwd = general_forward(
-                moe_inp, gate_top_k_idx,
-                self.expert_fn_single if per_expert else self.expert_fn,
-                self.num_expert, self.world_size,
-                experts=getattr(self, "experts", None))
-
-            if use_mask:
-                def recover(t):
-                    dim = t.shape[-1]
-                    t = t.view(-1, self.top_k, dim)
-                    full = torch.zeros(mask.shape[0], self.top_k, dim, device=t.device, dtype=t.dtype)
-                    full[mask == 0] = t
-                    for value, row in self.mask_dict.items():
-                        full[mask == value] = row
-                    return full
-                stacked = tree.map_structure(recover, fwd)
-            else:
-                stacked = tree.map_structure(lambda t: t.view(-1, self.top_k, t.shape[-1]), fwd)
-
-            score = gate_score.view(-1, 1, self.top_k)
-            moe_outp = tree.map_structure(
-                lambda t: torch.bmm(score.to(t.dtype), t).reshape(-1, t.shape[-1]), stacked)
-
-        if self.slice_size > 1:
-            moe_outp = tree.map_structure(
-                lambda t: AllGather.apply(t, self.slice_rank, self.slice_size, self.slice_group),
-                moe_outp)
-
-        sizes = [t.shape[0] for t in tree.flatten(moe_outp)]
-        assert all(s == sizes[0] for s in sizes), "MoE outputs must have the same batch size"
-        return moe_outp
+        if sliced:
+            out = tree.map_structure(
+                lambda t: AllGather.apply(t, self.slice_rank, self.slice_size, self.slice_group), out)
+        self._check_batch(out, "outputs")
+        return out

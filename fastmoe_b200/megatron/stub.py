@@ -197,3 +197,6 @@ def uninstall():
     for name in ("megatron", "megatron.mpu", "megatron.checkpointing", "megatron.utils"):
         sys.modules.pop(name, None)
     _state.clear()
+    # process groups derived from the stand-in's arguments are rebuilt on the next install
+    from . import distributed as _distributed
+    _distributed._registry.reset()  # pylint: disable=protected-access
