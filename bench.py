@@ -11,9 +11,12 @@ N > 1, and a fused Adam step on all parameters.  Weak scaling: per-GPU work is f
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N ...                 # N > 1
 
-Timing: after W warm-up steps, every step is bracketed by CUDA events on the launching stream;
-an L2 flush (a 256 MiB fill) runs between steps outside the events; the K per-step times are
-summed per rank and the maximum over ranks is reported.  The end-to-end number re-runs the K
+Timing: the GPU is first brought to its working clocks by one second of bf16 matrix products
+(both arms alike, not steps of the model), then exactly W warm-up steps run (W >= 3), then every
+one of the K timed steps is bracketed by CUDA events on the launching stream; an L2 flush (a
+256 MiB fill) runs between steps outside the events; the K per-step times are summed per rank
+and the maximum over ranks is reported.  SM clocks and throttle reasons are sampled with
+nvidia-smi from the pre-heat to the end of the end-to-end region.  The end-to-end number re-runs the K
 steps through the same public call with, per step, a host-to-device copy of the inputs from
 pinned memory and a device-to-host read of the loss inside the timed region.
 """
@@ -26,6 +29,7 @@ import sys
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
+PREHEAT_S = 1.0
 
 METRIC = "moe_fwd_bwd_tokens_per_s"
 
@@ -58,6 +62,18 @@ def skew_gate(layer, world):
             layer.gate.gate.bias.copy_(bias)
 
 
+def kept_slot_fraction(layer, x):
+    r"""Share of the top-k slots of one batch that survive the gate's capacity limit (1.0 for
+    gates that drop nothing).  Run once, outside every timed region."""
+    import torch
+    try:
+        with torch.no_grad():
+            idx = layer.gate(x)[0]
+        return float((idx >= 0).float().mean())
+    except Exception:  # pylint: disable=broad-except
+        return 1.0
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -88,7 +104,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -257,26 +273,32 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # Clock ramp: one second of dense bf16 products, the same for both arms; not model steps.
+    heat_a = torch.randn(4096, 4096, device=device, dtype=torch.bfloat16)
+    heat_b = torch.randn(4096, 4096, device=device, dtype=torch.bfloat16)
+    t_heat = time.perf_counter()
+    while time.perf_counter() - t_heat < PREHEAT_S:
+        for _ in range(20):
+            heat_a @ heat_b
+        torch.cuda.synchronize()
+    del heat_a, heat_b
+
+    warm_steps = max(args.warmup, 3)
     try:
-        # At least W warm-up steps, and at least ~1 s of them so that clocks have ramped up.
-        warm_done = 0
-        t_warm = time.perf_counter()
-        while warm_done < max(args.warmup, 3) or time.perf_counter() - t_warm < 1.0:
-            step(dev_inputs[warm_done % n_inputs])
-            warm_done += 1
-            if warm_done % 8 == 0:
-                torch.cuda.synchronize()
+        for i in range(warm_steps):
+            step(dev_inputs[i % n_inputs])
         barrier()
     except Exception as exc:  # pylint: disable=broad-except
+        if rank == 0:
+            sampler.stop()
         if args.impl == "reference":
             if rank == 0:
                 emit({"impl": "reference", "unavailable": "reference step failed: %r" % (exc,)})
             return
         raise
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
 
     # ------------------------------------------------ device-timed region (inputs resident)
     launches_before = launch_counter()
@@ -292,7 +314,23 @@ def main():
     launches = launch_counter() - launches_before
     if graphed:
         launches = launches_per_step * args.steps
-    dev_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    dev_ms = sum(step_ms)
+
+    # The same K steps without the CUDA graph (this framework only; extra key, not the headline).
+    eager_ms = None
+    if graphed:
+        for i in range(3):
+            eager_step(dev_inputs[i % n_inputs])
+        barrier()
+        eager_ms = 0.0
+        for i in range(args.steps):
+            flush.fill_(float(i))
+            starts[i].record()
+            eager_step(dev_inputs[i % n_inputs])
+            ends[i].record()
+        barrier()
+        eager_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
 
     # ------------------------------------------------ end-to-end region (H2D inputs, D2H loss)
     # One timed region around all K steps.  Inside it, every step: the pinned host batch is
@@ -352,20 +390,29 @@ def main():
 
     clocks = sampler.stop() if rank == 0 else None
 
-    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=device)
+    kept = kept_slot_fraction(layer, dev_inputs[0])
+    times = torch.tensor([dev_ms, e2e_ms, eager_ms or 0.0, max(step_ms), -min(step_ms)],
+                         dtype=torch.float64, device=device)
+    sums = torch.tensor([kept], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = float(times[0]), float(times[1])
+        dist.all_reduce(sums)
+    dev_ms, e2e_ms, eager_max = float(times[0]), float(times[1]), float(times[2])
+    step_max, step_min = float(times[3]), -float(times[4])
+    kept = float(sums[0]) / world
 
     if rank == 0:
         tokens = TOKENS_PER_GPU * world * args.steps
         value = tokens / (dev_ms / 1e3)
         e2e_value = tokens / (e2e_ms / 1e3)
-        flops_per_step = 3 * 2 * 2 * TOKENS_PER_GPU * TOP_K * D_MODEL * D_HIDDEN * world
+        # Slots a capacity limit dropped do no work in the expert GEMMs: count the kept ones.
+        flops_per_step = 3 * 2 * 2 * TOKENS_PER_GPU * TOP_K * kept * D_MODEL * D_HIDDEN * world
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": warm_done,
-            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "steps": args.steps, "warmup": warm_steps,
+            "ms_per_step": dev_ms / args.steps, "ms_per_step_min": step_min,
+            "ms_per_step_median": statistics.median(step_ms), "ms_per_step_max": step_max,
+            "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1) inputs, random-init weights",
             "impl": args.impl,
             "tflops": flops_per_step / (dev_ms / args.steps / 1e3) / 1e12,
@@ -375,12 +422,18 @@ def main():
                 "seq_len": 1, "d_model": D_MODEL, "d_hidden": D_HIDDEN,
                 "experts_per_gpu": EXPERTS_PER_GPU, "top_k": TOP_K,
                 "parallelism": "ep%d" % world,
-                "step": "fwd+bwd+gate-grad-allreduce+fused-adam"
-                        + (" (all-reduce on a side stream, overlapped with the Adam update of the"
-                           " expert parameters; same Adam, two optimizer objects)" if overlap else ""),
-                "cuda_graph": bool(graphed),
+                "step": "fwd+bwd+gate-grad-allreduce+fused-adam",
                 "l2": "flushed between timed steps (256 MiB fill outside the per-step events; "
                       "in the end-to-end region a 160 MiB fill per step inside the region)",
+            },
+            "kept_slot_fraction": kept,
+            "execution": {
+                "cuda_graph": bool(graphed),
+                "allreduce_overlap": ("gate-gradient all-reduce on a side stream, overlapped with the"
+                                      " Adam update of the expert parameters (same Adam, two optimizer"
+                                      " objects)") if overlap else "none",
+                "preheat": "%.1f s of bf16 matrix products before the warm-up steps" % PREHEAT_S,
+                "eager_ms_per_step": (eager_max / args.steps) if graphed else None,
             },
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s",
