@@ -125,6 +125,27 @@ def recv_capacity_factor():
     return float_from_env("FMOE_RECV_CAPACITY_FACTOR", 0.0)
 
 
+def force_ep_path():
+    r"""``FMOE_FORCE_EP=1``: layers with ``world_size == 1`` inside an initialised one-rank NCCL
+    group take the expert-parallel kernels (sender CTAs, arrival flags, return push) instead of
+    the single-GPU path.  Every peer table then points at the GPU itself; used to test and
+    profile the multi-GPU code on one GPU."""
+    return switch_from_env("FMOE_FORCE_EP", False)
+
+
+def max_tokens():
+    r"""``FMOE_MAX_TOKENS``: tokens per rank the exchange buffers of the fused expert-parallel
+    path are sized for.  ``0`` (default): the ranks agree on the largest batch of the first call."""
+    return int_from_env("FMOE_MAX_TOKENS", 0)
+
+
+def send_ctas():
+    r"""``FMOE_SEND_CTAS``: CTAs of the first expert GEMM launch that act as row senders of the
+    dispatch instead of computing tiles (default 16: about what saturates NVLink with bulk
+    copies; the other 132 SMs compute)."""
+    return max(1, int_from_env("FMOE_SEND_CTAS", 16))
+
+
 def push_before_wgrad():
     r"""``FMOE_PUSH_BEFORE_WGRAD`` (default off): in the fused expert-parallel backward, queue the
     input-gradient GEMM whose epilogue returns rows to their sources before the two weight

@@ -90,7 +90,7 @@ int num_sms(int device) {
 }
 
 // ------------------------------------------------------------------------------ routing
-std::vector<torch::Tensor> route(torch::Tensor idx, int64_t tot, bool want_offs) {
+std::vector<torch::Tensor> route(torch::Tensor idx, int64_t tot, bool want_offs, bool want_pos = false) {
   check_cuda_contig(idx, "idx");
   TORCH_CHECK(idx.scalar_type() == torch::kLong, "idx must be int64");
   c10::cuda::CUDAGuard guard(idx.device());
@@ -100,13 +100,20 @@ std::vector<torch::Tensor> route(torch::Tensor idx, int64_t tot, bool want_offs)
   auto rank = torch::empty({n_slots}, opt);
   torch::Tensor offs;
   int* offs_ptr = nullptr;
-  if (want_offs) {
+  if (want_offs || want_pos) {
     offs = torch::empty({tot + 1}, opt);
     offs_ptr = offs.data_ptr<int>();
   }
+  torch::Tensor pos;
+  int* pos_ptr = nullptr;
+  if (want_pos) {
+    pos = torch::empty({n_slots > 0 ? n_slots : 1}, opt);
+    pos_ptr = pos.data_ptr<int>();
+  }
   FMOE_CUDA_CHECK(fmoe::launch_route(idx.data_ptr<int64_t>(), n_slots, static_cast<int>(tot),
                                      counts.data_ptr<int>(), rank.data_ptr<int>(), offs_ptr,
-                                     cur_stream()));
+                                     pos_ptr, cur_stream()));
+  if (want_pos) return {counts, rank, offs, pos};
   if (want_offs) return {counts, rank, offs};
   return {counts, rank};
 }
@@ -451,6 +458,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   // device-count-driven API
   m.def("route", [](torch::Tensor idx, int64_t tot) { return route(idx, tot, false); });
   m.def("route_offs", [](torch::Tensor idx, int64_t tot) { return route(idx, tot, true); });
+  // counts, rank, offs and pos (slot ids sorted by expert then rank: the send order of the
+  // fused dispatch)
+  m.def("route_pos", [](torch::Tensor idx, int64_t tot) { return route(idx, tot, true, true); });
   m.def("grouped_gemm", &grouped_gemm, py::arg("mode"), py::arg("a"), py::arg("b"), py::arg("offs"),
         py::arg("out"), py::arg("bias") = py::none(), py::arg("pre_out") = py::none(),
         py::arg("aux") = py::none(), py::arg("act") = 0, py::arg("epi") = 0,

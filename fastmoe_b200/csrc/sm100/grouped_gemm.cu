@@ -94,6 +94,20 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a) {
   kp.push_counter = a.push_counter;
   kp.push_me = a.push_me;
   kp.push_world = a.push_world;
+  kp.push_slots = a.push_slots;
+  kp.send = a.send;
+  kp.gate = a.gate;
+  if (a.mode == kWgrad) {
+    kp.send.n_ctas = 0;
+    kp.gate.flags = nullptr;
+  }
+  if (kp.send.n_ctas > 0) {
+    // the sender's item table and row pieces
+    if (kp.send.world * kp.send.n_expert > gg::SEND_MAX_TOT || (kp.send.d * 2) % 16 != 0 ||
+        kp.send.n_ctas >= (a.num_sms > 0 ? a.num_sms : 148)) {
+      return cudaErrorInvalidValue;
+    }
+  }
 
   const int grid = a.num_sms > 0 ? a.num_sms : 148;
   return a.dtype == kBF16 ? gg::launch_bf16(a.mode, ta, tb, kp, grid, a.stream)

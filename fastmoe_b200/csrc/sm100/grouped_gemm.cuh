@@ -26,6 +26,44 @@ enum EpiKind : int {
 
 enum DType : int { kBF16 = 0, kF16 = 1 };
 
+// Row dispatch fused into a row-mode GEMM launch (optional).  The first `n_ctas` CTAs of the grid
+// do no tensor-core work: they walk this rank's slots in destination order and copy every token
+// row (optionally scaled) into the owning peer's receive buffer with bulk asynchronous stores,
+// then publish one flag word per (128-row block of the receiver, source rank).  The remaining
+// CTAs run the GEMM and gate every tile on the flags of its row block (`GateArgs`), so the
+// transfer overlaps the math tile by tile.
+struct SendArgs {
+  int n_ctas = 0;                 // 0 = no sender CTAs in this launch
+  int dtype_bytes = 2;
+  const void* x = nullptr;        // [n_tokens, d] rows to send (row s / k serves slot s)
+  const int* pos = nullptr;       // [n_slots] slot ids sorted by (global expert, rank in expert)
+  const int* my_offs = nullptr;   // [tot + 1] exclusive prefix of this rank's per-expert slot counts
+  const int* dst_base = nullptr;  // [tot] first destination row of my rows, per global expert
+  const int* seg_base = nullptr;  // [tot] first row of the expert's whole segment on its owner
+  const int* blk_base = nullptr;  // [tot] index of the expert's first 128-row block on its owner
+  const void* scale = nullptr;    // optional [n_slots]: row s is multiplied by scale[s]
+  PeerPtrs rows = {};             // every peer's receive buffer [capacity, d]
+  PeerPtrs meta = {};             // every peer's int64 [capacity] (source rank << 32 | slot); entries may be null
+  PeerPtrs flags = {};            // every peer's int32 [blocks][kMaxPeers] arrival flags
+  const int* epoch = nullptr;     // value to publish
+  int n_expert = 0;
+  int world = 1;
+  int me = 0;
+  int k = 1;
+  int d = 0;
+  int capacity = 0;
+};
+
+// Arrival gating of a row-mode GEMM whose A operand is being filled by the peers' sender CTAs.
+struct GateArgs {
+  const int* flags = nullptr;     // local int32 [blocks][kMaxPeers]; null = not gated
+  const int* seg_off = nullptr;   // [num_groups][world + 1] row where the rows of the j-th source begin
+  const int* epoch = nullptr;
+  int world = 1;
+  int me = 0;
+  unsigned long long timeout_ns = 0;
+};
+
 struct GroupedGemmArgs {
   int mode = kRowsNT;
   int dtype = kBF16;
@@ -64,6 +102,9 @@ struct GroupedGemmArgs {
   int* push_counter = nullptr;   // zero-initialised word in local memory (CTA completion count)
   int push_me = 0;
   int push_world = 0;
+  long push_slots = 0;           // rows of every return buffer: rows whose meta names a slot beyond it are skipped
+  SendArgs send;
+  GateArgs gate;
   int num_sms = 148;
   cudaStream_t stream = nullptr;
 };

@@ -6,20 +6,30 @@
 // bias, activation, activation-derivative and dtype conversion into its epilogue.
 //
 // Structure of a CTA (384 threads = 3 warpgroups, one CTA per SM, persistent over tiles):
-//   warp 0      TMA producer: cp.async.bulk.tensor (no multicast) into a 4-stage ring of
-//               128-byte-swizzled shared-memory tiles, completion on mbarriers;
+//   warp 0      TMA producer: plain cp.async.bulk.tensor loads into a ring of 128-byte-swizzled
+//               shared-memory tiles (3 stages in the row modes, 4 in the weight-gradient
+//               mode), completion on mbarriers;
 //   warp 1      one elected thread issues tcgen05.mma (128 x 256 x 16 per instruction, fp32
 //               accumulators in TMEM) and tcgen05.commit; the warp owns the TMEM allocation;
 //   warps 2-3   idle (they complete the first warpgroup);
-//   warps 4-11  epilogue (two warpgroups): two warps per
-//               TMEM lane quarter, taking alternate 32-column chunks
-//               of the 256 accumulator columns; the tcgen05.ld of chunk i+1 and the cp.async
-//               staging of the side operand (saved pre-activation) for chunk i+1 are in
-//               flight while chunk i gets bias / activation / derivative and leaves as 32-byte
-//               stores.  The side operand is fetched with coalesced 64-byte row segments
-//               into a per-warp shared-memory patch and read back one row per lane.
+//   warps 4-11  epilogue (two warpgroups): two warps per TMEM lane quarter.  Row modes: each
+//               warp owns 32 rows x 128 columns of the tile; the tcgen05.ld of chunk i+1 and
+//               the cp.async staging of the side operand (saved pre-activation) for chunk
+//               i+1 are in flight while chunk i gets bias / activation / derivative and is
+//               written into the lane's row of a per-warp shared-memory patch; every lane
+//               then sends its row piece (128 or 256 contiguous bytes) to global memory with
+//               one bulk asynchronous store, local or into a peer's return buffer over NVLink,
+//               and does not wait for it.  Weight-gradient mode: alternate 32-column chunks,
+//               32-byte stores.
 // Two 256-column accumulators (all 512 TMEM columns) let the epilogue of tile i overlap the
 // main loop of tile i+1.
+//
+// Optional roles of a row-mode launch (expert parallelism):
+//   * sender CTAs (the first `send.n_ctas` CTAs): no tensor-core work; they copy this rank's
+//     token rows into the owning peers' receive buffers with bulk copies through shared
+//     memory and publish per-(row block, source) arrival flags;
+//   * gated producer: the TMA warp waits (bounded) for the arrival flags of a tile's row
+//     block before loading it, so GEMM tiles start as their rows land.
 //
 // The weight-gradient mode reduces over token rows, so both operands are MN-major; the last
 // K block of an expert is ragged, and the producer warp zeroes the rows past the segment end
@@ -44,7 +54,9 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
+constexpr int STAGES = 4;        // ring slots the barrier arrays are sized for
+constexpr int STAGES_ROWS = 3;   // row modes: 3 x 48 KB, the rest of shared memory holds the store patches
+constexpr int STAGES_WGRAD = 4;
 constexpr int A_BYTES = BM * BK * 2;      // 16 KB
 constexpr int B_BYTES = BN * BK * 2;      // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -58,12 +70,24 @@ constexpr int NUM_THREADS = (FIRST_EPI_WARP + NUM_EPI_WARPS) * 32;
 
 constexpr int CHUNKS_PER_WARP = BN / 32 / 2;  // 4 chunks of 32 columns per epilogue warp
 constexpr int SIDE_PITCH = 80;                // bytes per staged row (64 data + 16 pad: no bank conflicts)
-constexpr int SIDE_BYTES = 32 * SIDE_PITCH;   // one 32-row x 32-column patch per epilogue warp
+constexpr int SIDE_BYTES = 32 * SIDE_PITCH;   // weight-gradient mode: one 32-row x 32-column patch per epilogue warp
+constexpr int PATCH_PITCH = 272;              // row modes: 256 bytes of a row piece + 16 pad (16-byte lanes spread over all banks)
+constexpr int PATCH_BYTES = 32 * PATCH_PITCH; // 32 rows x 128 columns per epilogue warp
 constexpr int TMEM_COLS = 512;
+
+// Sender CTAs: every warp owns a ring of SEND_SLOTS pieces of at most SEND_PIECE bytes.
+constexpr int SEND_PIECE = 2048;
+constexpr int SEND_SLOTS = 6;
+constexpr int SEND_AHEAD = 3;                 // loads in flight ahead of the piece being stored
+constexpr int SEND_DONE_RING = 2048;          // completion counters of the items a CTA has in flight
+constexpr int SEND_MAX_TOT = 4096;            // global experts the item table holds
+constexpr int NUM_WARPS = FIRST_EPI_WARP + NUM_EPI_WARPS;
 
 constexpr int STATUS_TIMEOUT_PRODUCER = 101;
 constexpr int STATUS_TIMEOUT_MMA = 102;
 constexpr int STATUS_TIMEOUT_EPILOGUE = 103;
+constexpr int STATUS_TIMEOUT_SENDER = 104;
+constexpr int STATUS_BAD_PUSH_META = 105;    // a row's (source, slot) word was out of range: row skipped
 
 struct SharedAux {
   uint64_t full[STAGES];
@@ -79,7 +103,26 @@ struct SharedAux {
 
 constexpr int AUX_BYTES = (static_cast<int>(sizeof(SharedAux)) + 127) & ~127;
 constexpr int BIAS_BYTES = CHUNKS_PER_WARP * 64;  // per epilogue warp: its four 32-column bias slices
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + NUM_EPI_WARPS * (SIDE_BYTES + BIAS_BYTES) + 1024;
+template <int MODE> struct Layout {
+  static constexpr int kStages = (MODE == kWgrad) ? STAGES_WGRAD : STAGES_ROWS;
+  static constexpr int kPatch = (MODE == kWgrad) ? SIDE_BYTES : PATCH_BYTES;
+  static constexpr int kAuxOff = kStages * STAGE_BYTES;
+  static constexpr int kEpiOff = kAuxOff + AUX_BYTES;
+  static constexpr int kBiasOff = kEpiOff + NUM_EPI_WARPS * kPatch;
+  static constexpr int kBytes = kBiasOff + NUM_EPI_WARPS * BIAS_BYTES + 1024;
+};
+static_assert(Layout<kRowsNT>::kBytes <= 232448 && Layout<kWgrad>::kBytes <= 232448, "shared memory");
+// What a sender CTA lays over the same dynamic shared memory.
+struct SenderShared {
+  uint64_t bar[NUM_WARPS][SEND_SLOTS];
+  int item_prefix[SEND_MAX_TOT + 1];
+  int partial[NUM_THREADS];
+  int done[SEND_DONE_RING];
+  int failed;
+};
+constexpr int SENDER_DATA_OFF = (static_cast<int>(sizeof(SenderShared)) + 1023) & ~1023;
+static_assert(SENDER_DATA_OFF + NUM_WARPS * SEND_SLOTS * SEND_PIECE + 1024 <= Layout<kRowsNT>::kBytes,
+              "sender rings must fit into the row-mode launch");
 
 struct KernelParams {
   int num_groups;
@@ -105,6 +148,9 @@ struct KernelParams {
   int* push_counter;
   int push_me;
   int push_world;
+  long push_slots;
+  SendArgs send;
+  GateArgs gate;
 };
 
 struct TileCoord {
@@ -253,6 +299,7 @@ struct Packed32 {
 // Stage a 32-row x 64-byte patch of a row-major 16-bit matrix into shared memory with
 // coalesced 16-byte cp.async copies: per instruction 4 lanes cover one row, 8 rows per
 // instruction.  Rows >= valid_rows are zero-filled without touching global memory.
+template <int PITCH = SIDE_PITCH>
 __device__ __forceinline__ void stage_side(uint8_t* patch, const uint8_t* gbase, long row_pitch,
                                            int valid_rows, int lane) {
   const int seg = lane & 3;
@@ -261,7 +308,7 @@ __device__ __forceinline__ void stage_side(uint8_t* patch, const uint8_t* gbase,
     const int rr = i * 8 + (lane >> 2);
     const bool ok = rr < valid_rows;
     const uint8_t* src = gbase + (ok ? rr : 0) * row_pitch + seg * 16;
-    const uint32_t dst = ptx::smem_u32(patch + rr * SIDE_PITCH + seg * 16);
+    const uint32_t dst = ptx::smem_u32(patch + rr * PITCH + seg * 16);
     const uint32_t bytes = ok ? 16u : 0u;
     asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
                  "r"(bytes)
@@ -270,10 +317,11 @@ __device__ __forceinline__ void stage_side(uint8_t* patch, const uint8_t* gbase,
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+template <int PITCH = SIDE_PITCH>
 __device__ __forceinline__ void read_side(const uint8_t* patch, int lane, Packed32& d) {
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncwarp();
-  const uint4* row = reinterpret_cast<const uint4*>(patch + lane * SIDE_PITCH);
+  const uint4* row = reinterpret_cast<const uint4*>(patch + lane * PITCH);
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     const uint4 w = row[q];
@@ -372,72 +420,6 @@ __device__ __forceinline__ void finish_chunk(const KernelParams& p, const EpiTil
         st256(reinterpret_cast<uint8_t*>(static_cast<T*>(p.out) + off) + q * 32, w);
       }
     }
-  } else if (et.use_aux) {
-#pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      uint32_t w[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float sa, sb;
-        Cvt<T>::unpack(side_cur.w[q * 8 + j], sa, sb);
-        const float a = __uint_as_float(r[q * 16 + 2 * j]) * act_grad<ACT>(sa);
-        const float b = __uint_as_float(r[q * 16 + 2 * j + 1]) * act_grad<ACT>(sb);
-        w[j] = Cvt<T>::pack(a, b);
-      }
-      st256(et.out_row_base + col0 * 2 + q * 32, w);
-    }
-  } else {
-    const uint8_t* bias = et.bias_sm == nullptr ? nullptr : et.bias_sm + ch * 64;
-#pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      uint32_t bw[8];
-      if (bias != nullptr) {
-        const uint4 b0 = *reinterpret_cast<const uint4*>(bias + q * 32);
-        const uint4 b1 = *reinterpret_cast<const uint4*>(bias + q * 32 + 16);
-        bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w;
-        bw[4] = b1.x; bw[5] = b1.y; bw[6] = b1.z; bw[7] = b1.w;
-      }
-      uint32_t wp[8], wo[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float a = __uint_as_float(r[q * 16 + 2 * j]);
-        float b = __uint_as_float(r[q * 16 + 2 * j + 1]);
-        if (bias != nullptr) {
-          float ba, bb;
-          Cvt<T>::unpack(bw[j], ba, bb);
-          a += ba;
-          b += bb;
-        }
-        if (ACT != kActNone) {
-          wp[j] = Cvt<T>::pack(a, b);
-          a = act_fwd<ACT>(a);
-          b = act_fwd<ACT>(b);
-        }
-        wo[j] = Cvt<T>::pack(a, b);
-      }
-      if (ACT != kActNone && p.pre_out != nullptr) {
-        st256(reinterpret_cast<uint8_t*>(static_cast<T*>(p.pre_out) + off) + q * 32, wp);
-      }
-      if (et.remote_row) {
-        // Rows bound for a peer are staged in this lane's 64-byte slot of the warp's patch and
-        // leave as one bulk asynchronous store per chunk: NVLink sees 64-byte writes instead
-        // of scattered 32-byte ones, and the warp does not wait for them.
-        uint8_t* slot = et.patch + et.lane * SIDE_PITCH + q * 32;
-        if (q == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        *reinterpret_cast<uint4*>(slot) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
-        *reinterpret_cast<uint4*>(slot + 16) = make_uint4(wo[4], wo[5], wo[6], wo[7]);
-        if (q == 1) {
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 64;" ::"l"(
-                           et.out_row_base + col0 * 2),
-                       "r"(ptx::smem_u32(et.patch + et.lane * SIDE_PITCH))
-                       : "memory");
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        }
-      } else {
-        st256(et.out_row_base + col0 * 2 + q * 32, wo);
-      }
-    }
   }
 }
 
@@ -500,6 +482,474 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, const EpiTi
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Row modes: epilogue through a shared-memory patch and bulk asynchronous stores.
+// ------------------------------------------------------------------------------------------
+struct RowTile {
+  uint32_t t_row;          // TMEM address: this warp's lane quarter, first column of its span
+  int lane;
+  int col_first;           // first output column of this warp's 128-column span
+  int n_chunks;            // valid 32-column chunks of the span (0..4)
+  int warp_valid;          // valid rows of this warp (0..32)
+  bool row_ok;
+  bool use_aux;            // multiply by the activation derivative of the staged side operand
+  const uint8_t* side;     // side operand at (first row of the warp, col_first)
+  long side_pitch;
+  uint8_t* patch;          // this warp's 32 x PATCH_PITCH bytes
+  uint8_t* out_row;        // column 0 of this lane's output row (local or a peer's); null = no store
+  uint8_t* pre_row;        // column 0 of this lane's pre-activation row, or null
+  const uint8_t* bias_sm;  // 4 x 64 bytes of bias for the span, or null
+  uint64_t* empty_bar;
+};
+
+// Bias / activation (or activation derivative) of one 32-column chunk; the results go into
+// the lane's own row of the patch.
+template <typename T, int ACT>
+__device__ __forceinline__ void rows_chunk(const RowTile& rt, int i, bool with_pre,
+                                           const uint32_t (&r)[32], const Packed32& side_cur) {
+  uint8_t* my = rt.patch + rt.lane * PATCH_PITCH;
+  uint8_t* dst = my + (with_pre ? (i & 1) : i) * 64;
+  if (rt.use_aux) {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      uint32_t w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float sa, sb;
+        Cvt<T>::unpack(side_cur.w[q * 8 + j], sa, sb);
+        const float a = __uint_as_float(r[q * 16 + 2 * j]) * act_grad<ACT>(sa);
+        const float b = __uint_as_float(r[q * 16 + 2 * j + 1]) * act_grad<ACT>(sb);
+        w[j] = Cvt<T>::pack(a, b);
+      }
+      *reinterpret_cast<uint4*>(dst + q * 32) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(dst + q * 32 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    return;
+  }
+  const uint8_t* bias = rt.bias_sm == nullptr ? nullptr : rt.bias_sm + i * 64;
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    uint32_t bw[8];
+    if (bias != nullptr) {
+      const uint4 b0 = *reinterpret_cast<const uint4*>(bias + q * 32);
+      const uint4 b1 = *reinterpret_cast<const uint4*>(bias + q * 32 + 16);
+      bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w;
+      bw[4] = b1.x; bw[5] = b1.y; bw[6] = b1.z; bw[7] = b1.w;
+    }
+    uint32_t wp[8], wo[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float a = __uint_as_float(r[q * 16 + 2 * j]);
+      float b = __uint_as_float(r[q * 16 + 2 * j + 1]);
+      if (bias != nullptr) {
+        float ba, bb;
+        Cvt<T>::unpack(bw[j], ba, bb);
+        a += ba;
+        b += bb;
+      }
+      if (ACT != kActNone) {
+        wp[j] = Cvt<T>::pack(a, b);
+        a = act_fwd<ACT>(a);
+        b = act_fwd<ACT>(b);
+      }
+      wo[j] = Cvt<T>::pack(a, b);
+    }
+    if (ACT != kActNone && with_pre) {
+      uint8_t* pd = my + 128 + (i & 1) * 64 + q * 32;
+      *reinterpret_cast<uint4*>(pd) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+      *reinterpret_cast<uint4*>(pd + 16) = make_uint4(wp[4], wp[5], wp[6], wp[7]);
+    }
+    *reinterpret_cast<uint4*>(dst + q * 32) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    *reinterpret_cast<uint4*>(dst + q * 32 + 16) = make_uint4(wo[4], wo[5], wo[6], wo[7]);
+  }
+}
+
+// After chunk i has been written: send what is complete.  Without a pre-activation output the
+// whole span (up to 256 bytes per row) leaves once, after the last chunk; with one, the patch
+// row holds a pair of output chunks and the pair of pre-activation chunks, and both leave
+// after every second chunk (128 bytes each).
+__device__ __forceinline__ void rows_send(const RowTile& rt, int i, bool with_pre) {
+  const bool last = i + 1 == rt.n_chunks;
+  if (with_pre) {
+    if (!(last || (i & 1))) return;
+    if (rt.row_ok && rt.out_row != nullptr) {
+      uint8_t* my = rt.patch + rt.lane * PATCH_PITCH;
+      const uint32_t bytes = ((i & 1) + 1) * 64;
+      const long col = rt.col_first + (i & ~1) * 32;
+      ptx::fence_proxy_async_smem();
+      ptx::bulk_store(rt.out_row + col * 2, my, bytes);
+      ptx::bulk_store(rt.pre_row + col * 2, my + 128, bytes);
+      ptx::bulk_commit();
+    }
+  } else if (last) {
+    if (rt.row_ok && rt.out_row != nullptr) {
+      uint8_t* my = rt.patch + rt.lane * PATCH_PITCH;
+      ptx::fence_proxy_async_smem();
+      ptx::bulk_store(rt.out_row + static_cast<long>(rt.col_first) * 2, my, rt.n_chunks * 64);
+      ptx::bulk_commit();
+    }
+  }
+}
+
+// One output tile for one epilogue warp in the row modes: 32 rows x up to four contiguous
+// 32-column chunks.  Two register buffers alternate: while chunk i is finished, the tcgen05.ld
+// of chunk i + 1 and the staging of its side operand are in flight.
+template <typename T, int ACT>
+__device__ __forceinline__ void epilogue_tile_rows(const RowTile& rt) {
+  const int lane = rt.lane;
+  const bool with_pre = (ACT != kActNone) && !rt.use_aux && rt.pre_row != nullptr;
+  uint32_t ra[32], rb[32];
+  bool released = false;
+  if (rt.n_chunks > 0) {
+    ptx::tmem_ld_32x32(rt.t_row, ra);
+#pragma unroll 1
+    for (int pair = 0; pair < CHUNKS_PER_WARP / 2; ++pair) {
+      {
+        const int i = 2 * pair;
+        if (i >= rt.n_chunks) break;
+        ptx::tmem_ld_wait();
+        Packed32 side_cur;
+        if (rt.use_aux) read_side<PATCH_PITCH>(rt.patch + i * 64, lane, side_cur);
+        if (i + 1 < rt.n_chunks) {
+          ptx::tmem_ld_32x32(rt.t_row + (i + 1) * 32, rb);
+          if (rt.use_aux) {
+            stage_side<PATCH_PITCH>(rt.patch + (i + 1) * 64, rt.side + (i + 1) * 64, rt.side_pitch,
+                                    rt.warp_valid, lane);
+          }
+        } else if (!released) {
+          ptx::tc_fence_before_sync();
+          ptx::mbar_arrive(rt.empty_bar);
+          released = true;
+        }
+        // with a pre-activation output the second pair reuses the bytes of the first
+        if (with_pre && i > 0) ptx::bulk_wait_read<0>();
+        if (rt.row_ok) rows_chunk<T, ACT>(rt, i, with_pre, ra, side_cur);
+        rows_send(rt, i, with_pre);
+      }
+      {
+        const int i = 2 * pair + 1;
+        if (i >= rt.n_chunks) break;
+        ptx::tmem_ld_wait();
+        Packed32 side_cur;
+        if (rt.use_aux) read_side<PATCH_PITCH>(rt.patch + i * 64, lane, side_cur);
+        if (i + 1 < rt.n_chunks) {
+          ptx::tmem_ld_32x32(rt.t_row + (i + 1) * 32, ra);
+          if (rt.use_aux) {
+            stage_side<PATCH_PITCH>(rt.patch + (i + 1) * 64, rt.side + (i + 1) * 64, rt.side_pitch,
+                                    rt.warp_valid, lane);
+          }
+        } else if (!released) {
+          ptx::tc_fence_before_sync();
+          ptx::mbar_arrive(rt.empty_bar);
+          released = true;
+        }
+        if (rt.row_ok) rows_chunk<T, ACT>(rt, i, with_pre, rb, side_cur);
+        rows_send(rt, i, with_pre);
+      }
+    }
+  }
+  if (!released) {
+    ptx::tc_fence_before_sync();
+    ptx::mbar_arrive(rt.empty_bar);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------
+// Sender CTAs: the dispatch direction of the exchange inside a GEMM launch.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ int ld_acquire_sys_i32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_i32(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// One unit of sender work: the part of one 128-row block of a peer's expert segment that this
+// rank's rows fill.  Rows are relative to the first row of the expert's segment on the owner.
+struct SendItem {
+  int g;        // global expert
+  int peer;
+  int blk;      // block index inside the peer's flag array
+  int r_lo;     // rows [r_lo, r_hi) of the segment
+  int r_hi;
+  int rel0;     // segment row of this rank's first row for the expert
+  long seg;     // first row of the segment in the peer's receive buffer
+  int src0;     // index into `pos` of this rank's first slot of the expert
+};
+
+// Send order: local expert e outer, peer distance j inner (j = 0 is this rank itself), so
+// that every receiver gets the rows of its first experts first, from all sources at once.
+__device__ __forceinline__ int send_order_expert(const SendArgs& s, int q) {
+  const int e = q / s.world;
+  const int j = q - e * s.world;
+  int peer = s.me + j;
+  if (peer >= s.world) peer -= s.world;
+  return peer * s.n_expert + e;
+}
+
+// Rows [rel0, r_end) of the segment of global expert g are mine (clamped to the receive
+// capacity); returns the number of 128-row blocks they touch.
+__device__ __forceinline__ int send_items_of(const SendArgs& s, int g, int& rel0, int& r_end) {
+  const int cnt = s.my_offs[g + 1] - s.my_offs[g];
+  const int seg = s.seg_base[g];
+  rel0 = s.dst_base[g] - seg;
+  r_end = rel0 + cnt;
+  if (r_end > s.capacity - seg) r_end = s.capacity - seg;
+  if (cnt <= 0 || r_end <= rel0) return 0;
+  return (r_end - 1) / BM - rel0 / BM + 1;
+}
+
+__device__ __forceinline__ SendItem send_decode(const SendArgs& s, const SenderShared* sh, int tot,
+                                                int item) {
+  int lo = 0, hi = tot;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (sh->item_prefix[mid] <= item) lo = mid; else hi = mid;
+  }
+  SendItem it;
+  it.g = send_order_expert(s, lo);
+  it.peer = it.g / s.n_expert;
+  int rel0, r_end;
+  send_items_of(s, it.g, rel0, r_end);
+  const int b = rel0 / BM + (item - sh->item_prefix[lo]);
+  it.blk = s.blk_base[it.g] + b;
+  it.r_lo = max(rel0, b * BM);
+  it.r_hi = min(r_end, (b + 1) * BM);
+  it.rel0 = rel0;
+  it.seg = s.seg_base[it.g];
+  it.src0 = s.my_offs[it.g];
+  return it;
+}
+
+// Bounded wait on a load barrier of a sender ring slot.
+__device__ __forceinline__ bool send_wait(uint64_t* bar, uint32_t parity, const volatile int* failed) {
+  return ptx::mbar_wait(bar, parity, failed);
+}
+
+template <int N> struct BulkWaitUpTo {
+  static __device__ __forceinline__ void run(int n) {
+    if (n >= N) ptx::bulk_wait<N>(); else BulkWaitUpTo<N - 1>::run(n);
+  }
+};
+template <> struct BulkWaitUpTo<0> {
+  static __device__ __forceinline__ void run(int) { ptx::bulk_wait<0>(); }
+};
+
+template <typename T>
+__device__ void sender_cta(const KernelParams& p, uint8_t* smem) {
+  const SendArgs& s = p.send;
+  SenderShared* sh = reinterpret_cast<SenderShared*>(smem);
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int tot = s.world * s.n_expert;
+  uint8_t* ring = smem + SENDER_DATA_OFF + warp * (SEND_SLOTS * SEND_PIECE);
+
+  for (int i = tid; i < SEND_DONE_RING; i += NUM_THREADS) sh->done[i] = 0;
+  if (tid < NUM_WARPS * SEND_SLOTS) ptx::mbar_init(&sh->bar[tid / SEND_SLOTS][tid % SEND_SLOTS], 1);
+  if (tid == 0) {
+    sh->failed = 0;
+    sh->item_prefix[0] = 0;
+    ptx::fence_barrier_init();
+  }
+  // Item table: blocks per (expert, peer) in send order, then an exclusive prefix.
+  const int per = (tot + NUM_THREADS - 1) / NUM_THREADS;
+  const int q0 = min(tot, tid * per);
+  const int q1 = min(tot, q0 + per);
+  int mine = 0;
+  for (int q = q0; q < q1; ++q) {
+    int rel0, r_end;
+    const int n = send_items_of(s, send_order_expert(s, q), rel0, r_end);
+    sh->item_prefix[q + 1] = n;
+    mine += n;
+  }
+  sh->partial[tid] = mine;
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int t = 0; t < NUM_THREADS; ++t) {
+      const int v = sh->partial[t];
+      sh->partial[t] = run;
+      run += v;
+    }
+  }
+  __syncthreads();
+  {
+    int run = sh->partial[tid];
+    for (int q = q0; q < q1; ++q) {
+      run += sh->item_prefix[q + 1];
+      sh->item_prefix[q + 1] = run;
+    }
+  }
+  __syncthreads();
+  const int total_items = sh->item_prefix[tot];
+  const int epoch = *s.epoch;
+  const volatile int* failed = &sh->failed;
+  const int n_ctas = s.n_ctas;
+  const int row_bytes = s.d * 2;
+  const int pieces_per_row = (row_bytes + SEND_PIECE - 1) / SEND_PIECE;
+
+  // Two cursors over the same piece sequence of this warp: `ld` issues loads SEND_AHEAD pieces
+  // ahead of `st`, which waits for a piece, scales it and stores it to the peer.
+  struct Cursor {
+    int item;      // item index, stride n_ctas; >= total_items: exhausted
+    int seq;       // ordinal of the item within this CTA
+    int row;       // segment row; rows of a warp are r_lo + warp, + NUM_WARPS, ...
+    int pc;
+    SendItem it;
+  };
+  auto seek = [&](Cursor& c) {
+    // Moves to the first item at or after c.item with a row for this warp.
+    while (c.item < total_items) {
+      c.it = send_decode(s, sh, tot, c.item);
+      c.row = c.it.r_lo + warp;
+      c.pc = 0;
+      if (c.row < c.it.r_hi) return;
+      c.item += n_ctas;
+      ++c.seq;
+    }
+  };
+  auto advance = [&](Cursor& c) {
+    if (++c.pc < pieces_per_row) return;
+    c.pc = 0;
+    c.row += NUM_WARPS;
+    if (c.row < c.it.r_hi) return;
+    c.item += n_ctas;
+    ++c.seq;
+    seek(c);
+  };
+  auto issue_load = [&](const Cursor& c, int n) {
+    const int slot = n % SEND_SLOTS;
+    const int sl = s.pos[c.it.src0 + (c.row - c.it.rel0)];
+    const int off = c.pc * SEND_PIECE;
+    const uint32_t bytes = static_cast<uint32_t>(min(SEND_PIECE, row_bytes - off));
+    const uint8_t* src = static_cast<const uint8_t*>(s.x) + static_cast<long>(sl / s.k) * row_bytes + off;
+    uint64_t* bar = &sh->bar[warp][slot];
+    ptx::mbar_arrive_expect_tx(bar, bytes);
+    ptx::bulk_load(ring + slot * SEND_PIECE, src, bytes, bar);
+  };
+  // Publishes item `seq` of this CTA once every warp has seen its own stores of it complete.
+  auto signal_item = [&](int seq) {
+    ptx::fence_proxy_async_all();
+    __threadfence_system();
+    const int old = atomicAdd(&sh->done[seq % SEND_DONE_RING], 1);
+    if (old == NUM_WARPS - 1) {
+      sh->done[seq % SEND_DONE_RING] = 0;
+      __threadfence_system();
+      const SendItem it = send_decode(s, sh, tot, static_cast<int>(blockIdx.x) + seq * n_ctas);
+      int* flag = static_cast<int*>(s.flags.p[it.peer]) + static_cast<long>(it.blk) * kMaxPeers + s.me;
+      st_release_sys_i32(flag, epoch);
+    }
+  };
+
+  Cursor ld, st;
+  ld.item = static_cast<int>(blockIdx.x);
+  ld.seq = 0;
+  seek(ld);
+  st = ld;
+  int n_ld = 0, n_st = 0;       // pieces whose load / store has been issued
+  int closed = 0;               // items of this CTA this warp has closed (all its stores issued)
+  int groups_in_item = 0;       // store groups lane 0 issued for the item being filled
+  const int items_cta = total_items > static_cast<int>(blockIdx.x)
+                            ? (total_items - static_cast<int>(blockIdx.x) + n_ctas - 1) / n_ctas : 0;
+  bool ok = true;
+
+  // Closes items [closed, upto): item t is published one close later, when the stores of the
+  // following item have been issued and a bounded look-back wait proves those of t complete.
+  auto close_until = [&](int upto) {
+    while (closed < upto) {
+      if (lane == 0 && closed > 0 && *failed == 0) {
+        BulkWaitUpTo<SEND_SLOTS>::run(groups_in_item);
+        signal_item(closed - 1);
+      }
+      groups_in_item = 0;
+      ++closed;
+      if (closed % SEND_DONE_RING == 0) {
+        // the counter ring wraps: nobody may run ahead into slots that are still counting
+        asm volatile("bar.sync 3, %0;" ::"n"(NUM_THREADS) : "memory");
+      }
+    }
+  };
+
+  if (lane == 0) {
+    for (int a = 0; a < SEND_AHEAD && ld.item < total_items; ++a) {
+      issue_load(ld, n_ld++);
+      advance(ld);
+    }
+  }
+  while (st.item < total_items && ok) {
+    close_until(st.seq);
+    const int slot = n_st % SEND_SLOTS;
+    if (lane == 0 && ld.item < total_items) {
+      // the slot of the next load was last read by the store issued three pieces ago
+      ptx::bulk_wait_read<SEND_SLOTS - SEND_AHEAD - 1>();
+      issue_load(ld, n_ld++);
+      advance(ld);
+    }
+    const uint32_t parity = static_cast<uint32_t>(n_st / SEND_SLOTS) & 1u;
+    if (!send_wait(&sh->bar[warp][slot], parity, failed)) {
+      if (lane == 0) {
+        sh->failed = 1;
+        if (p.status != nullptr) atomicCAS(p.status, 0, STATUS_TIMEOUT_SENDER);
+      }
+      ok = false;
+      break;
+    }
+    const int sl = s.pos[st.it.src0 + (st.row - st.it.rel0)];
+    const int off = st.pc * SEND_PIECE;
+    const int bytes = min(SEND_PIECE, row_bytes - off);
+    uint8_t* piece = ring + slot * SEND_PIECE;
+    if (s.scale != nullptr) {
+      const float sc = Cvt<T>::to_f(static_cast<const T*>(s.scale)[sl]);
+      for (int o = lane * 16; o < bytes; o += 32 * 16) {
+        uint4 v = *reinterpret_cast<uint4*>(piece + o);
+        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float a, b;
+          Cvt<T>::unpack(w[j], a, b);
+          w[j] = Cvt<T>::pack(a * sc, b * sc);
+        }
+        *reinterpret_cast<uint4*>(piece + o) = v;
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+    }
+    if (lane == 0) {
+      const long drow = st.it.seg + st.row;
+      uint8_t* dst = static_cast<uint8_t*>(s.rows.p[st.it.peer]) + drow * row_bytes + off;
+      ptx::bulk_store(dst, piece, static_cast<uint32_t>(bytes));
+      ptx::bulk_commit();
+      if (st.pc == 0 && s.meta.p[st.it.peer] != nullptr) {
+        static_cast<int64_t*>(s.meta.p[st.it.peer])[drow] =
+            (static_cast<int64_t>(s.me) << 32) | static_cast<int64_t>(sl);
+      }
+    }
+    ++groups_in_item;
+    ++n_st;
+    advance(st);
+    __syncwarp();  // lanes stay within one phase of the ring barriers
+  }
+  // Every warp closes every item (also after a failure: the others may be waiting for it at
+  // the ring barrier); after a failure nothing more is published.
+  close_until(items_cta);
+  if (lane == 0) {
+    ptx::bulk_wait<0>();
+    if (items_cta > 0 && *failed == 0) signal_item(items_cta - 1);
+  }
+  // Loads that were issued but never consumed (only after a failure) must land before the
+  // shared memory goes away.
+  if (!ok) {
+    const unsigned long long t0 = ptx::globaltimer();
+    while (ptx::globaltimer() - t0 < 200000ull) __nanosleep(1000);
+  }
+  __syncthreads();
+}
+
 template <int MODE, typename T, int ACT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
@@ -508,14 +958,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  SharedAux* aux = reinterpret_cast<SharedAux*>(smem + STAGES * STAGE_BYTES);
+  using L = Layout<MODE>;
+  constexpr int kStages = L::kStages;
+
+  // Sender CTAs (row modes only) take no part in the GEMM.
+  const int n_send = (MODE == kWgrad) ? 0 : p.send.n_ctas;
+  if constexpr (MODE != kWgrad) {
+    if (static_cast<int>(blockIdx.x) < n_send) {
+      sender_cta<T>(p, smem);
+      return;
+    }
+  }
+  const int cta = static_cast<int>(blockIdx.x) - n_send;
+  const int num_ctas = static_cast<int>(gridDim.x) - n_send;
+  SharedAux* aux = reinterpret_cast<SharedAux*>(smem + L::kAuxOff);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   // ---------------------------------------------------------------- set-up
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(&aux->full[s], 1);
       ptx::mbar_init(&aux->empty[s], 1);
     }
@@ -553,6 +1016,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   const uint32_t tmem_base = aux->tmem_base;
   const int total_tiles = aux->total_tiles;
   const volatile int* abort_flag = &aux->abort;
+  // When tiles wait for rows from peers, the roles behind the producer must outlast the
+  // longest wait the producer may legitimately sit in.
+  const unsigned long long wait_limit =
+      ptx::kWaitLimitNs + ((MODE != kWgrad && p.gate.flags != nullptr) ? p.gate.timeout_ns : 0ull);
 
   if (warp == 0) {
     // ============================================================== TMA producer
@@ -560,10 +1027,60 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     uint32_t phase = 0;
     uint32_t tail_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    // Arrival gating (row modes under expert parallelism): lane j looks after the j-th source
+    // of a tile's row block.  The flag of the NEXT tile is read one tile ahead, so that in the
+    // steady state the value is already in a register when the tile starts.
+    const bool gated = (MODE != kWgrad) && p.gate.flags != nullptr;
+    const int gate_epoch = gated ? *p.gate.epoch : 0;
+    const int n_tiles_n = (p.n + BN - 1) / BN;
+    auto gate_flag = [&](int tile) -> const int* {
+      if (!gated || tile >= total_tiles || lane >= p.gate.world) return nullptr;
+      const TileCoord c = decode_tile<MODE>(p, aux, tile);
+      const int r0 = c.row_begin + c.m_tile * BM;
+      const int r1 = min(r0 + BM, c.row_end);
+      const int* so = p.gate.seg_off + c.group * (p.gate.world + 1) + lane;
+      if (!(so[0] < r1 && so[1] > r0)) return nullptr;
+      int src = p.gate.me - lane;
+      if (src < 0) src += p.gate.world;
+      const int blk = aux->tile_prefix[c.group] / n_tiles_n + c.m_tile;
+      return p.gate.flags + static_cast<long>(blk) * kMaxPeers + src;
+    };
+    const int* flag_next = gate_flag(cta);
+    int seen_next = flag_next != nullptr ? ld_acquire_sys_i32(flag_next) : gate_epoch;
+    for (int tile = cta; tile < total_tiles && ok; tile += num_ctas) {
       const TileCoord c = decode_tile<MODE>(p, aux, tile);
       const int rows = c.row_end - c.row_begin;
       const int num_kb = (MODE == kWgrad) ? (rows + BK - 1) / BK : p.k / BK;
+      if constexpr (MODE != kWgrad) {
+        if (gated) {
+          const int* flag = flag_next;
+          int seen = seen_next;
+          flag_next = gate_flag(tile + num_ctas);
+          seen_next = flag_next != nullptr ? ld_acquire_sys_i32(flag_next) : gate_epoch;
+          bool here = true;
+          if (flag != nullptr && seen - gate_epoch < 0) {
+            const unsigned long long t0 = ptx::globaltimer();
+            unsigned spins = 0;
+            while (true) {
+              if (ld_acquire_sys_i32(flag) - gate_epoch >= 0) break;
+              if ((++spins & 0x3f) == 0) {
+                if (*abort_flag != 0 || ptx::globaltimer() - t0 > p.gate.timeout_ns) {
+                  here = false;
+                  break;
+                }
+              }
+              __nanosleep(100);
+            }
+          }
+          if (!__all_sync(0xffffffffu, here)) {
+            if (lane == 0) fail(aux, p.status, STATUS_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          // the rows were written by other GPUs and are now read through the async proxy
+          ptx::fence_proxy_async_all();
+        }
+      }
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!ptx::mbar_wait(&aux->empty[stage], phase ^ 1, abort_flag)) {
           if (lane == 0) fail(aux, p.status, STATUS_TIMEOUT_PRODUCER);
@@ -623,7 +1140,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(&aux->full[stage]);
         }
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -636,20 +1153,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       uint32_t phase = 0;
       int iter = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+      for (int tile = cta; tile < total_tiles && ok; tile += num_ctas, ++iter) {
         const TileCoord c = decode_tile<MODE>(p, aux, tile);
         const int rows = c.row_end - c.row_begin;
         const int num_kb = (MODE == kWgrad) ? (rows + BK - 1) / BK : p.k / BK;
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
-        if (!ptx::mbar_wait(&aux->tmem_empty[acc], acc_phase ^ 1, abort_flag)) {
+        if (!ptx::mbar_wait(&aux->tmem_empty[acc], acc_phase ^ 1, abort_flag, wait_limit)) {
           fail(aux, p.status, STATUS_TIMEOUT_MMA);
           break;
         }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait(&aux->full[stage], phase, abort_flag)) {
+          if (!ptx::mbar_wait(&aux->full[stage], phase, abort_flag, wait_limit)) {
             fail(aux, p.status, STATUS_TIMEOUT_MMA);
             ok = false;
             break;
@@ -671,7 +1188,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
             ptx::umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k16) != 0 ? 1u : 0u);
           }
           ptx::umma_commit(&aux->empty[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         ptx::umma_commit(&aux->tmem_full[acc]);
@@ -680,43 +1197,32 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   } else if (warp >= FIRST_EPI_WARP) {
     // ============================================================== epilogue (warps 4..11)
     const int part = warp & 3;                          // TMEM lane quarter this warp may read
-    const int half = (warp - FIRST_EPI_WARP) >> 2;      // takes the 32-column chunks 2 * i + half
-    uint8_t* patch = smem + STAGES * STAGE_BYTES + AUX_BYTES + (warp - FIRST_EPI_WARP) * SIDE_BYTES;
-    uint8_t* bias_sm = smem + STAGES * STAGE_BYTES + AUX_BYTES + NUM_EPI_WARPS * SIDE_BYTES +
-                       (warp - FIRST_EPI_WARP) * BIAS_BYTES;
+    const int half = (warp - FIRST_EPI_WARP) >> 2;      // which half of the accumulator columns
+    uint8_t* patch = smem + L::kEpiOff + (warp - FIRST_EPI_WARP) * L::kPatch;
+    uint8_t* bias_sm = smem + L::kBiasOff + (warp - FIRST_EPI_WARP) * BIAS_BYTES;
     int iter = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+    for (int tile = cta; tile < total_tiles; tile += num_ctas, ++iter) {
       const TileCoord c = decode_tile<MODE>(p, aux, tile);
       const int rows = c.row_end - c.row_begin;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
-
-      // Rows of the output matrix covered by this warp: [warp_row0, warp_row0 + warp_valid).
-      long warp_row0;
-      int warp_valid;
-      if (MODE == kWgrad) {
-        const int m0 = c.m_tile * BM + part * 32;
-        warp_row0 = static_cast<long>(c.group) * p.m + m0;
-        warp_valid = min(32, p.m - m0);
-      } else {
-        const int r0 = c.m_tile * BM + part * 32;
-        warp_row0 = static_cast<long>(c.row_begin) + r0;
-        warp_valid = min(32, rows - r0);
-      }
-      const bool row_ok = lane < warp_valid;
-      const long out_row = warp_row0 + lane;
-      const bool have_acc = (MODE != kWgrad) || rows > 0;
       const int n0 = c.n_tile * BN;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(part * 32) << 16) + acc * BN;
-      const bool use_aux = (MODE != kWgrad) && p.epi == kEpiDAct;
-      const bool read_old = (MODE == kWgrad) && p.accumulate && !p.out_fp32;
-      const bool use_side = (use_aux || read_old) && warp_valid > 0;
-      const uint8_t* side = reinterpret_cast<const uint8_t*>(use_aux ? p.aux : p.out) +
-                            (warp_row0 * p.n + n0) * 2;
-      const long side_pitch = static_cast<long>(p.n) * 2;
-      const int first_col = n0 + half * 32;
 
       if constexpr (MODE == kWgrad) {
+        // Rows of the output matrix covered by this warp: [warp_row0, warp_row0 + warp_valid).
+        const int m0 = c.m_tile * BM + part * 32;
+        const long warp_row0 = static_cast<long>(c.group) * p.m + m0;
+        const int warp_valid = min(32, p.m - m0);
+        const bool row_ok = lane < warp_valid;
+        const long out_row = warp_row0 + lane;
+        const bool have_acc = rows > 0;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(part * 32) << 16) + acc * BN;
+        const bool read_old = p.accumulate && !p.out_fp32;
+        const bool use_side = read_old && warp_valid > 0;
+        const uint8_t* side = reinterpret_cast<const uint8_t*>(p.out) + (warp_row0 * p.n + n0) * 2;
+        const long side_pitch = static_cast<long>(p.n) * 2;
+        const int first_col = n0 + half * 32;
+        {
         // The bias gradient of a grouped linear is the per-group column sum of the matrix the
         // weight gradient takes as P.  The epilogue warps have nothing to do while the main
         // loop of this tile runs, so on the tiles of the first N column block they add up the
@@ -766,7 +1272,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           asm volatile("bar.sync 2, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
           const int tid = static_cast<int>(threadIdx.x) - FIRST_EPI_WARP * 32;
           if (tid < BM && c.m_tile * BM + tid < p.m) {
-            const uint8_t* first = smem + STAGES * STAGE_BYTES + AUX_BYTES;
+            const uint8_t* first = smem + L::kEpiOff;
             float total = 0.f;
 #pragma unroll
             for (int w8 = 0; w8 < NUM_EPI_WARPS; ++w8) {
@@ -779,103 +1285,146 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           asm volatile("bar.sync 2, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
         }
       }
-      // The side operand (saved pre-activation, or the old gradient when accumulating) does
-      // not depend on the accumulator: fetch its first chunk before waiting for the MMAs.
-      if (use_side && first_col < p.n) {
-        stage_side(patch, side + half * 64, side_pitch, warp_valid, lane);
-      }
-      // Bias slices of this warp's four chunks go to shared memory once per tile.
-      const bool use_bias = (MODE != kWgrad) && !use_aux && p.bias != nullptr;
-      if (use_bias) {
-        __syncwarp();
-        if (lane < CHUNKS_PER_WARP * 4) {
-          const int q = lane >> 2, seg = lane & 3;
-          const int col = n0 + (2 * q + half) * 32;
-          if (col < p.n) {
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.bias) +
-                                 (static_cast<long>(c.group) * p.n + col) * 2 + seg * 16;
-            *reinterpret_cast<uint4*>(bias_sm + q * 64 + seg * 16) =
-                __ldg(reinterpret_cast<const uint4*>(src));
-          }
+        // The old gradient (when accumulating in 16 bits) does not depend on the accumulator:
+        // fetch its first chunk before waiting for the MMAs.
+        if (use_side && first_col < p.n) {
+          stage_side(patch, side + half * 64, side_pitch, warp_valid, lane);
         }
-        __syncwarp();
-      }
-      // Pull the side operand of the next tile of this CTA towards L2 while this tile is
-      // being finished: each lane asks for two of the four 128-byte lines of its row.
-      if (use_aux && tile + static_cast<int>(gridDim.x) < total_tiles) {
-        const TileCoord nx = decode_tile<MODE>(p, aux, tile + gridDim.x);
-        const int r0 = nx.m_tile * BM + part * 32 + lane;
-        if (r0 < nx.row_end - nx.row_begin) {
-          const uint8_t* row = reinterpret_cast<const uint8_t*>(p.aux) +
-                               ((static_cast<long>(nx.row_begin) + r0) * p.n + nx.n_tile * BN) * 2;
+        if (!ptx::mbar_wait(&aux->tmem_full[acc], acc_phase, abort_flag, wait_limit)) {
+          if (lane == 0) fail(aux, p.status, STATUS_TIMEOUT_EPILOGUE);
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        EpiTile et;
+        et.t_row = t_row;
+        et.half = half;
+        et.lane = lane;
+        et.n0 = n0;
+        et.out_row = out_row;
+        et.group = c.group;
+        et.warp_valid = warp_valid;
+        et.row_ok = row_ok;
+        et.have_acc = have_acc;
+        et.use_aux = false;
+        et.read_old = read_old;
+        et.use_side = use_side;
+        et.side = side;
+        et.side_pitch = side_pitch;
+        et.patch = patch;
+        et.out_row_base = nullptr;
+        et.remote_row = false;
+        et.bias_sm = nullptr;
+        et.empty_bar = &aux->tmem_empty[acc];
+        epilogue_tile<MODE, T, ACT>(p, et);
+      } else {
+        // This warp: rows [r0, r0 + 32) of the tile, columns [col_first, col_first + 128).
+        const int r0 = c.m_tile * BM + part * 32;
+        const long warp_row0 = static_cast<long>(c.row_begin) + r0;
+        const int warp_valid = max(0, min(32, rows - r0));
+        const bool row_ok = lane < warp_valid;
+        const long out_row = warp_row0 + lane;
+        const int col_first = n0 + half * (BN / 2);
+        const int n_chunks = max(0, min(CHUNKS_PER_WARP, (p.n - col_first) / 32));
+        const bool use_aux = p.epi == kEpiDAct;
+        const bool use_side = use_aux && warp_valid > 0 && n_chunks > 0;
+        const long side_pitch = static_cast<long>(p.n) * 2;
+        const uint8_t* side = reinterpret_cast<const uint8_t*>(p.aux) + (warp_row0 * p.n + col_first) * 2;
+
+        // The patch is free once the bulk stores of the previous tile have read it; the side
+        // operand is staged by other lanes than the one that owns a row, hence the warp sync.
+        ptx::bulk_wait_read<0>();
+        if (use_side) {
+          __syncwarp();
+          stage_side<PATCH_PITCH>(patch, side, side_pitch, warp_valid, lane);
+        }
+        // Bias slice of this warp's span goes to shared memory once per tile.
+        const bool use_bias = !use_aux && p.bias != nullptr;
+        if (use_bias) {
+          __syncwarp();
+          if (lane < n_chunks * 4) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.bias) +
+                                 (static_cast<long>(c.group) * p.n + col_first) * 2 + lane * 16;
+            *reinterpret_cast<uint4*>(bias_sm + lane * 16) = __ldg(reinterpret_cast<const uint4*>(src));
+          }
+          __syncwarp();
+        }
+        // Pull the side operand of the next tile of this CTA towards L2 while this tile is
+        // being finished: each lane asks for the two 128-byte lines of its row.
+        if (use_aux && tile + num_ctas < total_tiles) {
+          const TileCoord nx = decode_tile<MODE>(p, aux, tile + num_ctas);
+          const int nr = nx.m_tile * BM + part * 32 + lane;
+          if (nr < nx.row_end - nx.row_begin) {
+            const int ncol = nx.n_tile * BN + half * (BN / 2);
+            const uint8_t* row = reinterpret_cast<const uint8_t*>(p.aux) +
+                                 ((static_cast<long>(nx.row_begin) + nr) * p.n + ncol) * 2;
 #pragma unroll
-          for (int l = 0; l < 2; ++l) {
-            const int line = half * 2 + l;
-            if (nx.n_tile * BN + line * 64 < p.n) {
-              asm volatile("prefetch.global.L2 [%0];" ::"l"(row + line * 128));
+            for (int l = 0; l < 2; ++l) {
+              if (ncol + l * 64 < p.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + l * 128));
             }
           }
         }
-      }
 
-      if (!ptx::mbar_wait(&aux->tmem_full[acc], acc_phase, abort_flag)) {
-        if (lane == 0) fail(aux, p.status, STATUS_TIMEOUT_EPILOGUE);
-        break;
-      }
-      ptx::tc_fence_after_sync();
-
-      EpiTile et;
-      et.t_row = t_row;
-      et.half = half;
-      et.lane = lane;
-      et.n0 = n0;
-      et.out_row = out_row;
-      et.group = c.group;
-      et.warp_valid = warp_valid;
-      et.row_ok = row_ok;
-      et.have_acc = have_acc;
-      et.use_aux = use_aux;
-      et.read_old = read_old;
-      et.use_side = use_side;
-      et.side = side;
-      et.side_pitch = side_pitch;
-      et.patch = patch;
-      if (MODE != kWgrad && p.push_meta != nullptr) {
-        // Fused combine: this lane's output row lives in the source rank's return buffer.
-        et.out_row_base = nullptr;
-        et.remote_row = false;
-        if (row_ok) {
-          const int64_t m = p.push_meta[out_row];
-          const int src = static_cast<int>(m >> 32);
-          const long slot = static_cast<long>(m & 0xffffffffll);
-          et.out_row_base = static_cast<uint8_t*>(p.push_dst.p[src]) + slot * p.n * 2;
-          et.remote_row = src != p.push_me;
+        RowTile rt;
+        rt.lane = lane;
+        rt.col_first = col_first;
+        rt.n_chunks = n_chunks;
+        rt.warp_valid = warp_valid;
+        rt.row_ok = row_ok;
+        rt.use_aux = use_aux;
+        rt.side = side;
+        rt.side_pitch = side_pitch;
+        rt.patch = patch;
+        rt.out_row = nullptr;
+        rt.pre_row = nullptr;
+        if (p.push_meta != nullptr) {
+          // Fused combine: this lane's output row lives in the source rank's return buffer.
+          if (row_ok) {
+            const int64_t m = p.push_meta[out_row];
+            const int src = static_cast<int>(m >> 32);
+            const long slot = static_cast<long>(m & 0xffffffffll);
+            if (src >= 0 && src < p.push_world && slot < p.push_slots) {
+              rt.out_row = static_cast<uint8_t*>(p.push_dst.p[src]) + slot * p.n * 2;
+            } else if (p.status != nullptr) {
+              atomicCAS(p.status, 0, STATUS_BAD_PUSH_META);
+            }
+          }
+        } else {
+          rt.out_row = static_cast<uint8_t*>(p.out) + out_row * p.n * 2;
+          if (p.pre_out != nullptr) rt.pre_row = static_cast<uint8_t*>(p.pre_out) + out_row * p.n * 2;
         }
-      } else {
-        et.out_row_base = static_cast<uint8_t*>(p.out) + out_row * p.n * 2;
-        et.remote_row = false;
+        rt.bias_sm = use_bias ? bias_sm : nullptr;
+        rt.empty_bar = &aux->tmem_empty[acc];
+        rt.t_row = tmem_base + (static_cast<uint32_t>(part * 32) << 16) + acc * BN + half * (BN / 2);
+
+        if (!ptx::mbar_wait(&aux->tmem_full[acc], acc_phase, abort_flag, wait_limit)) {
+          if (lane == 0) fail(aux, p.status, STATUS_TIMEOUT_EPILOGUE);
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        epilogue_tile_rows<T, ACT>(rt);
       }
-      et.bias_sm = use_bias ? bias_sm : nullptr;
-      et.empty_bar = &aux->tmem_empty[acc];
-      epilogue_tile<MODE, T, ACT>(p, et);
     }
-    if (MODE != kWgrad && p.push_meta != nullptr) {
-      // All rows of this CTA are on their way: wait for the bulk stores, order everything
-      // before the completion count; the last CTA of the grid publishes the epoch on every
-      // peer's return channel.
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-      asm volatile("fence.proxy.async;" ::: "memory");
-      __threadfence_system();
-      asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
-      if (threadIdx.x == FIRST_EPI_WARP * 32) {
-        const int prev = atomicAdd(p.push_counter, 1);
-        if (prev == static_cast<int>(gridDim.x) - 1) {
-          *p.push_counter = 0;
-          __threadfence_system();
-          const int epoch = *p.push_epoch;
-          for (int peer = 0; peer < p.push_world; ++peer) {
-            int* flag = static_cast<int*>(p.push_flags.p[peer]) + kChanReturn * kMaxPeers + p.push_me;
-            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+    if constexpr (MODE != kWgrad) {
+      // Every bulk store of this thread has to be complete before the CTA may go away (and,
+      // in push mode, before the arrival of its rows is announced).
+      ptx::bulk_wait<0>();
+      if (p.push_meta != nullptr) {
+        // All rows of this CTA have landed: order everything before the completion count; the
+        // last CTA of the grid publishes the epoch on every peer's return channel.  A CTA that
+        // gave up still counts, so that the counter is zero again for the next launch.
+        ptx::fence_proxy_async_all();
+        __threadfence_system();
+        asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
+        if (threadIdx.x == FIRST_EPI_WARP * 32) {
+          const int prev = atomicAdd(p.push_counter, 1);
+          if (prev == num_ctas - 1) {
+            *p.push_counter = 0;
+            __threadfence_system();
+            const int epoch = *p.push_epoch;
+            for (int peer = 0; peer < p.push_world; ++peer) {
+              int* flag = static_cast<int*>(p.push_flags.p[peer]) + kChanReturn * kMaxPeers + p.push_me;
+              st_release_sys_i32(flag, epoch);
+            }
           }
         }
       }
@@ -910,13 +1459,13 @@ cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const Kerne
   {
     std::lock_guard<std::mutex> lock(mu);
     if (!(configured >> (dev & 63) & 1)) {
-      cudaError_t e =
-          cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           Layout<MODE>::kBytes);
       if (e != cudaSuccess) return e;
       configured |= 1ull << (dev & 63);
     }
   }
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, kp);
+  kernel<<<grid, NUM_THREADS, Layout<MODE>::kBytes, stream>>>(ta, tb, kp);
   return cudaGetLastError();
 }
 

@@ -90,17 +90,28 @@ __device__ __forceinline__ bool last_block(int* counter) {
 }
 
 // ------------------------------------------------------------------------------ counts
+// Receive layout on every rank p: local expert outer; inside an expert segment the rows of
+// source rank w sit at position (p - w) mod world — the rank's own rows first, then those of
+// rank p - 1, p - 2, ...  A sender serves its peers in the order me, me + 1, me + 2, ..., so a
+// receiver's rows arrive roughly in the order in which its GEMM reads them.
+__device__ __forceinline__ int source_position(int owner, int src, int world) {
+  int j = owner - src;
+  return j < 0 ? j + world : j;
+}
+
 __global__ void __launch_bounds__(1024, 1)
 count_exchange_kernel(const __grid_constant__ ExchangeCtx c, const int* __restrict__ lec, const __grid_constant__ PeerPtrs cnt, int n_expert,
-                      int capacity_rows, int* __restrict__ dst_base, int* __restrict__ expert_offs,
-                      int* __restrict__ total_rows) {
-  extern __shared__ int sh[];  // [world * tot] matrix, then [tot] column sums
+                      int capacity_rows, int* __restrict__ dst_base, int* __restrict__ seg_base,
+                      int* __restrict__ blk_base, int* __restrict__ expert_offs,
+                      int* __restrict__ seg_off, int* __restrict__ total_rows) {
+  extern __shared__ int sh[];  // [world * width] matrix, then [tot] column sums
   const int tot = n_expert * c.world;
+  const int width = tot + 1;   // a rank's row: its counts, then its receive capacity
   const int epoch = c.epoch[0] + 1;
   // 1. my row into every peer's matrix
-  for (int g = threadIdx.x; g < tot; g += blockDim.x) {
-    const int v = lec[g];
-    for (int p = 0; p < c.world; ++p) static_cast<int*>(cnt.p[p])[c.me * tot + g] = v;
+  for (int g = threadIdx.x; g < width; g += blockDim.x) {
+    const int v = g < tot ? lec[g] : capacity_rows;
+    for (int p = 0; p < c.world; ++p) static_cast<int*>(cnt.p[p])[c.me * width + g] = v;
   }
   __threadfence_system();
   __syncthreads();
@@ -111,50 +122,71 @@ count_exchange_kernel(const __grid_constant__ ExchangeCtx c, const int* __restri
   block_wait_all(c, kChanCounts, epoch);
   const volatile int* mine = static_cast<const volatile int*>(cnt.p[c.me]);
   int* mat = sh;
-  int* col = sh + c.world * tot;
-  for (int i = threadIdx.x; i < c.world * tot; i += blockDim.x) mat[i] = mine[i];
+  int* col = sh + c.world * width;
+  for (int i = threadIdx.x; i < c.world * width; i += blockDim.x) mat[i] = mine[i];
   __syncthreads();
   for (int g = threadIdx.x; g < tot; g += blockDim.x) {
     int s = 0;
-    for (int w = 0; w < c.world; ++w) s += mat[w * tot + g];
+    for (int w = 0; w < c.world; ++w) s += mat[w * width + g];
     col[g] = s;
   }
   __syncthreads();
-  // 3. offsets.  Receive layout on every rank: local expert outer, source rank inner.
+  // 3. offsets of every global expert on its owner, and of my rows inside them
   for (int g = threadIdx.x; g < tot; g += blockDim.x) {
     const int p = g / n_expert;
     const int e = g - p * n_expert;
-    int base = 0;
-    for (int e2 = 0; e2 < e; ++e2) base += col[p * n_expert + e2];
-    for (int w = 0; w < c.me; ++w) base += mat[w * tot + g];
-    dst_base[g] = base;
+    int seg = 0, blk = 0;
+    for (int e2 = 0; e2 < e; ++e2) {
+      const int n = col[p * n_expert + e2];
+      seg += n;
+      blk += (n + kRowBlock - 1) / kRowBlock;
+    }
+    const int my_pos = source_position(p, c.me, c.world);
+    int before = 0;
+    for (int j = 0; j < my_pos; ++j) {
+      int w = p - j;
+      if (w < 0) w += c.world;
+      before += mat[w * width + g];
+    }
+    seg_base[g] = seg;
+    blk_base[g] = blk;
+    dst_base[g] = seg + before;
   }
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < n_expert; ++e) {
-      expert_offs[e] = run;
-      run += col[c.me * n_expert + e];
-    }
-    expert_offs[n_expert] = run < capacity_rows ? run : capacity_rows;
-    total_rows[0] = expert_offs[n_expert];
-    // Overflow anywhere is visible to everybody (same matrix): report it on every rank.
-    for (int p = 0; p < c.world; ++p) {
-      int t = 0;
-      for (int e = 0; e < n_expert; ++e) t += col[p * n_expert + e];
-      if (t > capacity_rows) atomicCAS(c.status, 0, kStatusRecvOverflow);
-    }
-    if (run > capacity_rows) {
-      // Clamp the local expert segments to the buffer.
-      for (int e = 0; e <= n_expert; ++e) {
-        if (expert_offs[e] > capacity_rows) expert_offs[e] = capacity_rows;
+  // 4. my own segments: expert offsets and, per expert, where each source's rows begin
+  for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+    int seg = 0;
+    for (int e2 = 0; e2 < e; ++e2) seg += col[c.me * n_expert + e2];
+    expert_offs[e] = seg < capacity_rows ? seg : capacity_rows;
+    int run = seg;
+    for (int j = 0; j <= c.world; ++j) {
+      seg_off[e * (c.world + 1) + j] = run < capacity_rows ? run : capacity_rows;
+      if (j < c.world) {
+        int w = c.me - j;
+        if (w < 0) w += c.world;
+        run += mat[w * width + c.me * n_expert + e];
       }
     }
-    c.epoch[0] = epoch;
+    if (e == n_expert - 1) {
+      const int end = run < capacity_rows ? run : capacity_rows;
+      expert_offs[n_expert] = end;
+      total_rows[0] = end;
+    }
   }
+  // Overflow anywhere is visible to everybody (same matrix): report it on every rank.  So is a
+  // peer that sized its receive buffer differently: senders clamp against THEIR capacity, so
+  // a smaller buffer elsewhere would be overrun.
+  if (static_cast<int>(threadIdx.x) < c.world) {
+    const int p = threadIdx.x;
+    int t = 0;
+    for (int e = 0; e < n_expert; ++e) t += col[p * n_expert + e];
+    if (t > capacity_rows) atomicCAS(c.status, 0, kStatusRecvOverflow);
+    if (mat[p * width + tot] != capacity_rows) atomicCAS(c.status, 0, kStatusCapacityMismatch);
+  }
+  if (threadIdx.x == 0) c.epoch[0] = epoch;
 }
 
-__global__ void begin_epoch_kernel(const __grid_constant__ ExchangeCtx c) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) c.epoch[0] = c.epoch[0] + 1;
+__global__ void begin_epoch_kernel(const __grid_constant__ ExchangeCtx c, int word) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) c.epoch[word] = c.epoch[word] + 1;
 }
 
 // ------------------------------------------------------------------------------ row helpers
@@ -317,7 +349,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024, 1) return_push_kernel(const __grid_constant__ ExchangeCtx c, const T* __restrict__ rows_in,
                                    const int64_t* __restrict__ meta,
                                    const int* __restrict__ total_rows, const __grid_constant__ PeerPtrs ret, int d,
-                                   int capacity_rows) {
+                                   int capacity_rows, long ret_slots) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   int n_rows = total_rows[0];
@@ -328,7 +360,7 @@ __global__ void __launch_bounds__(1024, 1) return_push_kernel(const __grid_const
     const int64_t m = meta[r];
     const int src = static_cast<int>(m >> 32);
     const long slot = static_cast<long>(m & 0xffffffffll);
-    if (src < 0 || src >= c.world) continue;
+    if (src < 0 || src >= c.world || slot >= ret_slots) continue;
     const uint4* in = reinterpret_cast<const uint4*>(rows_in + static_cast<long>(r) * d);
     uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(ret.p[src]) + slot * d);
     for (int i0 = lane; i0 < nv; i0 += 128) {
@@ -435,7 +467,7 @@ template <> __device__ __forceinline__ __half from_float<__half>(float v) { retu
 template <typename T, typename Vec, int PER>
 __global__ void allreduce_kernel(const __grid_constant__ ExchangeCtx c, const __grid_constant__ PeerPtrs bufs, T* __restrict__ out, long n,
                                  float scale) {
-  const int target_ready = 2 * c.epoch[0];
+  const int target_ready = 2 * c.epoch[kReduceEpochWord];
   if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(c, kChanReduce, target_ready);
   block_wait_all(c, kChanReduce, target_ready);
   const long nvec = n / PER;
@@ -479,7 +511,7 @@ __global__ void allreduce_kernel(const __grid_constant__ ExchangeCtx c, const __
 template <typename T, typename Vec, int PER>
 __global__ void allreduce_two_shot_kernel(const __grid_constant__ ExchangeCtx c, const __grid_constant__ PeerPtrs bufs, T* __restrict__ out, long n,
                                           float scale) {
-  const int target_ready = 2 * c.epoch[0];
+  const int target_ready = 2 * c.epoch[kReduceEpochWord];
   if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(c, kChanReduce, target_ready);
   block_wait_all(c, kChanReduce, target_ready);
   const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
@@ -521,7 +553,7 @@ __global__ void allreduce_two_shot_kernel(const __grid_constant__ ExchangeCtx c,
 // The first handshake makes sure no peer is still reading its buffer from an earlier call.
 __global__ void allgather_kernel(const __grid_constant__ ExchangeCtx c, const uint4* __restrict__ src, const __grid_constant__ PeerPtrs bufs,
                                  uint4* __restrict__ out, long nvec) {
-  const int target_ready = 2 * c.epoch[0];
+  const int target_ready = 2 * c.epoch[kReduceEpochWord];
   if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(c, kChanReduce, target_ready);
   block_wait_all(c, kChanReduce, target_ready);
   const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
@@ -567,10 +599,11 @@ int push_grid(int work_items, int warps_per_block) {
   else { using T = __half; __VA_ARGS__; }
 
 cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const PeerPtrs& cnt,
-                                  int n_expert, int capacity_rows, int* dst_base,
-                                  int* expert_offs, int* total_rows, cudaStream_t stream) {
+                                  int n_expert, int capacity_rows, int* dst_base, int* seg_base,
+                                  int* blk_base, int* expert_offs, int* seg_off, int* total_rows,
+                                  cudaStream_t stream) {
   const int tot = n_expert * ctx.world;
-  const size_t smem = static_cast<size_t>(ctx.world + 1) * tot * sizeof(int);
+  const size_t smem = (static_cast<size_t>(ctx.world) * (tot + 1) + tot) * sizeof(int);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(count_exchange_kernel,
@@ -578,7 +611,8 @@ cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const 
     if (e != cudaSuccess) return e;
   }
   count_exchange_kernel<<<1, 1024, smem, stream>>>(ctx, lec, cnt, n_expert, capacity_rows, dst_base,
-                                                   expert_offs, total_rows);
+                                                   seg_base, blk_base, expert_offs, seg_off,
+                                                   total_rows);
   return cudaGetLastError();
 }
 
@@ -598,7 +632,12 @@ cudaError_t launch_capacity_grant(const ExchangeCtx& ctx, const int* lec, const 
 }
 
 cudaError_t launch_begin_epoch(const ExchangeCtx& ctx, cudaStream_t stream) {
-  begin_epoch_kernel<<<1, 32, 0, stream>>>(ctx);
+  begin_epoch_kernel<<<1, 32, 0, stream>>>(ctx, 0);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_begin_reduce_epoch(const ExchangeCtx& ctx, cudaStream_t stream) {
+  begin_epoch_kernel<<<1, 32, 0, stream>>>(ctx, kReduceEpochWord);
   return cudaGetLastError();
 }
 
@@ -635,11 +674,11 @@ cudaError_t launch_wait_copy(const ExchangeCtx& ctx, int channel, int dtype, con
 
 cudaError_t launch_return_push(const ExchangeCtx& ctx, int dtype, const void* rows,
                                const int64_t* meta, const int* total_rows, const PeerPtrs& ret,
-                               int d, int capacity_rows, cudaStream_t stream) {
+                               int d, int capacity_rows, long ret_slots, cudaStream_t stream) {
   if (d % 8 != 0) return cudaErrorInvalidValue;
   const int wpb = 32;  // one block per SM: see launch_dispatch_push
   FMOE_P2P_16(dtype, (return_push_kernel<T><<<148, wpb * 32, 0, stream>>>(
-      ctx, static_cast<const T*>(rows), meta, total_rows, ret, d, capacity_rows)));
+      ctx, static_cast<const T*>(rows), meta, total_rows, ret, d, capacity_rows, ret_slots)));
   return cudaGetLastError();
 }
 

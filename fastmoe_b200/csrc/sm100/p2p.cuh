@@ -20,6 +20,11 @@ struct PeerPtrs {
 // Status codes written to the status word when something goes wrong (0 = fine).
 constexpr int kStatusPeerTimeout = 201;      // a peer's flag did not arrive in time
 constexpr int kStatusRecvOverflow = 202;     // more rows routed to a rank than its buffer holds
+constexpr int kStatusCapacityMismatch = 203; // the ranks of a group sized their receive buffers differently
+
+// Arrival of dispatched rows is tracked per block of this many rows of the receive buffer
+// (the M extent of a GEMM tile).
+constexpr int kRowBlock = 128;
 
 // Flag channels inside the symmetric signal buffer: int32 [kNumChannels][kMaxPeers].
 constexpr int kChanCounts = 0;
@@ -28,9 +33,14 @@ constexpr int kChanReturn = 2;
 constexpr int kChanReduce = 3;
 constexpr int kNumChannels = 4;
 
+// Word of the local epoch array that counts the reductions (all-reduce, all-gather): separate
+// from the exchange epoch [0], so a gradient reduction on a side stream may run beside a layer.
+constexpr int kReduceEpochWord = 6;
+
 struct ExchangeCtx {
   PeerPtrs flags;        // each peer's signal buffer
-  int* epoch;            // local: [0] current epoch, [1] CTA completion counter (dispatch), [2] (return)
+  int* epoch;            // local int32[8]: [0] exchange epoch, [1]-[4] CTA completion counters
+                         // (dispatch, return, reduce, GEMM push), [6] reduction epoch
   int me;
   int world;
   int* status;           // local status word
@@ -39,17 +49,25 @@ struct ExchangeCtx {
 
 // Starts a new exchange epoch and (forward only) exchanges the routing counts:
 //   lec[tot]            my tokens per global expert
-//   cnt                 every peer's count matrix int32 [world][tot] (symmetric)
+//   cnt                 every peer's count matrix int32 [world][tot + 1] (symmetric; the last
+//                       entry of a row is that rank's receive capacity)
 // Outputs, all in local memory:
 //   dst_base[tot]       first row of my rows inside the owner's receive buffer, per global expert
+//   seg_base[tot]       first row of the expert's whole segment on its owner
+//   blk_base[tot]       index of the segment's first kRowBlock-row block on its owner
 //   expert_offs[E + 1]  row offsets of my local experts inside my receive buffer
+//   seg_off[E][world + 1]  inside my expert e, the row where the rows of the j-th source begin
+//                       (source j is rank (me - j) mod world)
 //   total_rows[1]
 cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const PeerPtrs& cnt,
-                                  int n_expert, int capacity_rows, int* dst_base,
-                                  int* expert_offs, int* total_rows, cudaStream_t stream);
+                                  int n_expert, int capacity_rows, int* dst_base, int* seg_base,
+                                  int* blk_base, int* expert_offs, int* seg_off, int* total_rows,
+                                  cudaStream_t stream);
 
 // Backward passes reuse the forward routing: only the epoch advances.
 cudaError_t launch_begin_epoch(const ExchangeCtx& ctx, cudaStream_t stream);
+// Advances the reduction epoch (all-reduce and all-gather launches follow it).
+cudaError_t launch_begin_reduce_epoch(const ExchangeCtx& ctx, cudaStream_t stream);
 
 // rows[p][dst_base[g] + rank[s]] = scale[s] * x[s / k]  on the owner p = g / n_expert of the
 // slot's expert g, plus meta[p][row] = (me << 32) | s.  The last CTA publishes the flags.
@@ -66,10 +84,11 @@ cudaError_t launch_wait_copy(const ExchangeCtx& ctx, int channel, int dtype, con
                              int capacity_rows, void* out_rows, int64_t* out_meta,
                              cudaStream_t stream);
 
-// ret[src][slot] = rows[r] for every received row r with meta[r] = (src << 32) | slot.
+// ret[src][slot] = rows[r] for every received row r with meta[r] = (src << 32) | slot; rows
+// whose source or slot (>= ret_slots, the rows of every return buffer) is out of range are skipped.
 cudaError_t launch_return_push(const ExchangeCtx& ctx, int dtype, const void* rows,
                                const int64_t* meta, const int* total_rows, const PeerPtrs& ret,
-                               int d, int capacity_rows, cudaStream_t stream);
+                               int d, int capacity_rows, long ret_slots, cudaStream_t stream);
 
 // Waits for the return flags, then out[t] = sum_j w[t, j] * ret[t * k + j] over kept slots
 // (w = 1 when null) and, when `keep` is given, keep[s] = ret[s] for the backward pass.

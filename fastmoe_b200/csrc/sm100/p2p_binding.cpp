@@ -4,6 +4,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
+#include <pybind11/stl.h>
 
 #include "grouped_gemm.cuh"
 #include "p2p.cuh"
@@ -38,8 +39,8 @@ class ExchangeContext {
   ExchangeContext(std::vector<int64_t> flag_ptrs, torch::Tensor epoch, int64_t me, int64_t world,
                   torch::Tensor status, double timeout_ms)
       : epoch_(epoch), status_(status) {
-    TORCH_CHECK(epoch.is_cuda() && epoch.scalar_type() == torch::kInt && epoch.numel() >= 4,
-                "epoch must be an int32 CUDA tensor with at least 4 elements");
+    TORCH_CHECK(epoch.is_cuda() && epoch.scalar_type() == torch::kInt && epoch.numel() >= 8,
+                "epoch must be an int32 CUDA tensor with at least 8 elements");
     TORCH_CHECK(status.is_cuda() && status.scalar_type() == torch::kInt, "status must be int32 CUDA");
     TORCH_CHECK(static_cast<int64_t>(flag_ptrs.size()) == world, "one signal buffer per rank");
     ctx_.flags = to_ptrs(flag_ptrs);
@@ -52,14 +53,21 @@ class ExchangeContext {
 
   void set_timeout_ms(double ms) { ctx_.timeout_ns = static_cast<unsigned long long>(ms * 1e6); }
 
+  // `tables` is one int32 tensor holding, back to back: dst_base[tot], seg_base[tot],
+  // blk_base[tot], expert_offs[E + 1], seg_off[E * (world + 1)], total_rows[1].
   void count_exchange(torch::Tensor lec, std::vector<int64_t> cnt_ptrs, int64_t n_expert,
-                      int64_t capacity_rows, torch::Tensor dst_base, torch::Tensor expert_offs,
-                      torch::Tensor total_rows) {
+                      int64_t capacity_rows, torch::Tensor tables) {
     c10::cuda::CUDAGuard guard(lec.device());
+    const int64_t tot = n_expert * ctx_.world;
+    TORCH_CHECK(tables.scalar_type() == torch::kInt && tables.is_contiguous() &&
+                    tables.numel() >= 3 * tot + (n_expert + 1) + n_expert * (ctx_.world + 1) + 1,
+                "count_exchange: table tensor too small");
+    int* t = tables.data_ptr<int>();
     FMOE_P2P_CHECK(fmoe::launch_count_exchange(
         ctx_, lec.data_ptr<int>(), to_ptrs(cnt_ptrs), static_cast<int>(n_expert),
-        static_cast<int>(capacity_rows), dst_base.data_ptr<int>(), expert_offs.data_ptr<int>(),
-        total_rows.data_ptr<int>(), stream()));
+        static_cast<int>(capacity_rows), t, t + tot, t + 2 * tot, t + 3 * tot,
+        t + 3 * tot + n_expert + 1, t + 3 * tot + n_expert + 1 + n_expert * (ctx_.world + 1),
+        stream()));
   }
 
   std::vector<torch::Tensor> capacity_grant(torch::Tensor lec, torch::Tensor cap,
@@ -117,12 +125,12 @@ class ExchangeContext {
   }
 
   void return_push(torch::Tensor rows, torch::Tensor meta, torch::Tensor total_rows,
-                   std::vector<int64_t> ret_ptrs) {
+                   std::vector<int64_t> ret_ptrs, int64_t ret_slots) {
     c10::cuda::CUDAGuard guard(rows.device());
     FMOE_P2P_CHECK(fmoe::launch_return_push(ctx_, dtype16(rows), rows.data_ptr(),
                                             meta.data_ptr<int64_t>(), total_rows.data_ptr<int>(),
                                             to_ptrs(ret_ptrs), static_cast<int>(rows.size(1)),
-                                            static_cast<int>(rows.size(0)), stream()));
+                                            static_cast<int>(rows.size(0)), ret_slots, stream()));
   }
 
   void wait_combine(torch::Tensor ret, torch::Tensor idx, c10::optional<torch::Tensor> weight,
@@ -147,7 +155,7 @@ class ExchangeContext {
       case torch::kFloat: code = 2; break;
       default: TORCH_CHECK(false, "allreduce: bf16, fp16 or fp32"); code = -1;
     }
-    FMOE_P2P_CHECK(fmoe::launch_begin_epoch(ctx_, stream()));
+    FMOE_P2P_CHECK(fmoe::launch_begin_reduce_epoch(ctx_, stream()));
     if (two_shot) {
       FMOE_P2P_CHECK(fmoe::launch_allreduce_two_shot(ctx_, code, to_ptrs(buf_ptrs), out.data_ptr(),
                                                      n, static_cast<float>(scale), stream()));
@@ -166,22 +174,32 @@ class ExchangeContext {
                     reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0,
                 "allgather operands must be 16-byte aligned");
     c10::cuda::CUDAGuard guard(out.device());
-    FMOE_P2P_CHECK(fmoe::launch_begin_epoch(ctx_, stream()));
+    FMOE_P2P_CHECK(fmoe::launch_begin_reduce_epoch(ctx_, stream()));
     FMOE_P2P_CHECK(fmoe::launch_allgather(ctx_, src.data_ptr(), to_ptrs(buf_ptrs), out.data_ptr(),
                                           bytes, stream()));
   }
 
-  // Grouped GEMM (forward mode 0 or input-gradient mode 1) whose epilogue stores each result
-  // row into the slot-indexed return buffer of the row's source rank (`meta`, `ret_ptrs`) and
-  // publishes the return flags when the grid is done: GEMM + combine-direction exchange in
-  // one kernel.
-  void gemm_push(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor offs,
-                 c10::optional<torch::Tensor> bias, torch::Tensor meta,
-                 std::vector<int64_t> ret_ptrs) {
+  // Row-mode grouped GEMM with the expert-parallel roles of the tcgen05 kernel:
+  //   * `send` (dict, optional): sender CTAs copy this rank's token rows `x` (scaled by
+  //     `scale` when given) into the peers' receive buffers in the order of `pos` and publish
+  //     arrival flags — the dispatch direction of the exchange inside the GEMM launch;
+  //   * `gate_flags` / `seg_off` (optional): the A operand is this rank's receive buffer and
+  //     every tile waits for the arrival flags of its row block;
+  //   * `push_meta` / `ret_ptrs` (optional): result rows go straight into their source ranks'
+  //     return buffers and the return flags are raised when the grid is done.
+  void gemm_ep(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor offs,
+               c10::optional<torch::Tensor> out, c10::optional<torch::Tensor> bias,
+               c10::optional<torch::Tensor> pre_out, c10::optional<torch::Tensor> aux, int64_t act,
+               int64_t epi, c10::optional<torch::Tensor> push_meta, std::vector<int64_t> ret_ptrs,
+               int64_t push_slots, c10::optional<pybind11::dict> send,
+               std::vector<int64_t> gate_flag_ptrs, c10::optional<torch::Tensor> seg_off) {
     c10::cuda::CUDAGuard guard(a.device());
-    TORCH_CHECK(mode == fmoe::kRowsNT || mode == fmoe::kRowsNN, "gemm_push: row modes only");
+    TORCH_CHECK(mode == fmoe::kRowsNT || mode == fmoe::kRowsNN, "gemm_ep: row modes only");
     TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && offs.scalar_type() == torch::kInt,
-                "gemm_push: contiguous operands, int32 offsets");
+                "gemm_ep: contiguous operands, int32 offsets");
+    auto opt_ptr = [](const c10::optional<torch::Tensor>& t) -> void* {
+      return (t.has_value() && t->defined()) ? t->data_ptr() : nullptr;
+    };
     fmoe::GroupedGemmArgs g;
     g.mode = static_cast<int>(mode);
     g.dtype = dtype16(a);
@@ -192,22 +210,75 @@ class ExchangeContext {
     g.a = a.data_ptr();
     g.b = b.data_ptr();
     g.offs = offs.data_ptr<int>();
-    g.out = nullptr;
-    if (bias.has_value() && bias->defined()) g.bias = bias->data_ptr();
+    g.out = opt_ptr(out);
+    g.bias = opt_ptr(bias);
+    g.pre_out = opt_ptr(pre_out);
+    g.aux = opt_ptr(aux);
+    g.act = static_cast<int>(act);
+    g.epi = static_cast<int>(epi);
     g.status = ctx_.status;
-    g.push_meta = meta.data_ptr<int64_t>();
-    g.push_dst = to_ptrs(ret_ptrs);
-    g.push_flags = ctx_.flags;
-    g.push_epoch = ctx_.epoch;
-    g.push_counter = ctx_.epoch + 4;
-    g.push_me = ctx_.me;
-    g.push_world = ctx_.world;
+    if (push_meta.has_value() && push_meta->defined()) {
+      g.push_meta = push_meta->data_ptr<int64_t>();
+      g.push_dst = to_ptrs(ret_ptrs);
+      g.push_flags = ctx_.flags;
+      g.push_epoch = ctx_.epoch;
+      g.push_counter = ctx_.epoch + 4;
+      g.push_me = ctx_.me;
+      g.push_world = ctx_.world;
+      g.push_slots = push_slots;
+    } else {
+      TORCH_CHECK(g.out != nullptr, "gemm_ep: an output tensor or a push target is required");
+    }
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, a.device().index());
     g.num_sms = sms;
+    if (send.has_value()) {
+      const pybind11::dict& d = *send;
+      auto tensor = [&](const char* key) { return d[key].cast<torch::Tensor>(); };
+      auto ptrs = [&](const char* key) { return to_ptrs(d[key].cast<std::vector<int64_t>>()); };
+      fmoe::SendArgs& sa = g.send;
+      torch::Tensor x = tensor("x");
+      TORCH_CHECK(x.is_contiguous() && x.scalar_type() == a.scalar_type() &&
+                      reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0,
+                  "gemm_ep: rows to send must be contiguous, 16-byte aligned, of the GEMM's dtype");
+      sa.x = x.data_ptr();
+      sa.d = static_cast<int>(x.size(1));
+      sa.pos = tensor("pos").data_ptr<int>();
+      sa.my_offs = tensor("my_offs").data_ptr<int>();
+      sa.dst_base = tensor("dst_base").data_ptr<int>();
+      sa.seg_base = tensor("seg_base").data_ptr<int>();
+      sa.blk_base = tensor("blk_base").data_ptr<int>();
+      if (d.contains("scale") && !d["scale"].is_none()) sa.scale = tensor("scale").data_ptr();
+      sa.rows = ptrs("rows_ptrs");
+      if (d.contains("meta_ptrs") && !d["meta_ptrs"].is_none()) {
+        sa.meta = ptrs("meta_ptrs");
+      } else {
+        for (int i = 0; i < fmoe::kMaxPeers; ++i) sa.meta.p[i] = nullptr;
+      }
+      sa.flags = ptrs("flag_ptrs");
+      sa.epoch = ctx_.epoch;
+      sa.n_expert = d["n_expert"].cast<int>();
+      sa.world = ctx_.world;
+      sa.me = ctx_.me;
+      sa.k = d["k"].cast<int>();
+      sa.capacity = d["capacity"].cast<int>();
+      sa.n_ctas = d["n_ctas"].cast<int>();
+      TORCH_CHECK(sa.n_ctas > 0 && sa.n_ctas < sms, "gemm_ep: sender CTA count");
+      TORCH_CHECK(sa.d == g.k, "gemm_ep: sent rows must have the GEMM's K extent");
+    }
+    if (!gate_flag_ptrs.empty()) {
+      TORCH_CHECK(seg_off.has_value() && seg_off->defined() && seg_off->scalar_type() == torch::kInt,
+                  "gemm_ep: gating needs the per-source segment offsets");
+      g.gate.flags = reinterpret_cast<const int*>(gate_flag_ptrs[ctx_.me]);
+      g.gate.seg_off = seg_off->data_ptr<int>();
+      g.gate.epoch = ctx_.epoch;
+      g.gate.world = ctx_.world;
+      g.gate.me = ctx_.me;
+      g.gate.timeout_ns = ctx_.timeout_ns;
+    }
     g.stream = stream();
     TORCH_CHECK(fmoe::grouped_gemm_supported(g.mode, 0, g.n, g.k, g.num_groups),
-                "gemm_push: shape not supported by the tcgen05 kernel");
+                "gemm_ep: shape not supported by the tcgen05 kernel");
     FMOE_P2P_CHECK(fmoe::launch_grouped_gemm(g));
   }
 
@@ -256,7 +327,13 @@ void bind_p2p(pybind11::module& m) {
       .def("allgather", &ExchangeContext::allgather)
       .def("allreduce", &ExchangeContext::allreduce, py::arg("buf_ptrs"), py::arg("out"),
            py::arg("n"), py::arg("scale"), py::arg("two_shot") = false)
-      .def("gemm_push", &ExchangeContext::gemm_push)
+      .def("gemm_ep", &ExchangeContext::gemm_ep, py::arg("mode"), py::arg("a"), py::arg("b"),
+           py::arg("offs"), py::arg("out") = py::none(), py::arg("bias") = py::none(),
+           py::arg("pre_out") = py::none(), py::arg("aux") = py::none(), py::arg("act") = 0,
+           py::arg("epi") = 0, py::arg("push_meta") = py::none(),
+           py::arg("ret_ptrs") = std::vector<int64_t>(), py::arg("push_slots") = 0,
+           py::arg("send") = py::none(), py::arg("gate_flag_ptrs") = std::vector<int64_t>(),
+           py::arg("seg_off") = py::none())
       .def("wait_only", &ExchangeContext::wait_only);
   m.def("slot_dot", &slot_dot);
   m.attr("P2P_CHAN_COUNTS") = fmoe::kChanCounts;

@@ -79,7 +79,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false on time-out or when `*abort_flag` (shared memory, set by a
 // role that already gave up) becomes non-zero.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          const volatile int* abort_flag) {
+                                          const volatile int* abort_flag,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = 0;
   uint32_t spins = 0;
@@ -90,7 +91,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
       if (abort_flag != nullptr && *abort_flag != 0) return false;
       unsigned long long now = globaltimer();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) return false;
+      if (now - t0 > limit_ns) return false;
     }
   }
 }
@@ -115,6 +116,36 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, ui
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)),
       "r"(x), "r"(y)
       : "memory");
+}
+
+// Untiled bulk copies (both addresses 16-byte aligned, size a multiple of 16 bytes).
+// global -> shared, completion counted in bytes on an mbarrier of this CTA:
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// shared -> global (local or a peer's memory), tracked by the issuing thread's bulk groups:
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
+               "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// At most N of this thread's most recent bulk groups may still be reading shared memory.
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// At most N of this thread's most recent bulk groups may still be incomplete (writes not done).
+template <int N> __device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
 }
 
 // ----------------------------------------------------------------------------- tcgen05

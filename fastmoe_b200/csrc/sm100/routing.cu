@@ -26,8 +26,9 @@ __device__ __forceinline__ unsigned lanemask_lt() {
 // every slot its rank.  Within a warp slots are visited in order, 32 at a time.
 __global__ void __launch_bounds__(kRouteThreads, 1)
 route_kernel(const int64_t* __restrict__ idx, int n_slots, int tot, int nw, int* __restrict__ counts,
-             int* __restrict__ rank, int* __restrict__ offs) {
-  extern __shared__ int hist[];  // [nw][tot]
+             int* __restrict__ rank, int* __restrict__ offs, int* __restrict__ pos) {
+  extern __shared__ int hist[];  // [nw][tot], then [tot + 1] expert offsets when `pos` is wanted
+  int* eoff = hist + nw * tot;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < nw * tot; i += blockDim.x) hist[i] = 0;
@@ -59,8 +60,21 @@ route_kernel(const int64_t* __restrict__ idx, int n_slots, int tot, int nw, int*
       run += t;
     }
     counts[e] = run;
+    if (pos != nullptr) eoff[e + 1] = run;
   }
   __syncthreads();
+  if (pos != nullptr) {
+    // exclusive prefix of the counts: where the slots of every expert start in `pos`
+    if (threadIdx.x == 0) {
+      int run = 0;
+      eoff[0] = 0;
+      for (int e = 0; e < tot; ++e) {
+        run += eoff[e + 1];
+        eoff[e + 1] = run;
+      }
+    }
+    __syncthreads();
+  }
   if (warp < nw) {
     int* h = hist + warp * tot;
     for (int s0 = begin; s0 < end; s0 += 32) {
@@ -76,11 +90,14 @@ route_kernel(const int64_t* __restrict__ idx, int n_slots, int tot, int nw, int*
       if (valid && before == 0) h[key] += __popc(peers);
       __syncwarp();
       if (s < end) rank[s] = r;
+      if (pos != nullptr && valid) pos[eoff[key] + r] = s;
     }
   }
   if (offs != nullptr) {
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (pos != nullptr) {
+      for (int e = threadIdx.x; e <= tot; e += blockDim.x) offs[e] = eoff[e];
+    } else if (threadIdx.x == 0) {
       int run = 0;
       for (int e = 0; e < tot; ++e) {
         offs[e] = run;
@@ -756,20 +773,20 @@ cudaError_t simt_typed(int mode, int num_groups, long rows_cap, int m, int n, in
 
 // ------------------------------------------------------------------------------ launchers
 cudaError_t launch_route(const int64_t* idx, int n_slots, int tot, int* counts, int* rank,
-                         int* offs, cudaStream_t stream) {
+                         int* offs, int* pos, cudaStream_t stream) {
   if (tot <= 0) return cudaErrorInvalidValue;
-  int nw = kRouteSmemLimit / (4 * tot);
+  int nw = (kRouteSmemLimit - 4 * (tot + 1)) / (4 * tot);
   if (nw < 1) return cudaErrorInvalidValue;
   if (nw > 32) nw = 32;
   const int by_work = (n_slots + 31) / 32;
   if (nw > by_work) nw = by_work > 0 ? by_work : 1;
-  const size_t smem = static_cast<size_t>(nw) * tot * 4;
+  const size_t smem = static_cast<size_t>(nw) * tot * 4 + static_cast<size_t>(tot + 1) * 4;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kRouteSmemLimit);
     if (e != cudaSuccess) return e;
   }
-  route_kernel<<<1, kRouteThreads, smem, stream>>>(idx, n_slots, tot, nw, counts, rank, offs);
+  route_kernel<<<1, kRouteThreads, smem, stream>>>(idx, n_slots, tot, nw, counts, rank, offs, pos);
   return cudaGetLastError();
 }
 

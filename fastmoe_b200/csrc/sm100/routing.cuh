@@ -6,9 +6,11 @@
 namespace fmoe {
 
 // counts[tot] (int32), rank[n_slots] (int32, -1 for dropped slots), optional offs[tot + 1]
-// (exclusive prefix of counts).  Deterministic: slots of one expert are ranked by slot id.
+// (exclusive prefix of counts) and optional pos[n_slots] (slot ids sorted by expert, then by
+// rank: pos[offs[e] + rank[s]] = s; entries past offs[tot] are not written).  Deterministic:
+// slots of one expert are ranked by slot id.
 cudaError_t launch_route(const int64_t* idx, int n_slots, int tot, int* counts, int* rank,
-                         int* offs, cudaStream_t stream);
+                         int* offs, int* pos, cudaStream_t stream);
 
 // new_idx[s] = (idx[s] >= 0 && rank[s] < cap[idx[s]]) ? idx[s] : -1
 cudaError_t launch_prune(const int64_t* idx, const int* rank, const int* cap, int n_slots, int tot,

@@ -38,10 +38,17 @@ def supports(layer, x, idx):
     d, h = layer.d_model, layer.d_hidden
     if d % 64 != 0 or h % 64 != 0:
         return False
-    if layer.world_size > 1:
+    if layer.world_size > 1 or _forced_ep():
         from ..parallel import symm
         return symm.fused_available(layer, x)
     return True
+
+
+def _forced_ep():
+    if not config.force_ep_path():
+        return False
+    import torch.distributed as dist
+    return dist.is_available() and dist.is_initialized()
 
 
 class _Dispatch(Function):
@@ -141,7 +148,7 @@ def expert_mlp(layer, xs, offs):
 
 def moe_mlp_forward(layer, x, gate_idx, gate_score):
     r"""``[B, d] → [B, d]`` for one ``FMoETransformerMLP`` call on the GPU."""
-    if layer.world_size > 1:
+    if layer.world_size > 1 or _forced_ep():
         from ..parallel import symm
         return symm.moe_mlp_forward(layer, x, gate_idx, gate_score)
     nat = native.get()

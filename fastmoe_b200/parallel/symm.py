@@ -11,25 +11,32 @@ what the reference does with a private NCCL communicator obtained by subclassing
 
 One layer call is, per rank and without any host read:
 
-    route → count_exchange (counts to all peers; offsets from the full matrix)
-          → dispatch_push (rows + (source, slot) words into the owners' staging buffers)
-          → wait_copy     (arrival flags, rows into the tensor kept for backward)
-          → grouped GEMM 1 (+ bias, activation) on the received rows
+    route → count_exchange (counts to all peers; offsets and block tables from the full matrix)
+          → grouped GEMM 1 launch.  Its first CTAs are *senders*: they copy this rank's token
+            rows (+ (source, slot) words) into the owners' receive buffers with bulk copies
+            and raise one arrival flag per (128-row block, source).  The other CTAs run the
+            GEMM (+ bias, activation) straight out of the receive buffer, every tile waiting
+            only for the flags of its own row block: dispatch and GEMM 1 overlap tile by tile
           → grouped GEMM 2 whose epilogue stores every output row straight into its source
-            rank's slot-indexed staging buffer (`gemm_push`; `return_push` is the separate
-            kernel used when the second linear is not a plain grouped GEMM)
+            rank's slot-indexed return buffer and raises the return flags
           → wait_combine  (arrival flags, gate-weighted sum over the k slots of a token)
 
-Backward runs the same two exchanges with gradient rows; the received gradient rows are read
-in place (no copy out of staging) and the last input-gradient GEMM pushes from its epilogue.
-The module also holds the other peer-to-peer collectives: gradient all-reduce (one- and
-two-shot), all-gather of slice groups, capacity grants.  Staging buffers are shared by all
-layers: a rank can only start the next exchange after it has seen every peer's flags of the
-current one, and a peer only raises them after it is done reading, so no buffer is
-overwritten early.
+Backward runs the same two exchanges with gradient rows: the score-scaled output gradients
+are sent by the sender CTAs of the first input-gradient GEMM, the last input-gradient GEMM
+pushes from its epilogue.  Layers whose activation the GEMM epilogue does not know use the
+stand-alone dispatch / return kernels around PyTorch ops.  The module also holds the other
+peer-to-peer collectives: gradient all-reduce (one- and two-shot), all-gather of slice
+groups, capacity grants.
 
-Requirements of the fused path: one process per GPU on one NVLink domain, at most 16 ranks,
-and the same number of tokens on every rank of the group.
+Buffers.  The receive buffer of a layer call (rows kept for the weight gradient) is leased
+from a pool of symmetric allocations and handed back when the backward pass is done; the
+return buffer, the gradient receive buffer and the flag words are shared by all layers: a
+rank can only start the next exchange after it has seen every peer's flags of the current one,
+and a peer only raises them after it is done reading, so no buffer is overwritten early.
+All of them are sized from ONE token budget per group, agreed once (see ``token_budget``);
+ranks may bring different numbers of tokens as long as none exceeds the budget.
+
+Requirements of the fused path: one process per GPU on one NVLink domain, at most 16 ranks.
 """
 import math
 import os
@@ -67,10 +74,12 @@ class SymmWorkspace:
             raise RuntimeError("fused expert parallelism supports at most %d ranks" % nat.P2P_MAX_PEERS)
         self._buffers = {}
         self.signal, self.signal_ptrs = self._alloc("signal", nat.P2P_NUM_CHANNELS * nat.P2P_MAX_PEERS * 4)
-        self.cnt, self.cnt_ptrs = self._alloc("counts", self.world * _MAX_TOT_EXPERT * 4)
+        self.cnt, self.cnt_ptrs = self._alloc("counts", self.world * (_MAX_TOT_EXPERT + 1) * 4)
         self.signal.zero_()
         self.cnt.zero_()
         self.epoch = torch.zeros(8, dtype=torch.int32, device=device)
+        self._budget = None
+        self._pool = {}
         self.status = nat.status_word(device.index)
         self.ctx = nat.ExchangeContext(self.signal_ptrs, self.epoch, self.me, self.world,
                                        self.status, float(config.wait_timeout_ms()))
@@ -83,20 +92,120 @@ class SymmWorkspace:
         t = self._symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
         hdl = self._symm_mem.rendezvous(t, group=self.group)
         ptrs = [int(p) for p in hdl.buffer_ptrs]
+        # Never hand out uninitialised staging memory: kernels that continue after a peer's
+        # time-out would otherwise act on whatever bits the allocation held.
+        t.zero_()
         self._buffers[name] = (t, ptrs, hdl)
         return t, ptrs
 
-    def buffer(self, name, nbytes):
-        r"""Symmetric byte buffer of at least ``nbytes`` (collective when it has to grow)."""
+    def buffer(self, name, nbytes, zero=False):
+        r"""Symmetric byte buffer of at least ``nbytes`` (collective when it has to grow).
+
+        ``zero``: the buffer holds flag words that peers write; a new allocation is cleared and
+        all ranks meet before anybody may store into it."""
         have = self._buffers.get(name)
         if have is None or have[0].numel() < nbytes:
             torch.cuda.synchronize(self.device)
             self._alloc(name, max(nbytes, 1))
             have = self._buffers[name]
+            if zero:
+                have[0].zero_()
+                torch.cuda.synchronize(self.device)
+                dist.barrier(self.group)
         return have[0], have[1]
+
+    # ------------------------------------------------------------------ token budget
+    def token_budget(self, n_tokens):
+        r"""Tokens per rank that every exchange buffer of this group is sized for.
+
+        Fixed by ``FMOE_MAX_TOKENS`` when set; otherwise agreed once, at the first fused call,
+        as the maximum of the ranks' batch sizes (one small all-reduce and one host read, never
+        again afterwards).  Ranks may bring fewer tokens than the budget — and different
+        numbers of them — at any later call.  A rank that brings more cannot be served: the
+        peers' buffers are already sized, and growing them is a collective operation the other
+        ranks do not know they should join.  That case raises; call :func:`reserve_tokens` on
+        all ranks (or set ``FMOE_MAX_TOKENS``) before the larger batch."""
+        if self._budget is None:
+            fixed = config.max_tokens()
+            if fixed > 0:
+                self._budget = fixed
+            else:
+                t = torch.tensor([int(n_tokens)], dtype=torch.int64, device=self.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+                self._budget = int(t.item())
+        if n_tokens > self._budget:
+            raise RuntimeError(
+                "fastmoe_b200: this rank brings %d tokens to an expert-parallel exchange whose "
+                "buffers were sized for %d tokens per rank; call "
+                "fastmoe_b200.parallel.symm.reserve_tokens(group, n) on every rank, or set "
+                "FMOE_MAX_TOKENS, before using larger batches" % (n_tokens, self._budget))
+        return self._budget
+
+    def reserve(self, n_tokens):
+        r"""Collective: raise the token budget to the largest ``n_tokens`` any rank asks for."""
+        t = torch.tensor([int(n_tokens)], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        self._budget = max(self._budget or 0, int(t.item()))
+        return self._budget
+
+    # ------------------------------------------------------------------ per-call leases
+    def lease(self, nbytes):
+        r"""A symmetric buffer for one layer call (the rows a layer keeps for its backward).
+
+        Buffers come from a pool keyed by size; a new one is a collective allocation, which is
+        safe because all ranks run the same sequence of layer calls and hand leases back at the
+        same points (end of backward, or end of forward when no graph is recorded)."""
+        key = int(math.ceil(max(nbytes, 1) / (1 << 20))) << 20
+        free = self._pool.setdefault(key, [])
+        if free:
+            t, ptrs = free.pop()
+        else:
+            torch.cuda.synchronize(self.device)
+            t = self._symm_mem.empty(key, dtype=torch.uint8, device=self.device)
+            hdl = self._symm_mem.rendezvous(t, group=self.group)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            self._leased_handles = getattr(self, "_leased_handles", [])
+            self._leased_handles.append(hdl)
+            t.zero_()
+        return _Lease(self, key, t, ptrs)
+
+    def gate_flags(self, capacity, n_expert):
+        r"""Arrival flags of the receive buffer: int32 ``[blocks][P2P_MAX_PEERS]``."""
+        nat = native.get()
+        blocks = capacity // 128 + n_expert + 1
+        return self.buffer("gate", blocks * nat.P2P_MAX_PEERS * 4, zero=True)
 
     def set_timeout_ms(self, ms):
         self.ctx.set_timeout_ms(float(ms))
+
+
+class _Lease:
+    r"""One pooled symmetric buffer in use; ``release()`` (or garbage collection) returns it."""
+
+    def __init__(self, ws, key, tensor, ptrs):
+        self.ws, self.key, self.tensor, self.ptrs = ws, key, tensor, ptrs
+
+    def release(self):
+        if self.tensor is not None:
+            self.ws._pool[self.key].append((self.tensor, self.ptrs))  # pylint: disable=protected-access
+            self.tensor = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:  # pylint: disable=broad-except
+            pass
+
+
+def reserve_tokens(group, n_tokens, device=None):
+    r"""Collective over ``group``: make the fused expert-parallel path ready for batches of up to
+    ``n_tokens`` tokens per rank (the largest value any rank passes wins)."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    ws = get_workspace(group, device)
+    if ws is None:
+        return None
+    return ws.reserve(n_tokens)
 
 
 def get_workspace(group, device):
@@ -136,7 +245,8 @@ def fused_available(layer, x):
 
 
 def receive_capacity(n_tokens, k, world):
-    r"""Rows reserved for tokens arriving at one rank (see ``config.recv_capacity_factor``)."""
+    r"""Rows reserved for tokens arriving at one rank (see ``config.recv_capacity_factor``);
+    ``n_tokens`` is the group's token budget, so every rank computes the same number."""
     factor = config.recv_capacity_factor()
     worst = n_tokens * k * world
     if factor <= 0:
@@ -144,32 +254,52 @@ def receive_capacity(n_tokens, k, world):
     return min(worst, int(math.ceil(factor * n_tokens * k)))
 
 
+class _Tables:
+    r"""Device tables of one exchange, produced by the count-exchange kernel in one tensor."""
+
+    def __init__(self, ws, lec, n_expert, capacity):
+        tot = n_expert * ws.world
+        w1 = ws.world + 1
+        self.buf = torch.empty(3 * tot + (n_expert + 1) + n_expert * w1 + 1, dtype=torch.int32,
+                               device=lec.device)
+        ws.ctx.count_exchange(lec, ws.cnt_ptrs, n_expert, capacity, self.buf)
+        o = 0
+        self.dst_base = self.buf[o:o + tot]; o += tot          # noqa: E702
+        self.seg_base = self.buf[o:o + tot]; o += tot          # noqa: E702
+        self.blk_base = self.buf[o:o + tot]; o += tot          # noqa: E702
+        self.expert_offs = self.buf[o:o + n_expert + 1]; o += n_expert + 1  # noqa: E702
+        self.seg_off = self.buf[o:o + n_expert * w1]; o += n_expert * w1    # noqa: E702
+        self.total = self.buf[o:o + 1]
+
+
+def _rows_view(byte_tensor, rows, d, dtype):
+    es = torch.empty(0, dtype=dtype).element_size()
+    return byte_tensor[:rows * d * es].view(dtype).view(rows, d)
+
+
 class _DispatchP2P(Function):
     r"""Token rows → the owning ranks' expert segments (forward); row gradients back, summed
     over the k copies of a token (backward)."""
 
     @staticmethod
-    def forward(ctx, x, idx, rank, lec, ws, n_expert, k, capacity):
+    def forward(ctx, x, idx, rank, lec, ws, n_expert, k, capacity, budget):
         nat = native.get()
-        tot = n_expert * ws.world
         d = x.shape[1]
         dev = x.device
-        dst_base = torch.empty(tot, dtype=torch.int32, device=dev)
-        expert_offs = torch.empty(n_expert + 1, dtype=torch.int32, device=dev)
-        total = torch.empty(1, dtype=torch.int32, device=dev)
-        ws.ctx.count_exchange(lec, ws.cnt_ptrs, n_expert, capacity, dst_base, expert_offs, total)
+        tb = _Tables(ws, lec, n_expert, capacity)
         stage_rows, rows_ptrs = ws.buffer("rows", capacity * d * x.element_size())
         stage_meta, meta_ptrs = ws.buffer("meta", capacity * 8)
-        ws.ctx.dispatch_push(x, idx, rank, dst_base, None, rows_ptrs, meta_ptrs, n_expert, k, capacity)
+        ws.ctx.dispatch_push(x, idx, rank, tb.dst_base, None, rows_ptrs, meta_ptrs, n_expert, k, capacity)
         xs = torch.empty(capacity, d, dtype=x.dtype, device=dev)
         meta = torch.empty(capacity, dtype=torch.int64, device=dev)
-        ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, stage_meta.view(torch.int64), total, xs, meta)
+        ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, stage_meta.view(torch.int64), tb.total, xs, meta)
         ctx.ws = ws
         ctx.k = k
         ctx.n_tok = x.shape[0]
-        ctx.save_for_backward(idx, meta, total)
-        ctx.mark_non_differentiable(expert_offs, meta, total, dst_base)
-        return xs, expert_offs, meta, total, dst_base
+        ctx.budget = budget
+        ctx.save_for_backward(idx, meta, tb.total)
+        ctx.mark_non_differentiable(tb.expert_offs, meta, tb.total, tb.dst_base)
+        return xs, tb.expert_offs, meta, tb.total, tb.dst_base
 
     @staticmethod
     def backward(ctx, dxs, _g1, _g2, _g3, _g4):
@@ -177,11 +307,11 @@ class _DispatchP2P(Function):
         ws = ctx.ws
         dxs = dxs.contiguous()
         d = dxs.shape[1]
-        stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * dxs.element_size())
-        ws.ctx.return_push(dxs, meta, total, ret_ptrs)
+        stage_ret, ret_ptrs = ws.buffer("ret", ctx.budget * ctx.k * d * dxs.element_size())
+        ws.ctx.return_push(dxs, meta, total, ret_ptrs, ctx.budget * ctx.k)
         dx = torch.empty(ctx.n_tok, d, dtype=dxs.dtype, device=dxs.device)
         ws.ctx.wait_combine(stage_ret, idx, None, ctx.k, dx, None)
-        return dx, None, None, None, None, None, None, None
+        return (dx,) + (None,) * 8
 
 
 class _CombineP2P(Function):
@@ -189,11 +319,11 @@ class _CombineP2P(Function):
     ``d score`` and score-scaled output gradients to the owners (backward)."""
 
     @staticmethod
-    def forward(ctx, ys, score, idx, rank, dst_base, meta, total, ws, n_expert, k, capacity):
+    def forward(ctx, ys, score, idx, rank, dst_base, meta, total, ws, n_expert, k, capacity, budget):
         d = ys.shape[1]
         n_tok = idx.numel() // k
-        stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * ys.element_size())
-        ws.ctx.return_push(ys, meta, total, ret_ptrs)
+        stage_ret, ret_ptrs = ws.buffer("ret", budget * k * d * ys.element_size())
+        ws.ctx.return_push(ys, meta, total, ret_ptrs, budget * k)
         out = torch.empty(n_tok, d, dtype=ys.dtype, device=ys.device)
         y_slots = torch.empty(idx.numel(), d, dtype=ys.dtype, device=ys.device)
         ws.ctx.wait_combine(stage_ret, idx, score, k, out, y_slots)
@@ -218,110 +348,111 @@ class _CombineP2P(Function):
                              n_expert, k, capacity)
         dys = torch.empty(capacity, d, dtype=dout.dtype, device=dout.device)
         ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, None, total, dys, None)
-        return dys, dscore, None, None, None, None, None, None, None, None, None
+        return (dys, dscore) + (None,) * 10
 
 
 class _FusedEPMLP(Function):
     r"""The whole expert-parallel MLP as one autograd node (activations the GEMM epilogue knows).
 
-    Forward: count exchange → dispatch push → wait/copy → GEMM 1 (+bias, activation) → GEMM 2
-    whose epilogue stores every output row straight into the source rank's return buffer and
-    raises the return flags → wait + gate-weighted combine.  Backward: ``d score`` locally,
-    score-scaled output gradients pushed to the owners, bias/weight/input gradients of both
-    linears, and the last input-gradient GEMM again pushes its rows home, where the k copies of
-    a token are summed.  GEMM 2's result and the expert input gradient never exist as local
-    tensors.
+    Forward: count exchange → GEMM 1 launch (sender CTAs dispatch the rows, the other CTAs
+    compute tiles as their rows arrive; + bias, activation) → GEMM 2 whose epilogue stores every
+    output row straight into the source rank's return buffer and raises the return flags →
+    wait + gate-weighted combine.  Backward: ``d score`` locally; the first input-gradient GEMM
+    carries the sender CTAs for the score-scaled output gradients (and applies the activation
+    derivative), then both weight gradients, and the last input-gradient GEMM again pushes its
+    rows home, where the k copies of a token are summed.  GEMM 2's result and the expert input
+    gradient never exist as local tensors; received rows are never copied out of the buffer
+    they landed in.
     """
 
     @staticmethod
-    def forward(ctx, x, score, w1, b1, w2, b2, idx, rank, lec, ws, n_expert, k, capacity, act):
+    def forward(ctx, x, score, w1, b1, w2, b2, idx, rank, lec, my_offs, pos, ws, n_expert, k,
+                capacity, budget, act):
         from ..ops import grouped_gemm as gg
-        nat = native.get()
-        tot = n_expert * ws.world
         d = x.shape[1]
+        h = w1.shape[1]
         dev = x.device
-        dst_base = torch.empty(tot, dtype=torch.int32, device=dev)
-        expert_offs = torch.empty(n_expert + 1, dtype=torch.int32, device=dev)
-        total = torch.empty(1, dtype=torch.int32, device=dev)
+        es = x.element_size()
+        code = gg.ACT_CODES[act]
         with fused_range("ep.counts"):
-            ws.ctx.count_exchange(lec, ws.cnt_ptrs, n_expert, capacity, dst_base, expert_offs, total)
-        with fused_range("ep.dispatch"):
-            stage_rows, rows_ptrs = ws.buffer("rows", capacity * d * x.element_size())
-            stage_meta, meta_ptrs = ws.buffer("meta", capacity * 8)
-            ws.ctx.dispatch_push(x, idx, rank, dst_base, None, rows_ptrs, meta_ptrs, n_expert, k, capacity)
-            xs = torch.empty(capacity, d, dtype=x.dtype, device=dev)
-            meta = torch.empty(capacity, dtype=torch.int64, device=dev)
-            ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, stage_meta.view(torch.int64), total, xs, meta)
-
-        with fused_range("ep.gemm1"):
-            a, pre = gg.forward(xs, w1, expert_offs, b1, act=act, want_pre=True)
+            tb = _Tables(ws, lec, n_expert, capacity)
+        lease = ws.lease(capacity * d * es + capacity * 8)
+        xs = _rows_view(lease.tensor, capacity, d, x.dtype)
+        meta = lease.tensor[capacity * d * es:capacity * d * es + capacity * 8].view(torch.int64)
+        meta_ptrs = [p + capacity * d * es for p in lease.ptrs]
+        _flags, flag_ptrs = ws.gate_flags(capacity, n_expert)
+        send = dict(x=x, pos=pos, my_offs=my_offs, dst_base=tb.dst_base, seg_base=tb.seg_base,
+                    blk_base=tb.blk_base, rows_ptrs=lease.ptrs, meta_ptrs=meta_ptrs,
+                    flag_ptrs=flag_ptrs, n_expert=n_expert, k=k, capacity=capacity,
+                    n_ctas=config.send_ctas())
+        with fused_range("ep.dispatch_gemm1"):
+            a = torch.empty(capacity, h, dtype=x.dtype, device=dev)
+            pre = torch.empty(capacity, h, dtype=x.dtype, device=dev) if code != 0 else a
+            ws.ctx.gemm_ep(gg.MODE_NT, xs, w1, tb.expert_offs, out=a, bias=b1,
+                           pre_out=pre if code != 0 else None, act=code, send=send,
+                           gate_flag_ptrs=flag_ptrs, seg_off=tb.seg_off)
         with fused_range("ep.gemm2_push_combine"):
-            stage_ret, ret_ptrs = ws.buffer("ret", idx.numel() * d * x.element_size())
-            ws.ctx.gemm_push(gg.MODE_NT, a, w2, expert_offs, b2, meta, ret_ptrs)
+            n_slots_cap = budget * k
+            stage_ret, ret_ptrs = ws.buffer("ret", n_slots_cap * d * es)
+            ws.ctx.gemm_ep(gg.MODE_NT, a, w2, tb.expert_offs, bias=b2, push_meta=meta,
+                           ret_ptrs=ret_ptrs, push_slots=n_slots_cap)
             n_tok = x.shape[0]
             out = torch.empty(n_tok, d, dtype=x.dtype, device=dev)
             y_slots = torch.empty(idx.numel(), d, dtype=x.dtype, device=dev)
             ws.ctx.wait_combine(stage_ret, idx, score, k, out, y_slots)
 
         ctx.ws = ws
-        ctx.args = n_expert, k, capacity, act, n_tok
-        ctx.save_for_backward(xs, pre, a, w1, w2, expert_offs, meta, total, idx, rank, dst_base,
-                              score, y_slots)
+        ctx.args = n_expert, k, capacity, budget, act, n_tok
+        ctx.lease = lease
+        ctx.save_for_backward(xs, pre, a, w1, w2, tb.buf, meta, idx, my_offs, pos, score, y_slots)
+        ctx.tables = tb
+        if not any(ctx.needs_input_grad):
+            lease.release()  # nothing will run backward through this call
         return out
 
     @staticmethod
     def backward(ctx, dout):
         from ..ops import grouped_gemm as gg
         nat = native.get()
-        (xs, pre, a, w1, w2, expert_offs, meta, total, idx, rank, dst_base, score,
-         y_slots) = ctx.saved_tensors
-        n_expert, k, capacity, act, n_tok = ctx.args
+        (xs, pre, a, w1, w2, _tbuf, meta, idx, my_offs, pos, score, y_slots) = ctx.saved_tensors
+        n_expert, k, capacity, budget, act, n_tok = ctx.args
+        tb = ctx.tables
         ws = ctx.ws
         dout = dout.contiguous()
         d = dout.shape[1]
+        h = w1.shape[1]
+        es = dout.element_size()
+        code = gg.ACT_CODES[act]
         dscore = torch.empty_like(score)
         nat.slot_dot(dout, y_slots, idx, k, dscore)
         ws.ctx.begin_epoch()
-        stage_rows, rows_ptrs = ws.buffer("rows", capacity * d * dout.element_size())
-        ws.ctx.dispatch_push(dout, idx, rank, dst_base, score, rows_ptrs, [0] * ws.world,
-                             n_expert, k, capacity)
-        push_first = config.push_before_wgrad()
-        need_dx = ctx.needs_input_grad[0]
-        if push_first or not need_dx:
-            dys = torch.empty(capacity, d, dtype=dout.dtype, device=dout.device)
-            ws.ctx.wait_copy(nat.P2P_CHAN_DISPATCH, stage_rows, None, total, dys, None)
-        else:
-            # The received gradient rows are only read by the next two GEMMs, and no peer can
-            # write this staging buffer again before it has combined what this rank pushes at
-            # the very end of this backward (that push exists because dx is wanted, and it comes
-            # last in the default order): use the rows in place, no copy.
-            ws.ctx.wait_arrival(nat.P2P_CHAN_DISPATCH)
-            dys = stage_rows[:capacity * d * dout.element_size()].view(dout.dtype).view(capacity, d)
-
-        # Order of the four GEMMs: weight gradients between the two input-gradient GEMMs by
-        # default; `FMOE_PUSH_BEFORE_WGRAD` runs the input-gradient chain (whose last GEMM
-        # pushes the rows home from its epilogue) first.
-        dw2 = db2 = None
-        if not push_first:
-            dw2, db2 = gg.wgrad(dys, a, expert_offs, n_expert, with_bias_grad=True)
-        da = gg.dgrad(dys, w2, expert_offs, pre=pre, act=act)
+        # The gradient rows land in a buffer all layers share and are read in place by the next
+        # two GEMMs: no peer writes it again before it has combined what this rank pushes at the
+        # very end of this backward (or, when no input gradient is wanted, before the count
+        # exchange of the next forward).
+        stage_rows, rows_ptrs = ws.buffer("rows_bwd", capacity * d * es)
+        dys = _rows_view(stage_rows, capacity, d, dout.dtype)
+        _flags, flag_ptrs = ws.gate_flags(capacity, n_expert)
+        send = dict(x=dout, pos=pos, my_offs=my_offs, dst_base=tb.dst_base, seg_base=tb.seg_base,
+                    blk_base=tb.blk_base, scale=score, rows_ptrs=rows_ptrs, meta_ptrs=None,
+                    flag_ptrs=flag_ptrs, n_expert=n_expert, k=k, capacity=capacity,
+                    n_ctas=config.send_ctas())
+        da = torch.empty(capacity, h, dtype=dout.dtype, device=dout.device)
+        ws.ctx.gemm_ep(gg.MODE_NN, dys, w2, tb.expert_offs, out=da, aux=pre if code != 0 else None,
+                       act=code, epi=gg.EPI_DACT if code != 0 else gg.EPI_BIAS_ACT, send=send,
+                       gate_flag_ptrs=flag_ptrs, seg_off=tb.seg_off)
+        dw2, db2 = gg.wgrad(dys, a, tb.expert_offs, n_expert, with_bias_grad=True)
+        dw1, db1 = gg.wgrad(da, xs, tb.expert_offs, n_expert, with_bias_grad=True)
         dx = None
-
-        def push():
-            stage, ret_ptrs = ws.buffer("ret", idx.numel() * d * dout.element_size())
-            ws.ctx.gemm_push(gg.MODE_NN, da, w1, expert_offs, None, meta, ret_ptrs)
-            return stage
-
-        stage_ret = push() if (need_dx and push_first) else None
-        if push_first:
-            dw2, db2 = gg.wgrad(dys, a, expert_offs, n_expert, with_bias_grad=True)
-        dw1, db1 = gg.wgrad(da, xs, expert_offs, n_expert, with_bias_grad=True)
-        if need_dx:
-            if stage_ret is None:
-                stage_ret = push()
+        if ctx.needs_input_grad[0]:
+            n_slots_cap = budget * k
+            stage_ret, ret_ptrs = ws.buffer("ret", n_slots_cap * d * es)
+            ws.ctx.gemm_ep(gg.MODE_NN, da, w1, tb.expert_offs, push_meta=meta, ret_ptrs=ret_ptrs,
+                           push_slots=n_slots_cap)
             dx = torch.empty(n_tok, d, dtype=dout.dtype, device=dout.device)
             ws.ctx.wait_combine(stage_ret, idx, None, k, dx, None)
-        return (dx, dscore, dw1, db1, dw2, db2) + (None,) * 8
+        ctx.lease.release()
+        return (dx, dscore, dw1, db1, dw2, db2) + (None,) * 11
 
 
 def moe_mlp_forward(layer, x, gate_idx, gate_score):
@@ -332,22 +463,25 @@ def moe_mlp_forward(layer, x, gate_idx, gate_score):
     ws = get_workspace(_layer_group(layer), x.device)
     k = gate_idx.shape[1]
     n_expert = layer.num_expert
+    budget = ws.token_budget(x.shape[0])
     idx = gate_idx.contiguous().view(-1)
     score = gate_score.reshape(-1).to(x.dtype)
-    lec, rank = nat.route(idx, n_expert * ws.world)
+    lec, rank, my_offs, pos = nat.route_pos(idx, n_expert * ws.world)
     if config.debug_bounds():
         from ..utils.profiling import check_routing
         check_routing(idx, rank, lec, n_expert * ws.world)
-    capacity = receive_capacity(x.shape[0], k, ws.world)
+    capacity = receive_capacity(budget, k, ws.world)
     act = activation_kind(layer.experts.activation)
     if act is not None:
         e = layer.experts
         return _FusedEPMLP.apply(x.contiguous(), score, e.htoh4.weight, e.htoh4.bias, e.h4toh.weight,
-                                 e.h4toh.bias, idx, rank, lec, ws, n_expert, k, capacity, act)
+                                 e.h4toh.bias, idx, rank, lec, my_offs, pos, ws, n_expert, k,
+                                 capacity, budget, act)
     xs, expert_offs, meta, total, dst_base = _DispatchP2P.apply(
-        x.contiguous(), idx, rank, lec, ws, n_expert, k, capacity)
+        x.contiguous(), idx, rank, lec, ws, n_expert, k, capacity, budget)
     ys = fused.expert_mlp(layer, xs, expert_offs)
-    return _CombineP2P.apply(ys, score, idx, rank, dst_base, meta, total, ws, n_expert, k, capacity)
+    return _CombineP2P.apply(ys, score, idx, rank, dst_base, meta, total, ws, n_expert, k, capacity,
+                             budget)
 
 
 # ------------------------------------------------------------------------------------------

@@ -9,7 +9,7 @@ import torch
 
 from dist_launch import run_ranks
 
-pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+pytestmark = [pytest.mark.gpu]
 
 # NVLS is switched off for these runs: no kernel here uses multimem, and a rank that died
 # while bound to a multicast object could disturb the other GPUs.
@@ -23,7 +23,8 @@ def _need(world):
         pytest.skip("needs %d GPUs" % world)
 
 
-@pytest.mark.parametrize("case", ["fused_vs_general", "allreduce", "grouped_ddp", "wait_timeout",
+@pytest.mark.parametrize("case", ["fused_vs_general", "oracle", "uneven_tokens", "multi_layer",
+                                  "recv_overflow", "allreduce", "grouped_ddp", "wait_timeout",
                                   "graph_step", "smart_schedule", "slice_group", "capacity"])
 def test_two_ranks(case):
     _need(2)
@@ -31,12 +32,27 @@ def test_two_ranks(case):
     assert codes == [0, 0], codes
 
 
-@pytest.mark.parametrize("case", ["fused_vs_general", "allreduce", "slice_group", "capacity"])
+@pytest.mark.parametrize("case", ["fused_vs_general", "oracle", "multi_layer", "allreduce",
+                                  "slice_group", "capacity", "smart_schedule"])
 def test_many_ranks(case):
     world = int(os.environ.get("FMOE_TEST_WORLD", "4"))
     _need(world)
     codes = run_ranks("dist_gpu_worker.py", case, world, timeout=TIMEOUT, extra_env=ENV)
     assert codes == [0] * world, codes
+
+
+@pytest.mark.parametrize("case", ["fused_vs_general", "oracle", "multi_layer", "graph_step"])
+def test_one_rank_group(case):
+    r"""The expert-parallel kernels (sender CTAs, arrival-gated tiles, return push, flags) in a
+    one-rank process group: every peer table points at this GPU, so one GPU runs exactly the
+    code of the multi-GPU path."""
+    pytest.importorskip("torch")
+    if not torch.cuda.is_available():
+        pytest.skip("no GPU")
+    env = dict(ENV)
+    env["FMOE_FORCE_EP"] = "1"
+    codes = run_ranks("dist_gpu_worker.py", case, 1, timeout=TIMEOUT, extra_env=env)
+    assert codes == [0], codes
 
 
 def test_data_parallel_in_one_process():

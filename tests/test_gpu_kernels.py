@@ -36,6 +36,7 @@ def _tol(dtype, k):
     ([128, 0, 257, 5], 128, 256),
     ([300, 1, 511], 256, 320),
     ([1000, 24], 1024, 512),
+    ([513, 130], 4096, 96),
 ])
 def test_grouped_gemm_forward(dtype, counts, k, n):
     from fastmoe_b200.ops import grouped_gemm as gg
@@ -52,6 +53,39 @@ def test_grouped_gemm_forward(dtype, counts, k, n):
         ref = torch.nn.functional.gelu(ref_pre)
         assert torch.allclose(pre[lo:hi].float(), ref_pre, atol=_tol(dtype, k), rtol=2e-2)
         assert torch.allclose(out[lo:hi].float(), ref, atol=_tol(dtype, k), rtol=2e-2)
+    assert _native().read_status(0) == 0
+
+
+@pytest.mark.parametrize("act", [None, "relu", "gelu_tanh"])
+@pytest.mark.parametrize("counts,k,n", [([70, 300, 129], 192, 416), ([2048, 2048], 4096, 1024)])
+def test_grouped_gemm_epilogues(act, counts, k, n):
+    r"""The other fused epilogues, forward and input gradient, including a span of columns that
+    is not a multiple of the 256-column tile and a K of 4096."""
+    from fastmoe_b200.ops import grouped_gemm as gg
+    torch.manual_seed(5)
+    dtype = torch.bfloat16
+    rows = sum(counts)
+    x = torch.randn(rows, k, device=DEV, dtype=dtype)
+    w = (torch.randn(len(counts), n, k, device=DEV) / k ** 0.5).to(dtype)
+    b = torch.randn(len(counts), n, device=DEV).to(dtype)
+    offs = _offs(counts)
+    out, pre = gg.forward(x, w, offs, b, act=act, want_pre=True)
+    fn = {None: lambda t: t, "relu": torch.relu,
+          "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh")}[act]
+    dy = torch.randn(rows, n, device=DEV, dtype=dtype)
+    wt = (torch.randn(len(counts), n, k, device=DEV) / n ** 0.5).to(dtype)   # [E, k(out)=n, n(in)=k]
+    pre_in = torch.randn(rows, k, device=DEV, dtype=dtype)
+    dx = gg.dgrad(dy, wt, offs, pre=pre_in if act else None, act=act)
+    p32 = pre_in.float().requires_grad_(True)
+    fn(p32).sum().backward()
+    for e, lo, hi in _segments(counts):
+        ref_pre = x[lo:hi].float() @ w[e].float().t() + b[e].float()
+        assert torch.allclose(pre[lo:hi].float(), ref_pre, atol=2e-2, rtol=2e-2)
+        assert torch.allclose(out[lo:hi].float(), fn(ref_pre), atol=2e-2, rtol=2e-2)
+        ref_dx = dy[lo:hi].float() @ wt[e].float()
+        if act:
+            ref_dx = ref_dx * p32.grad[lo:hi]
+        assert torch.allclose(dx[lo:hi].float(), ref_dx, atol=2e-2, rtol=2e-2)
     assert _native().read_status(0) == 0
 
 
@@ -117,6 +151,15 @@ def test_grouped_gemm_wgrad(dtype, counts, m, n):
         acc_b = bg2.clone()
         _native().grouped_gemm(gg.MODE_WGRAD, dy, x, offs, acc_w, None, None, None, 0, 0, True, acc_b)
         assert torch.allclose(acc_b.float(), 2 * bg2.float(), atol=0.6, rtol=3e-2)
+        for e, lo, hi in _segments(counts):
+            scale = max(1.0, (hi - lo) ** 0.5)
+            assert torch.allclose(acc_w[e].float(), 2 * out[e].float(), atol=_tol(dtype, 0) * 2 * scale,
+                                  rtol=3e-2), e
+        acc32 = torch.ones(len(counts), m, n, device=DEV, dtype=torch.float32)
+        _native().grouped_gemm(gg.MODE_WGRAD, dy, x, offs, acc32, None, None, None, 0, 0, True, None)
+        for e, lo, hi in _segments(counts):
+            ref = 1.0 + dy[lo:hi].float().t() @ x[lo:hi].float()
+            assert torch.allclose(acc32[e], ref, atol=1e-2 * max(1.0, (hi - lo) ** 0.5), rtol=1e-2), e
     assert _native().read_status(0) == 0
 
 
