@@ -11,8 +11,9 @@ N > 1, and a fused Adam step on all parameters.  Weak scaling: per-GPU work is f
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N ...                 # N > 1
 
-Timing: the GPU is first brought to its working clocks by one second of bf16 matrix products
-(both arms alike, not steps of the model), then exactly W warm-up steps run (W >= 3), then every
+Timing: the GPU is first brought to its working clocks by one second of the step itself (both
+arms alike; parameters and optimizer state are restored afterwards, and these steps are reported
+as pre-heat, not as warm-up), then exactly W warm-up steps run (W >= 3), then every
 one of the K timed steps is bracketed by CUDA events on the launching stream; an L2 flush (a
 256 MiB fill) runs between steps outside the events; the K per-step times are summed per rank
 and the maximum over ranks is reported.  SM clocks and throttle reasons are sampled with
@@ -276,15 +277,40 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    # Clock ramp: one second of dense bf16 products, the same for both arms; not model steps.
-    heat_a = torch.randn(4096, 4096, device=device, dtype=torch.bfloat16)
-    heat_b = torch.randn(4096, 4096, device=device, dtype=torch.bfloat16)
-    t_heat = time.perf_counter()
-    while time.perf_counter() - t_heat < PREHEAT_S:
-        for _ in range(20):
-            heat_a @ heat_b
+    # Clock ramp: the step itself, run for PREHEAT_S seconds (both arms alike), so that the timed
+    # steps see the clocks of sustained training.  Parameters and optimizer state are put back
+    # afterwards: the warm-up and the timed steps start from the random-init weights.
+    def snapshot():
+        tensors = [p.data for p in layer.parameters()]
+        for o in (opt, opt_local):
+            if o is not None:
+                for st in o.state.values():
+                    tensors.extend(v for v in st.values() if torch.is_tensor(v))
+        return tensors, [t.clone() for t in tensors]
+
+    preheat_steps = 0
+    try:
+        step(dev_inputs[0])          # creates the optimizer state that the snapshot covers
         torch.cuda.synchronize()
-    del heat_a, heat_b
+        live, saved = snapshot()
+        t_heat = time.perf_counter()
+        while time.perf_counter() - t_heat < PREHEAT_S:
+            for _ in range(4):
+                step(dev_inputs[preheat_steps % n_inputs])
+                preheat_steps += 1
+            torch.cuda.synchronize()
+        with torch.no_grad():
+            for t, s0 in zip(live, saved):
+                t.copy_(s0)
+        del saved
+    except Exception as exc:  # pylint: disable=broad-except
+        if rank == 0:
+            sampler.stop()
+        if args.impl == "reference":
+            if rank == 0:
+                emit({"impl": "reference", "unavailable": "reference step failed: %r" % (exc,)})
+            return
+        raise
 
     warm_steps = max(args.warmup, 3)
     try:
@@ -432,7 +458,8 @@ def main():
                 "allreduce_overlap": ("gate-gradient all-reduce on a side stream, overlapped with the"
                                       " Adam update of the expert parameters (same Adam, two optimizer"
                                       " objects)") if overlap else "none",
-                "preheat": "%.1f s of bf16 matrix products before the warm-up steps" % PREHEAT_S,
+                "preheat": "%.1f s of the same step before the warm-up steps (%d steps); parameters and"
+                           " optimizer state restored afterwards" % (PREHEAT_S, preheat_steps),
                 "eager_ms_per_step": (eager_max / args.steps) if graphed else None,
             },
             "clocks": clocks,

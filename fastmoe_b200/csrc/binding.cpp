@@ -222,14 +222,23 @@ void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor 
     TORCH_CHECK(aligned32(*bias), "grouped_gemm: bias must be 32-byte aligned");
     g.bias = bias->data_ptr();
   }
+  // The pre-activation (written as pre_out, read back as aux) is tile-blocked: one 128 x 256
+  // block per output tile, (ceil(rows / 128) + groups) * ceil(n / 256) blocks at most.
+  const int64_t pre_elems = mode == fmoe::kWgrad ? 0
+      : ((a.size(0) + 127) / 128 + g.num_groups) * ((g.n + 255) / 256) * (128 * 256);
   if (pre_out.has_value() && pre_out->defined()) {
     check_cuda_contig(*pre_out, "pre_out");
-    TORCH_CHECK(aligned32(*pre_out), "grouped_gemm: pre_out must be 32-byte aligned");
+    TORCH_CHECK(aligned32(*pre_out) && pre_out->numel() >= pre_elems &&
+                    pre_out->scalar_type() == a.scalar_type(),
+                "grouped_gemm: pre_out must be a 32-byte aligned tile-blocked buffer of ", pre_elems,
+                " elements");
     g.pre_out = pre_out->data_ptr();
   }
   if (aux.has_value() && aux->defined()) {
     check_cuda_contig(*aux, "aux");
-    TORCH_CHECK(aligned32(*aux), "grouped_gemm: aux must be 32-byte aligned");
+    TORCH_CHECK(aligned32(*aux) && aux->numel() >= pre_elems && aux->scalar_type() == a.scalar_type(),
+                "grouped_gemm: aux must be a 32-byte aligned tile-blocked buffer of ", pre_elems,
+                " elements");
     g.aux = aux->data_ptr();
   }
   if (psum.has_value() && psum->defined()) {

@@ -110,7 +110,7 @@ struct GroupedGemmArgs {
 };
 
 // Returns cudaSuccess or the launch error; shape requirements: k % 64 == 0 (row modes),
-// n % 32 == 0, m % 8 == 0 (wgrad), num_groups <= 1024, 16-byte aligned base pointers.
+// n % 32 == 0, m % 8 == 0 (wgrad), num_groups <= 256, 16-byte aligned base pointers.
 cudaError_t launch_grouped_gemm(const GroupedGemmArgs& args);
 
 bool grouped_gemm_supported(int mode, int m, int n, int k, int num_groups);

@@ -6,21 +6,21 @@
 // bias, activation, activation-derivative and dtype conversion into its epilogue.
 //
 // Structure of a CTA (384 threads = 3 warpgroups, one CTA per SM, persistent over tiles):
-//   warp 0      TMA producer: plain cp.async.bulk.tensor loads into a ring of 128-byte-swizzled
-//               shared-memory tiles (3 stages in the row modes, 4 in the weight-gradient
-//               mode), completion on mbarriers;
+//   warp 0      TMA producer: plain cp.async.bulk.tensor loads into a 4-stage ring of
+//               128-byte-swizzled shared-memory tiles, completion on mbarriers;
 //   warp 1      one elected thread issues tcgen05.mma (128 x 256 x 16 per instruction, fp32
 //               accumulators in TMEM) and tcgen05.commit; the warp owns the TMEM allocation;
 //   warps 2-3   idle (they complete the first warpgroup);
 //   warps 4-11  epilogue (two warpgroups): two warps per TMEM lane quarter.  Row modes: each
 //               warp owns 32 rows x 128 columns of the tile; the tcgen05.ld of chunk i+1 and
-//               the cp.async staging of the side operand (saved pre-activation) for chunk
-//               i+1 are in flight while chunk i gets bias / activation / derivative and is
-//               written into the lane's row of a per-warp shared-memory patch; every lane
-//               then sends its row piece (128 or 256 contiguous bytes) to global memory with
-//               one bulk asynchronous store, local or into a peer's return buffer over NVLink,
-//               and does not wait for it.  Weight-gradient mode: alternate 32-column chunks,
-//               32-byte stores.
+//               the load of its saved pre-activation are in flight while chunk i gets bias /
+//               activation / derivative and is written into the lane's row of a swizzled
+//               per-warp shared-memory patch; after every second chunk the warp stores whole
+//               128-byte lines of the 32 rows (8 lanes per row), locally or into a peer's
+//               return buffer over NVLink.  The pre-activation is kept in a tile-blocked
+//               layout that both its producer and its consumer access with fully coalesced
+//               16-byte accesses straight from registers.  Weight-gradient mode: alternate
+//               32-column chunks, 32-byte stores.
 // Two 256-column accumulators (all 512 TMEM columns) let the epilogue of tile i overlap the
 // main loop of tile i+1.
 //
@@ -54,14 +54,12 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;        // ring slots the barrier arrays are sized for
-constexpr int STAGES_ROWS = 3;   // row modes: 3 x 48 KB, the rest of shared memory holds the store patches
-constexpr int STAGES_WGRAD = 4;
+constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;      // 16 KB
 constexpr int B_BYTES = BN * BK * 2;      // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64-wide MN-major box: 8 KB
-constexpr int MAX_GROUPS = 1024;
+constexpr int MAX_GROUPS = 256;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int FIRST_EPI_WARP = 4;
 constexpr int NUM_THREADS = (FIRST_EPI_WARP + NUM_EPI_WARPS) * 32;
@@ -71,8 +69,13 @@ constexpr int NUM_THREADS = (FIRST_EPI_WARP + NUM_EPI_WARPS) * 32;
 constexpr int CHUNKS_PER_WARP = BN / 32 / 2;  // 4 chunks of 32 columns per epilogue warp
 constexpr int SIDE_PITCH = 80;                // bytes per staged row (64 data + 16 pad: no bank conflicts)
 constexpr int SIDE_BYTES = 32 * SIDE_PITCH;   // weight-gradient mode: one 32-row x 32-column patch per epilogue warp
-constexpr int PATCH_PITCH = 272;              // row modes: 256 bytes of a row piece + 16 pad (16-byte lanes spread over all banks)
-constexpr int PATCH_BYTES = 32 * PATCH_PITCH; // 32 rows x 128 columns per epilogue warp
+constexpr int PATCH_PITCH = 128;              // row modes: one 128-byte line (two 32-column chunks) of a row, 16-byte pieces XOR-swizzled by row
+constexpr int PATCH_BYTES = 32 * PATCH_PITCH; // 32 rows per epilogue warp
+// Tile-blocked layout of the saved pre-activation: per output tile 8 warps x 4 chunks x 2 KB,
+// each 2 KB being 4 pieces x 32 lanes x 16 bytes in exactly the order the epilogue threads
+// produce (first GEMM) and consume (activation derivative of the input-gradient GEMM) them.
+constexpr int PRE_TILE_BYTES = BM * BN * 2;
+constexpr int PRE_CHUNK_BYTES = 32 * 64;
 constexpr int TMEM_COLS = 512;
 
 // Sender CTAs: every warp owns a ring of SEND_SLOTS pieces of at most SEND_PIECE bytes.
@@ -104,12 +107,11 @@ struct SharedAux {
 constexpr int AUX_BYTES = (static_cast<int>(sizeof(SharedAux)) + 127) & ~127;
 constexpr int BIAS_BYTES = CHUNKS_PER_WARP * 64;  // per epilogue warp: its four 32-column bias slices
 template <int MODE> struct Layout {
-  static constexpr int kStages = (MODE == kWgrad) ? STAGES_WGRAD : STAGES_ROWS;
+  static constexpr int kStages = STAGES;
   static constexpr int kPatch = (MODE == kWgrad) ? SIDE_BYTES : PATCH_BYTES;
   static constexpr int kAuxOff = kStages * STAGE_BYTES;
   static constexpr int kEpiOff = kAuxOff + AUX_BYTES;
-  static constexpr int kBiasOff = kEpiOff + NUM_EPI_WARPS * kPatch;
-  static constexpr int kBytes = kBiasOff + NUM_EPI_WARPS * BIAS_BYTES + 1024;
+  static constexpr int kBytes = kEpiOff + NUM_EPI_WARPS * kPatch + 1024;
 };
 static_assert(Layout<kRowsNT>::kBytes <= 232448 && Layout<kWgrad>::kBytes <= 232448, "shared memory");
 // What a sender CTA lays over the same dynamic shared memory.
@@ -484,122 +486,132 @@ __device__ __forceinline__ void epilogue_tile(const KernelParams& p, const EpiTi
 
 
 // ------------------------------------------------------------------------------------------
-// Row modes: epilogue through a shared-memory patch and bulk asynchronous stores.
+// Row modes: outputs leave through a shared-memory patch as whole 128-byte lines.
 // ------------------------------------------------------------------------------------------
 struct RowTile {
   uint32_t t_row;          // TMEM address: this warp's lane quarter, first column of its span
   int lane;
   int col_first;           // first output column of this warp's 128-column span
   int n_chunks;            // valid 32-column chunks of the span (0..4)
-  int warp_valid;          // valid rows of this warp (0..32)
   bool row_ok;
-  bool use_aux;            // multiply by the activation derivative of the staged side operand
-  const uint8_t* side;     // side operand at (first row of the warp, col_first)
-  long side_pitch;
-  uint8_t* patch;          // this warp's 32 x PATCH_PITCH bytes
+  bool use_aux;            // multiply by the activation derivative of the saved pre-activation
+  uint8_t* patch;          // this warp's 32 rows x 128 bytes
   uint8_t* out_row;        // column 0 of this lane's output row (local or a peer's); null = no store
-  uint8_t* pre_row;        // column 0 of this lane's pre-activation row, or null
-  const uint8_t* bias_sm;  // 4 x 64 bytes of bias for the span, or null
+  uint8_t* pre_tile;       // this warp's 4 x 2 KB of the tile-blocked pre-activation (out or in), or null
+  const uint8_t* bias;     // bias of the span's first column (global memory), or null
   uint64_t* empty_bar;
 };
 
-// Bias / activation (or activation derivative) of one 32-column chunk; the results go into
-// the lane's own row of the patch.
+// 16-byte piece `c` (0..7) of patch row `row`; pieces are XOR-swizzled so that 32 lanes writing
+// the same piece of 32 different rows, and 8 lanes reading the 8 pieces of one row, are both
+// free of bank conflicts.
+__device__ __forceinline__ uint8_t* patch_piece(uint8_t* patch, int row, int c) {
+  return patch + row * PATCH_PITCH + ((c ^ (row & 7)) << 4);
+}
+
+__device__ __forceinline__ void load_pre_chunk(const uint8_t* pre_tile, int i, int lane, Packed32& d) {
+  const uint8_t* base = pre_tile + i * PRE_CHUNK_BYTES + lane * 16;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint4 w = __ldg(reinterpret_cast<const uint4*>(base + q * 512));
+    d.w[q * 4 + 0] = w.x;
+    d.w[q * 4 + 1] = w.y;
+    d.w[q * 4 + 2] = w.z;
+    d.w[q * 4 + 3] = w.w;
+  }
+}
+
+// Bias / activation (or activation derivative) of one 32-column chunk.  The output values go
+// into the lane's own row of the patch (half (i & 1) of the line); the pre-activation, when
+// wanted, goes straight to its tile-blocked buffer with fully coalesced 16-byte stores.
 template <typename T, int ACT>
 __device__ __forceinline__ void rows_chunk(const RowTile& rt, int i, bool with_pre,
                                            const uint32_t (&r)[32], const Packed32& side_cur) {
-  uint8_t* my = rt.patch + rt.lane * PATCH_PITCH;
-  uint8_t* dst = my + (with_pre ? (i & 1) : i) * 64;
-  if (rt.use_aux) {
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      uint32_t w[8];
+  for (int q = 0; q < 2; ++q) {
+    uint32_t wo[8];
+    if (rt.use_aux) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float sa, sb;
         Cvt<T>::unpack(side_cur.w[q * 8 + j], sa, sb);
         const float a = __uint_as_float(r[q * 16 + 2 * j]) * act_grad<ACT>(sa);
         const float b = __uint_as_float(r[q * 16 + 2 * j + 1]) * act_grad<ACT>(sb);
-        w[j] = Cvt<T>::pack(a, b);
+        wo[j] = Cvt<T>::pack(a, b);
       }
-      *reinterpret_cast<uint4*>(dst + q * 32) = make_uint4(w[0], w[1], w[2], w[3]);
-      *reinterpret_cast<uint4*>(dst + q * 32 + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-    }
-    return;
-  }
-  const uint8_t* bias = rt.bias_sm == nullptr ? nullptr : rt.bias_sm + i * 64;
+    } else {
+      uint32_t bw[8];
+      if (rt.bias != nullptr) {
+        const uint4 b0 = __ldg(reinterpret_cast<const uint4*>(rt.bias + i * 64 + q * 32));
+        const uint4 b1 = __ldg(reinterpret_cast<const uint4*>(rt.bias + i * 64 + q * 32 + 16));
+        bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w;
+        bw[4] = b1.x; bw[5] = b1.y; bw[6] = b1.z; bw[7] = b1.w;
+      }
+      uint32_t wp[8];
 #pragma unroll
-  for (int q = 0; q < 2; ++q) {
-    uint32_t bw[8];
-    if (bias != nullptr) {
-      const uint4 b0 = *reinterpret_cast<const uint4*>(bias + q * 32);
-      const uint4 b1 = *reinterpret_cast<const uint4*>(bias + q * 32 + 16);
-      bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w;
-      bw[4] = b1.x; bw[5] = b1.y; bw[6] = b1.z; bw[7] = b1.w;
-    }
-    uint32_t wp[8], wo[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float a = __uint_as_float(r[q * 16 + 2 * j]);
-      float b = __uint_as_float(r[q * 16 + 2 * j + 1]);
-      if (bias != nullptr) {
-        float ba, bb;
-        Cvt<T>::unpack(bw[j], ba, bb);
-        a += ba;
-        b += bb;
+      for (int j = 0; j < 8; ++j) {
+        float a = __uint_as_float(r[q * 16 + 2 * j]);
+        float b = __uint_as_float(r[q * 16 + 2 * j + 1]);
+        if (rt.bias != nullptr) {
+          float ba, bb;
+          Cvt<T>::unpack(bw[j], ba, bb);
+          a += ba;
+          b += bb;
+        }
+        if (ACT != kActNone) {
+          wp[j] = Cvt<T>::pack(a, b);
+          a = act_fwd<ACT>(a);
+          b = act_fwd<ACT>(b);
+        }
+        wo[j] = Cvt<T>::pack(a, b);
       }
-      if (ACT != kActNone) {
-        wp[j] = Cvt<T>::pack(a, b);
-        a = act_fwd<ACT>(a);
-        b = act_fwd<ACT>(b);
+      if (ACT != kActNone && with_pre) {
+        uint8_t* pd = rt.pre_tile + i * PRE_CHUNK_BYTES + rt.lane * 16 + q * 1024;
+        *reinterpret_cast<uint4*>(pd) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+        *reinterpret_cast<uint4*>(pd + 512) = make_uint4(wp[4], wp[5], wp[6], wp[7]);
       }
-      wo[j] = Cvt<T>::pack(a, b);
     }
-    if (ACT != kActNone && with_pre) {
-      uint8_t* pd = my + 128 + (i & 1) * 64 + q * 32;
-      *reinterpret_cast<uint4*>(pd) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-      *reinterpret_cast<uint4*>(pd + 16) = make_uint4(wp[4], wp[5], wp[6], wp[7]);
+    if (rt.row_ok) {
+      const int c = (i & 1) * 4 + q * 2;
+      *reinterpret_cast<uint4*>(patch_piece(rt.patch, rt.lane, c)) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+      *reinterpret_cast<uint4*>(patch_piece(rt.patch, rt.lane, c + 1)) = make_uint4(wo[4], wo[5], wo[6], wo[7]);
     }
-    *reinterpret_cast<uint4*>(dst + q * 32) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
-    *reinterpret_cast<uint4*>(dst + q * 32 + 16) = make_uint4(wo[4], wo[5], wo[6], wo[7]);
   }
 }
 
-// After chunk i has been written: send what is complete.  Without a pre-activation output the
-// whole span (up to 256 bytes per row) leaves once, after the last chunk; with one, the patch
-// row holds a pair of output chunks and the pair of pre-activation chunks, and both leave
-// after every second chunk (128 bytes each).
-__device__ __forceinline__ void rows_send(const RowTile& rt, int i, bool with_pre) {
+// After an odd chunk (or the last one): the line of every valid row goes to its destination,
+// 8 lanes per row with 16-byte accesses, four rows per instruction — whole 128-byte lines,
+// local or over NVLink.
+__device__ __forceinline__ void rows_send(const RowTile& rt, int i) {
   const bool last = i + 1 == rt.n_chunks;
-  if (with_pre) {
-    if (!(last || (i & 1))) return;
-    if (rt.row_ok && rt.out_row != nullptr) {
-      uint8_t* my = rt.patch + rt.lane * PATCH_PITCH;
-      const uint32_t bytes = ((i & 1) + 1) * 64;
-      const long col = rt.col_first + (i & ~1) * 32;
-      ptx::fence_proxy_async_smem();
-      ptx::bulk_store(rt.out_row + col * 2, my, bytes);
-      ptx::bulk_store(rt.pre_row + col * 2, my + 128, bytes);
-      ptx::bulk_commit();
-    }
-  } else if (last) {
-    if (rt.row_ok && rt.out_row != nullptr) {
-      uint8_t* my = rt.patch + rt.lane * PATCH_PITCH;
-      ptx::fence_proxy_async_smem();
-      ptx::bulk_store(rt.out_row + static_cast<long>(rt.col_first) * 2, my, rt.n_chunks * 64);
-      ptx::bulk_commit();
+  if (!(last || (i & 1))) return;
+  const int bytes = ((i & 1) + 1) * 64;
+  const long dst_off = static_cast<long>(rt.col_first + (i & ~1) * 32) * 2;
+  const int sub = rt.lane & 7;
+  const unsigned long long mine =
+      rt.row_ok ? reinterpret_cast<unsigned long long>(rt.out_row) : 0ull;
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int row = 4 * it + (rt.lane >> 3);
+    const unsigned long long dst = __shfl_sync(0xffffffffu, mine, row);
+    if (dst != 0ull && sub * 16 < bytes) {
+      const uint4 v = *reinterpret_cast<const uint4*>(patch_piece(rt.patch, row, sub));
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(dst) + dst_off + sub * 16) = v;
     }
   }
+  __syncwarp();  // the next pair of chunks overwrites the patch
 }
 
 // One output tile for one epilogue warp in the row modes: 32 rows x up to four contiguous
 // 32-column chunks.  Two register buffers alternate: while chunk i is finished, the tcgen05.ld
-// of chunk i + 1 and the staging of its side operand are in flight.
+// of chunk i + 1 and the load of its saved pre-activation are in flight.
 template <typename T, int ACT>
-__device__ __forceinline__ void epilogue_tile_rows(const RowTile& rt) {
+__device__ __forceinline__ void epilogue_tile_rows(const RowTile& rt, Packed32& side_first) {
   const int lane = rt.lane;
-  const bool with_pre = (ACT != kActNone) && !rt.use_aux && rt.pre_row != nullptr;
+  const bool with_pre = (ACT != kActNone) && !rt.use_aux && rt.pre_tile != nullptr;
   uint32_t ra[32], rb[32];
+  Packed32 sb;
   bool released = false;
   if (rt.n_chunks > 0) {
     ptx::tmem_ld_32x32(rt.t_row, ra);
@@ -609,43 +621,31 @@ __device__ __forceinline__ void epilogue_tile_rows(const RowTile& rt) {
         const int i = 2 * pair;
         if (i >= rt.n_chunks) break;
         ptx::tmem_ld_wait();
-        Packed32 side_cur;
-        if (rt.use_aux) read_side<PATCH_PITCH>(rt.patch + i * 64, lane, side_cur);
         if (i + 1 < rt.n_chunks) {
           ptx::tmem_ld_32x32(rt.t_row + (i + 1) * 32, rb);
-          if (rt.use_aux) {
-            stage_side<PATCH_PITCH>(rt.patch + (i + 1) * 64, rt.side + (i + 1) * 64, rt.side_pitch,
-                                    rt.warp_valid, lane);
-          }
+          if (rt.use_aux) load_pre_chunk(rt.pre_tile, i + 1, lane, sb);
         } else if (!released) {
           ptx::tc_fence_before_sync();
           ptx::mbar_arrive(rt.empty_bar);
           released = true;
         }
-        // with a pre-activation output the second pair reuses the bytes of the first
-        if (with_pre && i > 0) ptx::bulk_wait_read<0>();
-        if (rt.row_ok) rows_chunk<T, ACT>(rt, i, with_pre, ra, side_cur);
-        rows_send(rt, i, with_pre);
+        rows_chunk<T, ACT>(rt, i, with_pre, ra, side_first);
+        rows_send(rt, i);
       }
       {
         const int i = 2 * pair + 1;
         if (i >= rt.n_chunks) break;
         ptx::tmem_ld_wait();
-        Packed32 side_cur;
-        if (rt.use_aux) read_side<PATCH_PITCH>(rt.patch + i * 64, lane, side_cur);
         if (i + 1 < rt.n_chunks) {
           ptx::tmem_ld_32x32(rt.t_row + (i + 1) * 32, ra);
-          if (rt.use_aux) {
-            stage_side<PATCH_PITCH>(rt.patch + (i + 1) * 64, rt.side + (i + 1) * 64, rt.side_pitch,
-                                    rt.warp_valid, lane);
-          }
+          if (rt.use_aux) load_pre_chunk(rt.pre_tile, i + 1, lane, side_first);
         } else if (!released) {
           ptx::tc_fence_before_sync();
           ptx::mbar_arrive(rt.empty_bar);
           released = true;
         }
-        if (rt.row_ok) rows_chunk<T, ACT>(rt, i, with_pre, rb, side_cur);
-        rows_send(rt, i, with_pre);
+        rows_chunk<T, ACT>(rt, i, with_pre, rb, sb);
+        rows_send(rt, i);
       }
     }
   }
@@ -1199,7 +1199,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     const int part = warp & 3;                          // TMEM lane quarter this warp may read
     const int half = (warp - FIRST_EPI_WARP) >> 2;      // which half of the accumulator columns
     uint8_t* patch = smem + L::kEpiOff + (warp - FIRST_EPI_WARP) * L::kPatch;
-    uint8_t* bias_sm = smem + L::kBiasOff + (warp - FIRST_EPI_WARP) * BIAS_BYTES;
     int iter = 0;
     for (int tile = cta; tile < total_tiles; tile += num_ctas, ++iter) {
       const TileCoord c = decode_tile<MODE>(p, aux, tile);
@@ -1326,56 +1325,36 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         const int col_first = n0 + half * (BN / 2);
         const int n_chunks = max(0, min(CHUNKS_PER_WARP, (p.n - col_first) / 32));
         const bool use_aux = p.epi == kEpiDAct;
-        const bool use_side = use_aux && warp_valid > 0 && n_chunks > 0;
-        const long side_pitch = static_cast<long>(p.n) * 2;
-        const uint8_t* side = reinterpret_cast<const uint8_t*>(p.aux) + (warp_row0 * p.n + col_first) * 2;
-
-        // The patch is free once the bulk stores of the previous tile have read it; the side
-        // operand is staged by other lanes than the one that owns a row, hence the warp sync.
-        ptx::bulk_wait_read<0>();
-        if (use_side) {
-          __syncwarp();
-          stage_side<PATCH_PITCH>(patch, side, side_pitch, warp_valid, lane);
-        }
-        // Bias slice of this warp's span goes to shared memory once per tile.
-        const bool use_bias = !use_aux && p.bias != nullptr;
-        if (use_bias) {
-          __syncwarp();
-          if (lane < n_chunks * 4) {
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.bias) +
-                                 (static_cast<long>(c.group) * p.n + col_first) * 2 + lane * 16;
-            *reinterpret_cast<uint4*>(bias_sm + lane * 16) = __ldg(reinterpret_cast<const uint4*>(src));
-          }
-          __syncwarp();
-        }
-        // Pull the side operand of the next tile of this CTA towards L2 while this tile is
-        // being finished: each lane asks for the two 128-byte lines of its row.
-        if (use_aux && tile + num_ctas < total_tiles) {
-          const TileCoord nx = decode_tile<MODE>(p, aux, tile + num_ctas);
-          const int nr = nx.m_tile * BM + part * 32 + lane;
-          if (nr < nx.row_end - nx.row_begin) {
-            const int ncol = nx.n_tile * BN + half * (BN / 2);
-            const uint8_t* row = reinterpret_cast<const uint8_t*>(p.aux) +
-                                 ((static_cast<long>(nx.row_begin) + nr) * p.n + ncol) * 2;
-#pragma unroll
-            for (int l = 0; l < 2; ++l) {
-              if (ncol + l * 64 < p.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + l * 128));
-            }
-          }
-        }
+        const int ew = warp - FIRST_EPI_WARP;
 
         RowTile rt;
         rt.lane = lane;
         rt.col_first = col_first;
         rt.n_chunks = n_chunks;
-        rt.warp_valid = warp_valid;
         rt.row_ok = row_ok;
         rt.use_aux = use_aux;
-        rt.side = side;
-        rt.side_pitch = side_pitch;
         rt.patch = patch;
         rt.out_row = nullptr;
-        rt.pre_row = nullptr;
+        rt.pre_tile = nullptr;
+        // The saved pre-activation is tile-blocked: this warp's four chunks of this tile.
+        if (use_aux) {
+          rt.pre_tile = const_cast<uint8_t*>(static_cast<const uint8_t*>(p.aux)) +
+                        static_cast<long>(tile) * PRE_TILE_BYTES + ew * (CHUNKS_PER_WARP * PRE_CHUNK_BYTES);
+        } else if (p.pre_out != nullptr) {
+          rt.pre_tile = static_cast<uint8_t*>(p.pre_out) + static_cast<long>(tile) * PRE_TILE_BYTES +
+                        ew * (CHUNKS_PER_WARP * PRE_CHUNK_BYTES);
+        }
+        // It does not depend on the accumulator: fetch the first chunk before waiting for the
+        // MMAs, and pull the next tile's chunks of this warp (8 KB, two lines per lane) to L2.
+        Packed32 side_first;
+        if (use_aux && n_chunks > 0) {
+          load_pre_chunk(rt.pre_tile, 0, lane, side_first);
+          if (tile + num_ctas < total_tiles) {
+            const uint8_t* nx = rt.pre_tile + static_cast<long>(num_ctas) * PRE_TILE_BYTES + lane * 256;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(nx));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 128));
+          }
+        }
         if (p.push_meta != nullptr) {
           // Fused combine: this lane's output row lives in the source rank's return buffer.
           if (row_ok) {
@@ -1390,9 +1369,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           }
         } else {
           rt.out_row = static_cast<uint8_t*>(p.out) + out_row * p.n * 2;
-          if (p.pre_out != nullptr) rt.pre_row = static_cast<uint8_t*>(p.pre_out) + out_row * p.n * 2;
         }
-        rt.bias_sm = use_bias ? bias_sm : nullptr;
+        rt.bias = (!use_aux && p.bias != nullptr)
+                      ? static_cast<const uint8_t*>(p.bias) + (static_cast<long>(c.group) * p.n + col_first) * 2
+                      : nullptr;
         rt.empty_bar = &aux->tmem_empty[acc];
         rt.t_row = tmem_base + (static_cast<uint32_t>(part * 32) << 16) + acc * BN + half * (BN / 2);
 
@@ -1401,18 +1381,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           break;
         }
         ptx::tc_fence_after_sync();
-        epilogue_tile_rows<T, ACT>(rt);
+        epilogue_tile_rows<T, ACT>(rt, side_first);
       }
     }
     if constexpr (MODE != kWgrad) {
-      // Every bulk store of this thread has to be complete before the CTA may go away (and,
-      // in push mode, before the arrival of its rows is announced).
-      ptx::bulk_wait<0>();
       if (p.push_meta != nullptr) {
-        // All rows of this CTA have landed: order everything before the completion count; the
+        // All rows of this CTA are on their way: order them before the completion count; the
         // last CTA of the grid publishes the epoch on every peer's return channel.  A CTA that
         // gave up still counts, so that the counter is zero again for the next launch.
-        ptx::fence_proxy_async_all();
         __threadfence_system();
         asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
         if (threadIdx.x == FIRST_EPI_WARP * 32) {

@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdint>
 #include <mutex>
 
 #include "routing.cuh"
@@ -64,6 +65,25 @@ extern "C" int fmoe_bias_grad_noalloc(const void* x, const int* offs, int num_gr
     g_last_error = "fmoe_bias_grad_noalloc: bad argument (null pointer, n not a multiple of 8, or dtype not 0/1)";
     return -1;
   }
+  // The kernels read x sixteen bytes at a time and the offsets as 32-bit words: a pointer a
+  // C caller got wrong must come back as an error code, not as a device fault.
+  if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(offs) % 4 != 0 ||
+      reinterpret_cast<uintptr_t>(out) % 2 != 0) {
+    g_last_error = "fmoe_bias_grad_noalloc: x must be 16-byte aligned, offs 4-byte, out 2-byte";
+    return -1;
+  }
+#if CUDART_VERSION >= 12080
+  {
+    // A stream of another device would run the kernels against this device's scratch address.
+    int cur = -1, sdev = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cudaStreamGetDevice(stream, &sdev) == cudaSuccess &&
+        sdev != cur) {
+      g_last_error = "fmoe_bias_grad_noalloc: the stream does not belong to the current device";
+      return -1;
+    }
+    (void)cudaGetLastError();
+  }
+#endif
   const long elems = static_cast<long>(num_groups) * n;
   if (elems > FMOE_NOALLOC_MAX_ELEMS) {
     g_last_error = "fmoe_bias_grad_noalloc: num_groups * n exceeds FMOE_NOALLOC_MAX_ELEMS (65536)";

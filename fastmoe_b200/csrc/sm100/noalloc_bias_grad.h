@@ -22,9 +22,14 @@ extern "C" {
 // out[g, :] = sum of the rows x[offs[g] : offs[g + 1], :]   for g in [0, num_groups)
 //
 //   x         device, [rows_cap, n], bf16 (dtype 0) or fp16 (dtype 1), 16-byte aligned, n % 8 == 0
-//   offs      device, int32 [num_groups + 1], ascending row offsets
+//   offs      device, int32 [num_groups + 1], ascending row offsets; rows at or past rows_cap
+//             are not read, whatever the offsets say
 //   out       device, [num_groups, n], same dtype as x
-//   stream    stream the three kernels (clear, accumulate, convert) are enqueued on
+//   stream    stream of the CURRENT device on which the three kernels (clear, accumulate,
+//             convert) are enqueued
+//
+// Misaligned pointers, a stream of another device and sizes the launch cannot express
+// (n > 16,776,960) are refused with -1 before anything is launched.
 //
 // Returns 0 on success, a negative value otherwise (fmoe_noalloc_last_error() describes it):
 //   -1 bad argument, -2 num_groups * n exceeds FMOE_NOALLOC_MAX_ELEMS, -3 CUDA error.

@@ -341,9 +341,9 @@ __global__ void combine_bwd_kernel(const T* __restrict__ dout, const T* __restri
 template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_kernel(const T* __restrict__ x, const int* __restrict__ offs, int num_groups, int n,
-              float* __restrict__ out) {
+              long rows_cap, float* __restrict__ out) {
   __shared__ float red[8][256 + 8];
-  int piece = blockIdx.y;
+  int piece = blockIdx.x;  // pieces on x (up to 2^31 - 1 blocks), column blocks on y
   int g = 0, r0 = 0, r1 = 0;
   bool found = false;
   for (; g < num_groups; ++g) {
@@ -352,6 +352,7 @@ colsum_kernel(const T* __restrict__ x, const int* __restrict__ offs, int num_gro
     if (piece < pieces) {
       r0 = b + piece * 128;
       r1 = min(e, r0 + 128);
+      if (r1 > rows_cap) r1 = static_cast<int>(rows_cap);  // offsets past the matrix are not followed
       found = true;
       break;
     }
@@ -359,7 +360,7 @@ colsum_kernel(const T* __restrict__ x, const int* __restrict__ offs, int num_gro
   }
   if (!found) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col = blockIdx.x * 256 + lane * 8;
+  const int col = blockIdx.y * 256 + lane * 8;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (col < n) {
     for (int r = r0 + warp; r < r1; r += 8) {
@@ -372,7 +373,7 @@ colsum_kernel(const T* __restrict__ x, const int* __restrict__ offs, int num_gro
 #pragma unroll
   for (int q = 0; q < 8; ++q) red[warp][lane * 8 + q] = acc[q];
   __syncthreads();
-  const int c = blockIdx.x * 256 + threadIdx.x;
+  const int c = blockIdx.y * 256 + threadIdx.x;
   if (c < n) {
     float s = 0.f;
 #pragma unroll
@@ -856,9 +857,12 @@ cudaError_t launch_colsum(int dtype, const void* x, const int* offs, int num_gro
                           int n, float* out, cudaStream_t stream) {
   if (rows_cap == 0) return cudaSuccess;
   if (n % 8 != 0) return cudaErrorInvalidValue;
-  dim3 grid((n + 255) / 256, static_cast<unsigned>((rows_cap + 127) / 128 + num_groups));
+  if ((n + 255) / 256 > 65535 || (rows_cap + 127) / 128 + num_groups > 2147483647L) {
+    return cudaErrorInvalidValue;
+  }
+  dim3 grid(static_cast<unsigned>((rows_cap + 127) / 128 + num_groups), (n + 255) / 256);
   FMOE_DISPATCH_16(dtype, (colsum_kernel<T><<<grid, 256, 0, stream>>>(
-      static_cast<const T*>(x), offs, num_groups, n, out)));
+      static_cast<const T*>(x), offs, num_groups, n, rows_cap, out)));
   return cudaGetLastError();
 }
 

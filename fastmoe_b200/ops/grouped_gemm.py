@@ -41,8 +41,44 @@ def _aligned(t):
     return t
 
 
+TILE_M, TILE_N = 128, 256
+
+
+def pre_buffer(rows_cap, n, groups, dtype, device):
+    r"""Storage of the saved pre-activation of a fused first GEMM: one ``128 x 256`` block per
+    output tile, in the tile-blocked order the tensor-core epilogues write and read it (a 1-D
+    tensor; :func:`untile_pre` gives the ``[rows, n]`` view of it for inspection)."""
+    tiles = ((rows_cap + TILE_M - 1) // TILE_M + groups) * ((n + TILE_N - 1) // TILE_N)
+    return torch.empty(tiles * TILE_M * TILE_N, dtype=dtype, device=device)
+
+
+def untile_pre(pre, offs, n, rows_cap):
+    r"""``[rows_cap, n]`` row-major copy of a tile-blocked pre-activation (rows outside the
+    expert segments are zero).  For tests and debugging: reads ``offs`` on the host."""
+    o = [int(v) for v in offs.tolist()]
+    n_tiles = (n + TILE_N - 1) // TILE_N
+    out = torch.zeros(rows_cap, n, dtype=pre.dtype, device=pre.device)
+    blocks = pre.view(-1, 8, 4, 4, 32, 8)      # tile, warp (half*4 + part), chunk, piece, lane, 8 values
+    tile = 0
+    for e in range(len(o) - 1):
+        rows = o[e + 1] - o[e]
+        for m in range((rows + TILE_M - 1) // TILE_M):
+            for nt in range(n_tiles):
+                blk = blocks[tile]                                    # [8, 4, 4, 32, 8]
+                blk = blk.view(2, 4, 4, 4, 32, 8)                      # half, part, chunk, piece, lane, v
+                full = blk.permute(1, 4, 0, 2, 3, 5).reshape(TILE_M, TILE_N)   # (part, lane) x (half, chunk, piece, v)
+                r0, c0 = o[e] + m * TILE_M, nt * TILE_N
+                nr, nc = min(TILE_M, o[e + 1] - r0), min(TILE_N, n - c0)
+                out[r0:r0 + nr, c0:c0 + nc] = full[:nr, :nc]
+                tile += 1
+    return out
+
+
 def forward(x, weight, offs, bias=None, act=None, want_pre=False):
-    r"""``act(x W^T + b)`` per expert; optionally also the pre-activation (for backward)."""
+    r"""``act(x W^T + b)`` per expert; optionally also the pre-activation (for backward).
+
+    On the tensor-core path with a fused activation the pre-activation comes back tile-blocked
+    (1-D, see :func:`pre_buffer`); hand it to :func:`dgrad` as it is."""
     nat = native.get()
     groups, n, k = weight.shape
     out = torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
@@ -52,7 +88,7 @@ def forward(x, weight, offs, bias=None, act=None, want_pre=False):
         return (out, out.clone()) if want_pre else out
     if _tc_ok(x, MODE_NT, 0, n, k, groups):
         if want_pre and code != 0:
-            pre = torch.empty_like(out)
+            pre = pre_buffer(x.shape[0], n, groups, x.dtype, x.device)
         nat.grouped_gemm(MODE_NT, _aligned(x), _aligned(weight), offs, out, _aligned(bias), pre, None,
                          code, EPI_BIAS_ACT, False)
         if want_pre and pre is None:
@@ -68,16 +104,23 @@ def forward(x, weight, offs, bias=None, act=None, want_pre=False):
 
 
 def dgrad(dy, weight, offs, pre=None, act=None):
-    r"""``(dy W) * act'(pre)`` per expert (``pre`` = saved pre-activation of the producing layer)."""
+    r"""``(dy W) * act'(pre)`` per expert (``pre`` = saved pre-activation of the producing layer,
+    tile-blocked as :func:`forward` returned it, or a plain ``[rows, n]`` matrix)."""
     nat = native.get()
     groups, k, n = weight.shape
     out = torch.empty(dy.shape[0], n, dtype=dy.dtype, device=dy.device)
     code = ACT_CODES[act] if pre is not None else 0
     if dy.shape[0] == 0:
         return out
-    if _tc_ok(dy, MODE_NN, 0, n, k, groups):
+    if _tc_ok(dy, MODE_NN, 0, n, k, groups) and (not code or pre.dim() == 1):
         nat.grouped_gemm(MODE_NN, _aligned(dy), _aligned(weight), offs, out, None, None,
-                         _aligned(pre) if code else None, code, EPI_DACT if code else EPI_BIAS_ACT, False)
+                         pre if code else None, code, EPI_DACT if code else EPI_BIAS_ACT, False)
+    elif _tc_ok(dy, MODE_NN, 0, n, k, groups):
+        # a row-major pre-activation: plain tensor-core product, derivative as a PyTorch op
+        nat.grouped_gemm(MODE_NN, _aligned(dy), _aligned(weight), offs, out, None, None, None, 0,
+                         EPI_BIAS_ACT, False)
+        _zero_tail(out, offs)
+        out = out * _torch_act_grad(pre, act)
     else:
         nat.simt_grouped_gemm(MODE_NN, dy, weight, offs, out, None)
         _zero_tail(out, offs)

@@ -387,7 +387,7 @@ class _FusedEPMLP(Function):
                     n_ctas=config.send_ctas())
         with fused_range("ep.dispatch_gemm1"):
             a = torch.empty(capacity, h, dtype=x.dtype, device=dev)
-            pre = torch.empty(capacity, h, dtype=x.dtype, device=dev) if code != 0 else a
+            pre = gg.pre_buffer(capacity, h, n_expert, x.dtype, dev) if code != 0 else a
             ws.ctx.gemm_ep(gg.MODE_NT, xs, w1, tb.expert_offs, out=a, bias=b1,
                            pre_out=pre if code != 0 else None, act=code, send=send,
                            gate_flag_ptrs=flag_ptrs, seg_off=tb.seg_off)

@@ -46,6 +46,8 @@ def case_fused_vs_general():
     rank, world = dist.get_rank(), dist.get_world_size()
     cases = ((2, 2, 512, None), (1, 1, 300, None), (4, 3, 1000, nn.ReLU()),
              (2, 2, 640, nn.Sequential(nn.ReLU(), nn.Dropout(0.0))))
+    # the exchange buffers are sized once per group: announce the largest batch of this test
+    symm.reserve_tokens(dist.group.WORLD, max(c[2] for c in cases), _dev())
     for num_expert, top_k, n_tok, activation in cases:
         layer = _make_layer(world, rank, num_expert=num_expert, top_k=top_k, activation=activation)
         torch.manual_seed(1000 + rank)
@@ -130,7 +132,8 @@ def case_oracle():
     rank, world = dist.get_rank(), dist.get_world_size()
     cases = ((torch.bfloat16, 2, 2, 512, 256, 512, None, 6e-2),
              (torch.float16, 3, 1, 333, 128, 320, nn.ReLU(), 2e-2),
-             (torch.bfloat16, 1, 2, 1200, 256, 1024, nn.GELU(approximate="tanh"), 6e-2))
+             (torch.bfloat16, 2, 2, 1200, 256, 1024, nn.GELU(approximate="tanh"), 6e-2))
+    symm.reserve_tokens(dist.group.WORLD, max(c[3] for c in cases), _dev())
     for dtype, num_expert, top_k, n_tok, d, h, act, tol in cases:
         layer = _make_layer(world, rank, num_expert=num_expert, d=d, h=h, top_k=top_k, dtype=dtype,
                             activation=act)
@@ -219,15 +222,13 @@ def case_multi_layer():
     static_grads = {}
 
     def step(x):
-        model.zero_grad(set_to_none=False)
+        model.zero_grad(set_to_none=True)
         xx = x.detach().requires_grad_(True)
         y = model(xx)
         y.float().pow(2).mean().backward()
         static_grads["x"] = xx.grad
         return y
 
-    for p in model.parameters():
-        p.grad = torch.zeros_like(p)
     g = GraphedStep(step, xs[0], warmup=2)
     for i in (1, 2, 0, 1):
         y = g(xs[i]).float()

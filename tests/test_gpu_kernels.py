@@ -25,6 +25,27 @@ def _segments(counts):
         base += n
 
 
+def _tiled(pre, offs, groups):
+    r"""Tile-blocked copy of a row-major pre-activation: the inverse of ``gg.untile_pre``."""
+    from fastmoe_b200.ops import grouped_gemm as gg
+    rows, n = pre.shape
+    buf = gg.pre_buffer(rows, n, groups, pre.dtype, pre.device).zero_()
+    blocks = buf.view(-1, 2, 4, 4, 4, 32, 8)     # tile, half, part, chunk, piece, lane, v
+    o = [int(v) for v in offs.tolist()]
+    n_tiles = (n + gg.TILE_N - 1) // gg.TILE_N
+    tile = 0
+    for e in range(groups):
+        for m in range((o[e + 1] - o[e] + gg.TILE_M - 1) // gg.TILE_M):
+            for nt in range(n_tiles):
+                full = torch.zeros(gg.TILE_M, gg.TILE_N, dtype=pre.dtype, device=pre.device)
+                r0, c0 = o[e] + m * gg.TILE_M, nt * gg.TILE_N
+                nr, nc = min(gg.TILE_M, o[e + 1] - r0), min(gg.TILE_N, n - c0)
+                full[:nr, :nc] = pre[r0:r0 + nr, c0:c0 + nc]
+                blocks[tile] = full.view(4, 32, 2, 4, 4, 8).permute(2, 0, 3, 4, 1, 5)
+                tile += 1
+    return buf
+
+
 def _tol(dtype, k):
     # bf16 has 8 bits of mantissa: inputs are exact in fp32, the only error is the output rounding.
     return (2e-2 if dtype == torch.bfloat16 else 4e-3)
@@ -48,6 +69,8 @@ def test_grouped_gemm_forward(dtype, counts, k, n):
     b = torch.randn(len(counts), n, device=DEV).to(dtype)
     offs = _offs(counts)
     out, pre = gg.forward(x, w, offs, b, act="gelu", want_pre=True)
+    if pre.dim() == 1:
+        pre = gg.untile_pre(pre, offs, n, x.shape[0])
     for e, lo, hi in _segments(counts):
         ref_pre = x[lo:hi].float() @ w[e].float().t() + b[e].float()
         ref = torch.nn.functional.gelu(ref_pre)
@@ -57,7 +80,7 @@ def test_grouped_gemm_forward(dtype, counts, k, n):
 
 
 @pytest.mark.parametrize("act", [None, "relu", "gelu_tanh"])
-@pytest.mark.parametrize("counts,k,n", [([70, 300, 129], 192, 416), ([2048, 2048], 4096, 1024)])
+@pytest.mark.parametrize("counts,k,n", [([70, 300, 129], 192, 448), ([2048, 2048], 4096, 1024)])
 def test_grouped_gemm_epilogues(act, counts, k, n):
     r"""The other fused epilogues, forward and input gradient, including a span of columns that
     is not a multiple of the 256-column tile and a K of 4096."""
@@ -70,12 +93,14 @@ def test_grouped_gemm_epilogues(act, counts, k, n):
     b = torch.randn(len(counts), n, device=DEV).to(dtype)
     offs = _offs(counts)
     out, pre = gg.forward(x, w, offs, b, act=act, want_pre=True)
+    if pre.dim() == 1:
+        pre = gg.untile_pre(pre, offs, n, rows)
     fn = {None: lambda t: t, "relu": torch.relu,
           "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh")}[act]
     dy = torch.randn(rows, n, device=DEV, dtype=dtype)
     wt = (torch.randn(len(counts), n, k, device=DEV) / n ** 0.5).to(dtype)   # [E, k(out)=n, n(in)=k]
     pre_in = torch.randn(rows, k, device=DEV, dtype=dtype)
-    dx = gg.dgrad(dy, wt, offs, pre=pre_in if act else None, act=act)
+    dx = gg.dgrad(dy, wt, offs, pre=_tiled(pre_in, offs, len(counts)) if act else None, act=act)
     p32 = pre_in.float().requires_grad_(True)
     fn(p32).sum().backward()
     for e, lo, hi in _segments(counts):
@@ -105,7 +130,9 @@ def test_grouped_gemm_dgrad(dtype, counts, k, n):
     pre = torch.randn(rows, n, device=DEV, dtype=dtype)
     offs = _offs(counts)
     plain = gg.dgrad(dy, w, offs)
-    fused = gg.dgrad(dy, w, offs, pre=pre, act="gelu")
+    fused = gg.dgrad(dy, w, offs, pre=_tiled(pre, offs, len(counts)), act="gelu")
+    rowmajor = gg.dgrad(dy, w, offs, pre=pre, act="gelu")   # plain matrix: derivative as a PyTorch op
+    assert torch.allclose(rowmajor[:rows].float(), fused[:rows].float(), atol=2e-2, rtol=2e-2)
     p32 = pre.float().requires_grad_(True)
     torch.nn.functional.gelu(p32).sum().backward()
     for e, lo, hi in _segments(counts):

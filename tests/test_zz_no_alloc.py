@@ -58,6 +58,30 @@ def test_noalloc_matches_regular_entry_twice(dtype):
         assert torch.allclose(out.float(), ref.float(), atol=2e-2, rtol=2e-2), \
             float((out.float() - ref.float()).abs().max())
         assert float(out[1].abs().max()) == 0.0  # the empty expert
+        # and against plain fp32 sums of the segments (an oracle that shares no kernel with it)
+        base = 0
+        for e, cnt in enumerate(counts):
+            want = x[base:base + cnt].float().sum(0)
+            tol = 2e-2 * float(want.abs().max()) + 1e-2     # one rounding of the 16-bit result
+            assert float((out[e].float() - want).abs().max()) <= tol, e
+            base += cnt
+
+
+def test_noalloc_rejects_bad_pointers_and_follows_no_offsets_past_the_matrix():
+    lib = _lib()
+    dev = "cuda"
+    x = torch.ones(64, 64, device=dev, dtype=torch.bfloat16)
+    offs = torch.tensor([0, 64], dtype=torch.int32, device=dev)
+    out = torch.zeros(1, 64, device=dev, dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+    # host-side rejection only: nothing is launched for a misaligned x
+    rc = lib.fmoe_bias_grad_noalloc(x.data_ptr() + 2, offs.data_ptr(), 1, 63, 64, 0, out.data_ptr(), stream)
+    assert rc == -1 and b"aligned" in lib.fmoe_noalloc_last_error()
+    # offsets that claim more rows than the matrix has: the extra rows are not read
+    big = torch.tensor([0, 1000], dtype=torch.int32, device=dev)
+    assert lib.fmoe_bias_grad_noalloc(x.data_ptr(), big.data_ptr(), 1, 64, 64, 0, out.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out.float(), torch.full((1, 64), 64.0, device=dev))
 
 
 def test_noalloc_rejects_oversize():
