@@ -294,11 +294,16 @@ def main():
         torch.cuda.synchronize()
         live, saved = snapshot()
         t_heat = time.perf_counter()
-        while time.perf_counter() - t_heat < PREHEAT_S:
-            for _ in range(4):
+        go_on = torch.ones(1, dtype=torch.int32, device=device)
+        while int(go_on.item()) == 1:
+            for _ in range(8):
                 step(dev_inputs[preheat_steps % n_inputs])
                 preheat_steps += 1
             torch.cuda.synchronize()
+            # every rank must run the same number of steps: rank 0 decides when to stop
+            go_on.fill_(1 if time.perf_counter() - t_heat < PREHEAT_S else 0)
+            if world > 1:
+                dist.broadcast(go_on, 0)
         with torch.no_grad():
             for t, s0 in zip(live, saved):
                 t.copy_(s0)

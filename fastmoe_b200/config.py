@@ -139,13 +139,6 @@ def max_tokens():
     return int_from_env("FMOE_MAX_TOKENS", 0)
 
 
-def send_ctas():
-    r"""``FMOE_SEND_CTAS``: CTAs of the first expert GEMM launch that act as row senders of the
-    dispatch instead of computing tiles (default 16: about what saturates NVLink with bulk
-    copies; the other 132 SMs compute)."""
-    return max(1, int_from_env("FMOE_SEND_CTAS", 16))
-
-
 def push_before_wgrad():
     r"""``FMOE_PUSH_BEFORE_WGRAD`` (default off): in the fused expert-parallel backward, queue the
     input-gradient GEMM whose epilogue returns rows to their sources before the two weight

@@ -98,15 +98,12 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a) {
   kp.send = a.send;
   kp.gate = a.gate;
   if (a.mode == kWgrad) {
-    kp.send.n_ctas = 0;
+    kp.send.enabled = 0;
     kp.gate.flags = nullptr;
   }
-  if (kp.send.n_ctas > 0) {
-    // the sender's item table and row pieces
-    if (kp.send.world * kp.send.n_expert > gg::SEND_MAX_TOT || (kp.send.d * 2) % 16 != 0 ||
-        kp.send.n_ctas >= (a.num_sms > 0 ? a.num_sms : 148)) {
-      return cudaErrorInvalidValue;
-    }
+  if (kp.send.enabled && (kp.send.d % 8 != 0 || kp.send.item_prefix == nullptr ||
+                          kp.send.item_count == nullptr)) {
+    return cudaErrorInvalidValue;
   }
 
   const int grid = a.num_sms > 0 ? a.num_sms : 148;

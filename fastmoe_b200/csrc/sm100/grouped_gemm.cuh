@@ -26,21 +26,23 @@ enum EpiKind : int {
 
 enum DType : int { kBF16 = 0, kF16 = 1 };
 
-// Row dispatch fused into a row-mode GEMM launch (optional).  The first `n_ctas` CTAs of the grid
-// do no tensor-core work: they walk this rank's slots in destination order and copy every token
-// row (optionally scaled) into the owning peer's receive buffer with bulk asynchronous stores,
-// then publish one flag word per (128-row block of the receiver, source rank).  The remaining
-// CTAs run the GEMM and gate every tile on the flags of its row block (`GateArgs`), so the
-// transfer overlaps the math tile by tile.
+// Row dispatch fused into a row-mode GEMM launch (optional).  Warps 2 and 3 of every CTA,
+// which the GEMM roles leave idle, walk this rank's slots in destination order and copy every
+// token row (optionally scaled) through registers into the owning peer's receive buffer; one
+// flag word per (128-row block of the receiver, source rank) is published when all rows of the
+// block have left.  The TMA producer gates every tile on the flags of its row block
+// (`GateArgs`), so the transfer overlaps the math tile by tile and no SM is set aside for it.
 struct SendArgs {
-  int n_ctas = 0;                 // 0 = no sender CTAs in this launch
-  int dtype_bytes = 2;
+  int enabled = 0;
   const void* x = nullptr;        // [n_tokens, d] rows to send (row s / k serves slot s)
   const int* pos = nullptr;       // [n_slots] slot ids sorted by (global expert, rank in expert)
   const int* my_offs = nullptr;   // [tot + 1] exclusive prefix of this rank's per-expert slot counts
   const int* dst_base = nullptr;  // [tot] first destination row of my rows, per global expert
   const int* seg_base = nullptr;  // [tot] first row of the expert's whole segment on its owner
   const int* blk_base = nullptr;  // [tot] index of the expert's first 128-row block on its owner
+  const int* item_prefix = nullptr;  // [tot + 1] exclusive prefix of the 128-row blocks my rows touch,
+                                     // per (expert, peer) in send order
+  int* item_count = nullptr;      // local, zero between launches: rows sent so far, per block in send order
   const void* scale = nullptr;    // optional [n_slots]: row s is multiplied by scale[s]
   PeerPtrs rows = {};             // every peer's receive buffer [capacity, d]
   PeerPtrs meta = {};             // every peer's int64 [capacity] (source rank << 32 | slot); entries may be null
@@ -54,7 +56,7 @@ struct SendArgs {
   int capacity = 0;
 };
 
-// Arrival gating of a row-mode GEMM whose A operand is being filled by the peers' sender CTAs.
+// Arrival gating of a row-mode GEMM whose A operand is being filled by the peers' sender warps.
 struct GateArgs {
   const int* flags = nullptr;     // local int32 [blocks][kMaxPeers]; null = not gated
   const int* seg_off = nullptr;   // [num_groups][world + 1] row where the rows of the j-th source begin

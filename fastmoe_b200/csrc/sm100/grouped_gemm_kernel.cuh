@@ -10,7 +10,7 @@
 //               128-byte-swizzled shared-memory tiles, completion on mbarriers;
 //   warp 1      one elected thread issues tcgen05.mma (128 x 256 x 16 per instruction, fp32
 //               accumulators in TMEM) and tcgen05.commit; the warp owns the TMEM allocation;
-//   warps 2-3   idle (they complete the first warpgroup);
+//   warps 2-3   idle, or row senders of the fused dispatch (see below);
 //   warps 4-11  epilogue (two warpgroups): two warps per TMEM lane quarter.  Row modes: each
 //               warp owns 32 rows x 128 columns of the tile; the tcgen05.ld of chunk i+1 and
 //               the load of its saved pre-activation are in flight while chunk i gets bias /
@@ -25,9 +25,9 @@
 // main loop of tile i+1.
 //
 // Optional roles of a row-mode launch (expert parallelism):
-//   * sender CTAs (the first `send.n_ctas` CTAs): no tensor-core work; they copy this rank's
-//     token rows into the owning peers' receive buffers with bulk copies through shared
-//     memory and publish per-(row block, source) arrival flags;
+//   * sender warps (warps 2 and 3 of every CTA): they copy this rank's token rows through
+//     registers into the owning peers' receive buffers and publish per-(row block, source)
+//     arrival flags;
 //   * gated producer: the TMA warp waits (bounded) for the arrival flags of a tile's row
 //     block before loading it, so GEMM tiles start as their rows land.
 //
@@ -78,12 +78,12 @@ constexpr int PRE_TILE_BYTES = BM * BN * 2;
 constexpr int PRE_CHUNK_BYTES = 32 * 64;
 constexpr int TMEM_COLS = 512;
 
-// Sender CTAs: every warp owns a ring of SEND_SLOTS pieces of at most SEND_PIECE bytes.
-constexpr int SEND_PIECE = 2048;
-constexpr int SEND_SLOTS = 6;
-constexpr int SEND_AHEAD = 3;                 // loads in flight ahead of the piece being stored
-constexpr int SEND_DONE_RING = 2048;          // completion counters of the items a CTA has in flight
-constexpr int SEND_MAX_TOT = 4096;            // global experts the item table holds
+// Sender warps (warps 2 and 3 of every CTA): a unit of work is SEND_UNIT_ROWS consecutive
+// destination rows of one 128-row block.
+constexpr int SEND_UNIT_ROWS = 16;
+constexpr int SEND_UNITS_PER_ITEM = BM / SEND_UNIT_ROWS;
+constexpr int FIRST_SEND_WARP = 2;
+constexpr int NUM_SEND_WARPS = 2;
 constexpr int NUM_WARPS = FIRST_EPI_WARP + NUM_EPI_WARPS;
 
 constexpr int STATUS_TIMEOUT_PRODUCER = 101;
@@ -114,18 +114,6 @@ template <int MODE> struct Layout {
   static constexpr int kBytes = kEpiOff + NUM_EPI_WARPS * kPatch + 1024;
 };
 static_assert(Layout<kRowsNT>::kBytes <= 232448 && Layout<kWgrad>::kBytes <= 232448, "shared memory");
-// What a sender CTA lays over the same dynamic shared memory.
-struct SenderShared {
-  uint64_t bar[NUM_WARPS][SEND_SLOTS];
-  int item_prefix[SEND_MAX_TOT + 1];
-  int partial[NUM_THREADS];
-  int done[SEND_DONE_RING];
-  int failed;
-};
-constexpr int SENDER_DATA_OFF = (static_cast<int>(sizeof(SenderShared)) + 1023) & ~1023;
-static_assert(SENDER_DATA_OFF + NUM_WARPS * SEND_SLOTS * SEND_PIECE + 1024 <= Layout<kRowsNT>::kBytes,
-              "sender rings must fit into the row-mode launch");
-
 struct KernelParams {
   int num_groups;
   int m;  // wgrad only
@@ -668,10 +656,9 @@ __device__ __forceinline__ void st_release_sys_i32(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// One unit of sender work: the part of one 128-row block of a peer's expert segment that this
+// One item of sender work: the part of one 128-row block of a peer's expert segment that this
 // rank's rows fill.  Rows are relative to the first row of the expert's segment on the owner.
 struct SendItem {
-  int g;        // global expert
   int peer;
   int blk;      // block index inside the peer's flag array
   int r_lo;     // rows [r_lo, r_hi) of the segment
@@ -683,6 +670,7 @@ struct SendItem {
 
 // Send order: local expert e outer, peer distance j inner (j = 0 is this rank itself), so
 // that every receiver gets the rows of its first experts first, from all sources at once.
+// The count-exchange kernel builds `item_prefix` in the same order.
 __device__ __forceinline__ int send_order_expert(const SendArgs& s, int q) {
   const int e = q / s.world;
   const int j = q - e * s.world;
@@ -691,263 +679,120 @@ __device__ __forceinline__ int send_order_expert(const SendArgs& s, int q) {
   return peer * s.n_expert + e;
 }
 
-// Rows [rel0, r_end) of the segment of global expert g are mine (clamped to the receive
-// capacity); returns the number of 128-row blocks they touch.
-__device__ __forceinline__ int send_items_of(const SendArgs& s, int g, int& rel0, int& r_end) {
-  const int cnt = s.my_offs[g + 1] - s.my_offs[g];
-  const int seg = s.seg_base[g];
-  rel0 = s.dst_base[g] - seg;
-  r_end = rel0 + cnt;
-  if (r_end > s.capacity - seg) r_end = s.capacity - seg;
-  if (cnt <= 0 || r_end <= rel0) return 0;
-  return (r_end - 1) / BM - rel0 / BM + 1;
-}
-
-__device__ __forceinline__ SendItem send_decode(const SendArgs& s, const SenderShared* sh, int tot,
-                                                int item) {
+__device__ __forceinline__ SendItem send_decode(const SendArgs& s, int tot, int item) {
   int lo = 0, hi = tot;
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
-    if (sh->item_prefix[mid] <= item) lo = mid; else hi = mid;
+    if (__ldg(s.item_prefix + mid) <= item) lo = mid; else hi = mid;
   }
+  const int g = send_order_expert(s, lo);
   SendItem it;
-  it.g = send_order_expert(s, lo);
-  it.peer = it.g / s.n_expert;
-  int rel0, r_end;
-  send_items_of(s, it.g, rel0, r_end);
-  const int b = rel0 / BM + (item - sh->item_prefix[lo]);
-  it.blk = s.blk_base[it.g] + b;
+  it.peer = g / s.n_expert;
+  const int seg = __ldg(s.seg_base + g);
+  const int cnt = __ldg(s.my_offs + g + 1) - __ldg(s.my_offs + g);
+  const int rel0 = __ldg(s.dst_base + g) - seg;
+  int r_end = rel0 + cnt;
+  if (r_end > s.capacity - seg) r_end = s.capacity - seg;
+  const int b = rel0 / BM + (item - __ldg(s.item_prefix + lo));
+  it.blk = __ldg(s.blk_base + g) + b;
   it.r_lo = max(rel0, b * BM);
   it.r_hi = min(r_end, (b + 1) * BM);
   it.rel0 = rel0;
-  it.seg = s.seg_base[it.g];
-  it.src0 = s.my_offs[it.g];
+  it.seg = seg;
+  it.src0 = __ldg(s.my_offs + g);
   return it;
 }
 
-// Bounded wait on a load barrier of a sender ring slot.
-__device__ __forceinline__ bool send_wait(uint64_t* bar, uint32_t parity, const volatile int* failed) {
-  return ptx::mbar_wait(bar, parity, failed);
-}
-
-template <int N> struct BulkWaitUpTo {
-  static __device__ __forceinline__ void run(int n) {
-    if (n >= N) ptx::bulk_wait<N>(); else BulkWaitUpTo<N - 1>::run(n);
-  }
-};
-template <> struct BulkWaitUpTo<0> {
-  static __device__ __forceinline__ void run(int) { ptx::bulk_wait<0>(); }
-};
-
+// One sender warp.  Units are dealt round-robin over all sender warps of the grid; the eight
+// units of an item are therefore in flight on eight different warps at once and the item's
+// flag goes up early.  A row travels global -> registers -> (peer) global, 16 bytes per lane
+// and access, two rows in flight per warp; nothing here waits for anything.
 template <typename T>
-__device__ void sender_cta(const KernelParams& p, uint8_t* smem) {
+__device__ __forceinline__ void sender_warp(const KernelParams& p, int sender_id, int n_senders,
+                                            int lane) {
   const SendArgs& s = p.send;
-  SenderShared* sh = reinterpret_cast<SenderShared*>(smem);
-  const int tid = threadIdx.x;
-  const int warp = tid >> 5;
-  const int lane = tid & 31;
   const int tot = s.world * s.n_expert;
-  uint8_t* ring = smem + SENDER_DATA_OFF + warp * (SEND_SLOTS * SEND_PIECE);
-
-  for (int i = tid; i < SEND_DONE_RING; i += NUM_THREADS) sh->done[i] = 0;
-  if (tid < NUM_WARPS * SEND_SLOTS) ptx::mbar_init(&sh->bar[tid / SEND_SLOTS][tid % SEND_SLOTS], 1);
-  if (tid == 0) {
-    sh->failed = 0;
-    sh->item_prefix[0] = 0;
-    ptx::fence_barrier_init();
-  }
-  // Item table: blocks per (expert, peer) in send order, then an exclusive prefix.
-  const int per = (tot + NUM_THREADS - 1) / NUM_THREADS;
-  const int q0 = min(tot, tid * per);
-  const int q1 = min(tot, q0 + per);
-  int mine = 0;
-  for (int q = q0; q < q1; ++q) {
-    int rel0, r_end;
-    const int n = send_items_of(s, send_order_expert(s, q), rel0, r_end);
-    sh->item_prefix[q + 1] = n;
-    mine += n;
-  }
-  sh->partial[tid] = mine;
-  __syncthreads();
-  if (tid == 0) {
-    int run = 0;
-    for (int t = 0; t < NUM_THREADS; ++t) {
-      const int v = sh->partial[t];
-      sh->partial[t] = run;
-      run += v;
-    }
-  }
-  __syncthreads();
-  {
-    int run = sh->partial[tid];
-    for (int q = q0; q < q1; ++q) {
-      run += sh->item_prefix[q + 1];
-      sh->item_prefix[q + 1] = run;
-    }
-  }
-  __syncthreads();
-  const int total_items = sh->item_prefix[tot];
+  const int total_items = __ldg(s.item_prefix + tot);
+  const int total_units = total_items * SEND_UNITS_PER_ITEM;
   const int epoch = *s.epoch;
-  const volatile int* failed = &sh->failed;
-  const int n_ctas = s.n_ctas;
-  const int row_bytes = s.d * 2;
-  const int pieces_per_row = (row_bytes + SEND_PIECE - 1) / SEND_PIECE;
-
-  // Two cursors over the same piece sequence of this warp: `ld` issues loads SEND_AHEAD pieces
-  // ahead of `st`, which waits for a piece, scales it and stores it to the peer.
-  struct Cursor {
-    int item;      // item index, stride n_ctas; >= total_items: exhausted
-    int seq;       // ordinal of the item within this CTA
-    int row;       // segment row; rows of a warp are r_lo + warp, + NUM_WARPS, ...
-    int pc;
-    SendItem it;
-  };
-  auto seek = [&](Cursor& c) {
-    // Moves to the first item at or after c.item with a row for this warp.
-    while (c.item < total_items) {
-      c.it = send_decode(s, sh, tot, c.item);
-      c.row = c.it.r_lo + warp;
-      c.pc = 0;
-      if (c.row < c.it.r_hi) return;
-      c.item += n_ctas;
-      ++c.seq;
+  const int nv = s.d >> 3;                    // 16-byte pieces per row
+  const bool scaled = s.scale != nullptr;
+  for (int u = sender_id; u < total_units; u += n_senders) {
+    const int item = u / SEND_UNITS_PER_ITEM;
+    const SendItem it = send_decode(s, tot, item);
+    const int r0 = it.r_lo + (u - item * SEND_UNITS_PER_ITEM) * SEND_UNIT_ROWS;
+    const int r1 = min(r0 + SEND_UNIT_ROWS, it.r_hi);
+    if (r0 >= r1) continue;
+    // lanes 0..15 fetch the slot ids (and scales) of the unit's rows with one load
+    int slot_of = -1;
+    float scale_of = 1.f;
+    if (r0 + lane < r1) {
+      slot_of = __ldg(s.pos + it.src0 + (r0 + lane - it.rel0));
+      if (scaled) scale_of = Cvt<T>::to_f(static_cast<const T*>(s.scale)[slot_of]);
     }
-  };
-  auto advance = [&](Cursor& c) {
-    if (++c.pc < pieces_per_row) return;
-    c.pc = 0;
-    c.row += NUM_WARPS;
-    if (c.row < c.it.r_hi) return;
-    c.item += n_ctas;
-    ++c.seq;
-    seek(c);
-  };
-  auto issue_load = [&](const Cursor& c, int n) {
-    const int slot = n % SEND_SLOTS;
-    const int sl = s.pos[c.it.src0 + (c.row - c.it.rel0)];
-    const int off = c.pc * SEND_PIECE;
-    const uint32_t bytes = static_cast<uint32_t>(min(SEND_PIECE, row_bytes - off));
-    const uint8_t* src = static_cast<const uint8_t*>(s.x) + static_cast<long>(sl / s.k) * row_bytes + off;
-    uint64_t* bar = &sh->bar[warp][slot];
-    ptx::mbar_arrive_expect_tx(bar, bytes);
-    ptx::bulk_load(ring + slot * SEND_PIECE, src, bytes, bar);
-  };
-  // Publishes item `seq` of this CTA once every warp has seen its own stores of it complete.
-  auto signal_item = [&](int seq) {
-    ptx::fence_proxy_async_all();
-    __threadfence_system();
-    const int old = atomicAdd(&sh->done[seq % SEND_DONE_RING], 1);
-    if (old == NUM_WARPS - 1) {
-      sh->done[seq % SEND_DONE_RING] = 0;
-      __threadfence_system();
-      const SendItem it = send_decode(s, sh, tot, static_cast<int>(blockIdx.x) + seq * n_ctas);
-      int* flag = static_cast<int*>(s.flags.p[it.peer]) + static_cast<long>(it.blk) * kMaxPeers + s.me;
-      st_release_sys_i32(flag, epoch);
-    }
-  };
-
-  Cursor ld, st;
-  ld.item = static_cast<int>(blockIdx.x);
-  ld.seq = 0;
-  seek(ld);
-  st = ld;
-  int n_ld = 0, n_st = 0;       // pieces whose load / store has been issued
-  int closed = 0;               // items of this CTA this warp has closed (all its stores issued)
-  int groups_in_item = 0;       // store groups lane 0 issued for the item being filled
-  const int items_cta = total_items > static_cast<int>(blockIdx.x)
-                            ? (total_items - static_cast<int>(blockIdx.x) + n_ctas - 1) / n_ctas : 0;
-  bool ok = true;
-
-  // Closes items [closed, upto): item t is published one close later, when the stores of the
-  // following item have been issued and a bounded look-back wait proves those of t complete.
-  auto close_until = [&](int upto) {
-    while (closed < upto) {
-      if (lane == 0 && closed > 0 && *failed == 0) {
-        BulkWaitUpTo<SEND_SLOTS>::run(groups_in_item);
-        signal_item(closed - 1);
-      }
-      groups_in_item = 0;
-      ++closed;
-      if (closed % SEND_DONE_RING == 0) {
-        // the counter ring wraps: nobody may run ahead into slots that are still counting
-        asm volatile("bar.sync 3, %0;" ::"n"(NUM_THREADS) : "memory");
-      }
-    }
-  };
-
-  if (lane == 0) {
-    for (int a = 0; a < SEND_AHEAD && ld.item < total_items; ++a) {
-      issue_load(ld, n_ld++);
-      advance(ld);
-    }
-  }
-  while (st.item < total_items && ok) {
-    close_until(st.seq);
-    const int slot = n_st % SEND_SLOTS;
-    if (lane == 0 && ld.item < total_items) {
-      // the slot of the next load was last read by the store issued three pieces ago
-      ptx::bulk_wait_read<SEND_SLOTS - SEND_AHEAD - 1>();
-      issue_load(ld, n_ld++);
-      advance(ld);
-    }
-    const uint32_t parity = static_cast<uint32_t>(n_st / SEND_SLOTS) & 1u;
-    if (!send_wait(&sh->bar[warp][slot], parity, failed)) {
-      if (lane == 0) {
-        sh->failed = 1;
-        if (p.status != nullptr) atomicCAS(p.status, 0, STATUS_TIMEOUT_SENDER);
-      }
-      ok = false;
-      break;
-    }
-    const int sl = s.pos[st.it.src0 + (st.row - st.it.rel0)];
-    const int off = st.pc * SEND_PIECE;
-    const int bytes = min(SEND_PIECE, row_bytes - off);
-    uint8_t* piece = ring + slot * SEND_PIECE;
-    if (s.scale != nullptr) {
-      const float sc = Cvt<T>::to_f(static_cast<const T*>(s.scale)[sl]);
-      for (int o = lane * 16; o < bytes; o += 32 * 16) {
-        uint4 v = *reinterpret_cast<uint4*>(piece + o);
-        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+    T* dst_rows = static_cast<T*>(s.rows.p[it.peer]);
+    int64_t* dst_meta = static_cast<int64_t*>(s.meta.p[it.peer]);
+    for (int r = r0; r < r1; r += 2) {
+      const bool two = r + 1 < r1;
+      const int sl0 = __shfl_sync(0xffffffffu, slot_of, r - r0);
+      const int sl1 = __shfl_sync(0xffffffffu, slot_of, two ? r + 1 - r0 : r - r0);
+      const float sc0 = __shfl_sync(0xffffffffu, scale_of, r - r0);
+      const float sc1 = __shfl_sync(0xffffffffu, scale_of, two ? r + 1 - r0 : r - r0);
+      const uint4* in0 = reinterpret_cast<const uint4*>(static_cast<const T*>(s.x) + static_cast<long>(sl0 / s.k) * s.d);
+      const uint4* in1 = reinterpret_cast<const uint4*>(static_cast<const T*>(s.x) + static_cast<long>(sl1 / s.k) * s.d);
+      uint4* out0 = reinterpret_cast<uint4*>(dst_rows + (it.seg + r) * s.d);
+      uint4* out1 = reinterpret_cast<uint4*>(dst_rows + (it.seg + r + 1) * s.d);
+      for (int i0 = lane; i0 < nv; i0 += 128) {
+        uint4 v0[4], v1[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float a, b;
-          Cvt<T>::unpack(w[j], a, b);
-          w[j] = Cvt<T>::pack(a * sc, b * sc);
+        for (int q = 0; q < 4; ++q) {
+          if (i0 + q * 32 < nv) {
+            v0[q] = __ldg(in0 + i0 + q * 32);
+            if (two) v1[q] = __ldg(in1 + i0 + q * 32);
+          }
         }
-        *reinterpret_cast<uint4*>(piece + o) = v;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (i0 + q * 32 < nv) {
+            if (scaled) {
+              uint32_t* w0 = reinterpret_cast<uint32_t*>(&v0[q]);
+              uint32_t* w1 = reinterpret_cast<uint32_t*>(&v1[q]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float a, b;
+                Cvt<T>::unpack(w0[j], a, b);
+                w0[j] = Cvt<T>::pack(a * sc0, b * sc0);
+                if (two) {
+                  Cvt<T>::unpack(w1[j], a, b);
+                  w1[j] = Cvt<T>::pack(a * sc1, b * sc1);
+                }
+              }
+            }
+            out0[i0 + q * 32] = v0[q];
+            if (two) out1[i0 + q * 32] = v1[q];
+          }
+        }
       }
-      ptx::fence_proxy_async_smem();
-      __syncwarp();
+      if (dst_meta != nullptr && lane < (two ? 2 : 1)) {
+        dst_meta[it.seg + r + lane] =
+            (static_cast<int64_t>(s.me) << 32) | static_cast<int64_t>(lane == 0 ? sl0 : sl1);
+      }
     }
+    // Every lane orders its own stores at system scope; lane 0 then counts the unit's rows.
+    // The warp that completes the item clears the counter and raises the flag on the owner.
+    __threadfence_system();
+    __syncwarp();
     if (lane == 0) {
-      const long drow = st.it.seg + st.row;
-      uint8_t* dst = static_cast<uint8_t*>(s.rows.p[st.it.peer]) + drow * row_bytes + off;
-      ptx::bulk_store(dst, piece, static_cast<uint32_t>(bytes));
-      ptx::bulk_commit();
-      if (st.pc == 0 && s.meta.p[st.it.peer] != nullptr) {
-        static_cast<int64_t*>(s.meta.p[st.it.peer])[drow] =
-            (static_cast<int64_t>(s.me) << 32) | static_cast<int64_t>(sl);
+      const int n = r1 - r0;
+      const int old = atomicAdd(s.item_count + item, n);
+      if (old + n == it.r_hi - it.r_lo) {
+        s.item_count[item] = 0;
+        __threadfence_system();
+        int* flag = static_cast<int*>(s.flags.p[it.peer]) + static_cast<long>(it.blk) * kMaxPeers + s.me;
+        st_release_sys_i32(flag, epoch);
       }
     }
-    ++groups_in_item;
-    ++n_st;
-    advance(st);
-    __syncwarp();  // lanes stay within one phase of the ring barriers
   }
-  // Every warp closes every item (also after a failure: the others may be waiting for it at
-  // the ring barrier); after a failure nothing more is published.
-  close_until(items_cta);
-  if (lane == 0) {
-    ptx::bulk_wait<0>();
-    if (items_cta > 0 && *failed == 0) signal_item(items_cta - 1);
-  }
-  // Loads that were issued but never consumed (only after a failure) must land before the
-  // shared memory goes away.
-  if (!ok) {
-    const unsigned long long t0 = ptx::globaltimer();
-    while (ptx::globaltimer() - t0 < 200000ull) __nanosleep(1000);
-  }
-  __syncthreads();
 }
 
 template <int MODE, typename T, int ACT>
@@ -961,16 +806,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   using L = Layout<MODE>;
   constexpr int kStages = L::kStages;
 
-  // Sender CTAs (row modes only) take no part in the GEMM.
-  const int n_send = (MODE == kWgrad) ? 0 : p.send.n_ctas;
-  if constexpr (MODE != kWgrad) {
-    if (static_cast<int>(blockIdx.x) < n_send) {
-      sender_cta<T>(p, smem);
-      return;
-    }
-  }
-  const int cta = static_cast<int>(blockIdx.x) - n_send;
-  const int num_ctas = static_cast<int>(gridDim.x) - n_send;
+  const int cta = static_cast<int>(blockIdx.x);
+  const int num_ctas = static_cast<int>(gridDim.x);
   SharedAux* aux = reinterpret_cast<SharedAux*>(smem + L::kAuxOff);
 
   const int warp = threadIdx.x >> 5;
@@ -1064,7 +901,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
             while (true) {
               if (ld_acquire_sys_i32(flag) - gate_epoch >= 0) break;
               if ((++spins & 0x3f) == 0) {
-                if (*abort_flag != 0 || ptx::globaltimer() - t0 > p.gate.timeout_ns) {
+                // a failure already recorded on this GPU (by any kernel) ends the wait at once:
+                // one lost peer must not cost a full time-out in every tile that follows
+                const bool failed_before =
+                    p.status != nullptr && *reinterpret_cast<const volatile int*>(p.status) != 0;
+                if (*abort_flag != 0 || failed_before || ptx::globaltimer() - t0 > p.gate.timeout_ns) {
                   here = false;
                   break;
                 }
@@ -1194,7 +1035,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         ptx::umma_commit(&aux->tmem_full[acc]);
       }
     }
-  } else if (warp >= FIRST_EPI_WARP) {
+  } else if (warp < FIRST_EPI_WARP) {
+    // ============================================================== sender warps (2, 3)
+    if constexpr (MODE != kWgrad) {
+      if (p.send.enabled) {
+        sender_warp<T>(p, cta * NUM_SEND_WARPS + (warp - FIRST_SEND_WARP), num_ctas * NUM_SEND_WARPS, lane);
+      }
+    }
+  } else {
     // ============================================================== epilogue (warps 4..11)
     const int part = warp & 3;                          // TMEM lane quarter this warp may read
     const int half = (warp - FIRST_EPI_WARP) >> 2;      // which half of the accumulator columns

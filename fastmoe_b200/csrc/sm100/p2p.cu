@@ -103,8 +103,9 @@ __global__ void __launch_bounds__(1024, 1)
 count_exchange_kernel(const __grid_constant__ ExchangeCtx c, const int* __restrict__ lec, const __grid_constant__ PeerPtrs cnt, int n_expert,
                       int capacity_rows, int* __restrict__ dst_base, int* __restrict__ seg_base,
                       int* __restrict__ blk_base, int* __restrict__ expert_offs,
-                      int* __restrict__ seg_off, int* __restrict__ total_rows) {
-  extern __shared__ int sh[];  // [world * width] matrix, then [tot] column sums
+                      int* __restrict__ seg_off, int* __restrict__ total_rows,
+                      int* __restrict__ item_prefix) {
+  extern __shared__ int sh[];  // [world * width] matrix, [tot] column sums, [tot] items per pair
   const int tot = n_expert * c.world;
   const int width = tot + 1;   // a rank's row: its counts, then its receive capacity
   const int epoch = c.epoch[0] + 1;
@@ -151,6 +152,25 @@ count_exchange_kernel(const __grid_constant__ ExchangeCtx c, const int* __restri
     seg_base[g] = seg;
     blk_base[g] = blk;
     dst_base[g] = seg + before;
+    // row blocks my rows touch on the owner (clamped to its capacity), stored at the pair's
+    // place in send order; turned into a prefix below
+    int items = 0;
+    const int cnt_mine = mat[c.me * width + g];
+    int r_end = before + cnt_mine;
+    if (r_end > capacity_rows - seg) r_end = capacity_rows - seg;
+    if (cnt_mine > 0 && r_end > before) items = (r_end - 1) / kRowBlock - before / kRowBlock + 1;
+    int j = p - c.me;
+    if (j < 0) j += c.world;
+    col[tot + e * c.world + j] = items;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    item_prefix[0] = 0;
+    for (int q = 0; q < tot; ++q) {
+      run += col[tot + q];
+      item_prefix[q + 1] = run;
+    }
   }
   // 4. my own segments: expert offsets and, per expert, where each source's rows begin
   for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
@@ -601,9 +621,9 @@ int push_grid(int work_items, int warps_per_block) {
 cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const PeerPtrs& cnt,
                                   int n_expert, int capacity_rows, int* dst_base, int* seg_base,
                                   int* blk_base, int* expert_offs, int* seg_off, int* total_rows,
-                                  cudaStream_t stream) {
+                                  int* item_prefix, cudaStream_t stream) {
   const int tot = n_expert * ctx.world;
-  const size_t smem = (static_cast<size_t>(ctx.world) * (tot + 1) + tot) * sizeof(int);
+  const size_t smem = (static_cast<size_t>(ctx.world) * (tot + 1) + 2 * tot) * sizeof(int);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(count_exchange_kernel,
@@ -612,7 +632,7 @@ cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const 
   }
   count_exchange_kernel<<<1, 1024, smem, stream>>>(ctx, lec, cnt, n_expert, capacity_rows, dst_base,
                                                    seg_base, blk_base, expert_offs, seg_off,
-                                                   total_rows);
+                                                   total_rows, item_prefix);
   return cudaGetLastError();
 }
 

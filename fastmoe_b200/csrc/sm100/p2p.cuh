@@ -59,10 +59,13 @@ struct ExchangeCtx {
 //   seg_off[E][world + 1]  inside my expert e, the row where the rows of the j-th source begin
 //                       (source j is rank (me - j) mod world)
 //   total_rows[1]
+//   item_prefix[tot + 1]  exclusive prefix of the number of kRowBlock-row blocks my rows touch
+//                       on the owner, per (expert, peer) pair in send order: local expert e
+//                       outer, peer distance j inner, global expert ((me + j) mod world) * E + e
 cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const PeerPtrs& cnt,
                                   int n_expert, int capacity_rows, int* dst_base, int* seg_base,
                                   int* blk_base, int* expert_offs, int* seg_off, int* total_rows,
-                                  cudaStream_t stream);
+                                  int* item_prefix, cudaStream_t stream);
 
 // Backward passes reuse the forward routing: only the epoch advances.
 cudaError_t launch_begin_epoch(const ExchangeCtx& ctx, cudaStream_t stream);

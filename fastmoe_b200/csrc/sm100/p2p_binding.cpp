@@ -54,20 +54,21 @@ class ExchangeContext {
   void set_timeout_ms(double ms) { ctx_.timeout_ns = static_cast<unsigned long long>(ms * 1e6); }
 
   // `tables` is one int32 tensor holding, back to back: dst_base[tot], seg_base[tot],
-  // blk_base[tot], expert_offs[E + 1], seg_off[E * (world + 1)], total_rows[1].
+  // blk_base[tot], expert_offs[E + 1], seg_off[E * (world + 1)], total_rows[1],
+  // item_prefix[tot + 1].
   void count_exchange(torch::Tensor lec, std::vector<int64_t> cnt_ptrs, int64_t n_expert,
                       int64_t capacity_rows, torch::Tensor tables) {
     c10::cuda::CUDAGuard guard(lec.device());
     const int64_t tot = n_expert * ctx_.world;
     TORCH_CHECK(tables.scalar_type() == torch::kInt && tables.is_contiguous() &&
-                    tables.numel() >= 3 * tot + (n_expert + 1) + n_expert * (ctx_.world + 1) + 1,
+                    tables.numel() >= 4 * tot + (n_expert + 1) + n_expert * (ctx_.world + 1) + 2,
                 "count_exchange: table tensor too small");
     int* t = tables.data_ptr<int>();
     FMOE_P2P_CHECK(fmoe::launch_count_exchange(
         ctx_, lec.data_ptr<int>(), to_ptrs(cnt_ptrs), static_cast<int>(n_expert),
         static_cast<int>(capacity_rows), t, t + tot, t + 2 * tot, t + 3 * tot,
         t + 3 * tot + n_expert + 1, t + 3 * tot + n_expert + 1 + n_expert * (ctx_.world + 1),
-        stream()));
+        t + 3 * tot + n_expert + 2 + n_expert * (ctx_.world + 1), stream()));
   }
 
   std::vector<torch::Tensor> capacity_grant(torch::Tensor lec, torch::Tensor cap,
@@ -262,8 +263,9 @@ class ExchangeContext {
       sa.me = ctx_.me;
       sa.k = d["k"].cast<int>();
       sa.capacity = d["capacity"].cast<int>();
-      sa.n_ctas = d["n_ctas"].cast<int>();
-      TORCH_CHECK(sa.n_ctas > 0 && sa.n_ctas < sms, "gemm_ep: sender CTA count");
+      sa.item_prefix = tensor("item_prefix").data_ptr<int>();
+      sa.item_count = tensor("item_count").data_ptr<int>();
+      sa.enabled = 1;
       TORCH_CHECK(sa.d == g.k, "gemm_ep: sent rows must have the GEMM's K extent");
     }
     if (!gate_flag_ptrs.empty()) {

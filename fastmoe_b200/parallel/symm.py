@@ -75,8 +75,6 @@ class SymmWorkspace:
         self._buffers = {}
         self.signal, self.signal_ptrs = self._alloc("signal", nat.P2P_NUM_CHANNELS * nat.P2P_MAX_PEERS * 4)
         self.cnt, self.cnt_ptrs = self._alloc("counts", self.world * (_MAX_TOT_EXPERT + 1) * 4)
-        self.signal.zero_()
-        self.cnt.zero_()
         self.epoch = torch.zeros(8, dtype=torch.int32, device=device)
         self._budget = None
         self._pool = {}
@@ -92,26 +90,29 @@ class SymmWorkspace:
         t = self._symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
         hdl = self._symm_mem.rendezvous(t, group=self.group)
         ptrs = [int(p) for p in hdl.buffer_ptrs]
-        # Never hand out uninitialised staging memory: kernels that continue after a peer's
-        # time-out would otherwise act on whatever bits the allocation held.
-        t.zero_()
+        self._clear_new(t)
         self._buffers[name] = (t, ptrs, hdl)
         return t, ptrs
 
-    def buffer(self, name, nbytes, zero=False):
-        r"""Symmetric byte buffer of at least ``nbytes`` (collective when it has to grow).
+    def _clear_new(self, t):
+        r"""Zero a fresh symmetric allocation and meet the peers before anybody may store into it.
 
-        ``zero``: the buffer holds flag words that peers write; a new allocation is cleared and
-        all ranks meet before anybody may store into it."""
+        Never hand out uninitialised staging memory: kernels that continue after a peer's
+        time-out would otherwise act on whatever bits the allocation held.  The barrier matters
+        as much as the fill: a peer that is ahead could otherwise deliver rows into the buffer
+        before this rank's fill has run, and the fill would wipe them."""
+        t.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def buffer(self, name, nbytes):
+        r"""Symmetric byte buffer of at least ``nbytes`` (collective when it has to grow; a new
+        allocation is cleared and all ranks meet before anybody may store into it)."""
         have = self._buffers.get(name)
         if have is None or have[0].numel() < nbytes:
             torch.cuda.synchronize(self.device)
             self._alloc(name, max(nbytes, 1))
             have = self._buffers[name]
-            if zero:
-                have[0].zero_()
-                torch.cuda.synchronize(self.device)
-                dist.barrier(self.group)
         return have[0], have[1]
 
     # ------------------------------------------------------------------ token budget
@@ -166,14 +167,24 @@ class SymmWorkspace:
             ptrs = [int(p) for p in hdl.buffer_ptrs]
             self._leased_handles = getattr(self, "_leased_handles", [])
             self._leased_handles.append(hdl)
-            t.zero_()
+            self._clear_new(t)
         return _Lease(self, key, t, ptrs)
+
+    def item_counters(self, capacity, n_expert):
+        r"""Local, self-clearing row counters of the sender warps: one per 128-row block this rank
+        can be sending in one exchange (zero between launches)."""
+        need = capacity // 128 + 2 * n_expert * self.world + 2
+        have = getattr(self, "_item_count", None)
+        if have is None or have.numel() < need:
+            have = torch.zeros(need, dtype=torch.int32, device=self.device)
+            self._item_count = have
+        return have
 
     def gate_flags(self, capacity, n_expert):
         r"""Arrival flags of the receive buffer: int32 ``[blocks][P2P_MAX_PEERS]``."""
         nat = native.get()
         blocks = capacity // 128 + n_expert + 1
-        return self.buffer("gate", blocks * nat.P2P_MAX_PEERS * 4, zero=True)
+        return self.buffer("gate", blocks * nat.P2P_MAX_PEERS * 4)
 
     def set_timeout_ms(self, ms):
         self.ctx.set_timeout_ms(float(ms))
@@ -260,7 +271,7 @@ class _Tables:
     def __init__(self, ws, lec, n_expert, capacity):
         tot = n_expert * ws.world
         w1 = ws.world + 1
-        self.buf = torch.empty(3 * tot + (n_expert + 1) + n_expert * w1 + 1, dtype=torch.int32,
+        self.buf = torch.empty(4 * tot + (n_expert + 1) + n_expert * w1 + 2, dtype=torch.int32,
                                device=lec.device)
         ws.ctx.count_exchange(lec, ws.cnt_ptrs, n_expert, capacity, self.buf)
         o = 0
@@ -269,7 +280,8 @@ class _Tables:
         self.blk_base = self.buf[o:o + tot]; o += tot          # noqa: E702
         self.expert_offs = self.buf[o:o + n_expert + 1]; o += n_expert + 1  # noqa: E702
         self.seg_off = self.buf[o:o + n_expert * w1]; o += n_expert * w1    # noqa: E702
-        self.total = self.buf[o:o + 1]
+        self.total = self.buf[o:o + 1]; o += 1                 # noqa: E702
+        self.item_prefix = self.buf[o:o + tot + 1]
 
 
 def _rows_view(byte_tensor, rows, d, dtype):
@@ -384,7 +396,7 @@ class _FusedEPMLP(Function):
         send = dict(x=x, pos=pos, my_offs=my_offs, dst_base=tb.dst_base, seg_base=tb.seg_base,
                     blk_base=tb.blk_base, rows_ptrs=lease.ptrs, meta_ptrs=meta_ptrs,
                     flag_ptrs=flag_ptrs, n_expert=n_expert, k=k, capacity=capacity,
-                    n_ctas=config.send_ctas())
+                    item_prefix=tb.item_prefix, item_count=ws.item_counters(capacity, n_expert))
         with fused_range("ep.dispatch_gemm1"):
             a = torch.empty(capacity, h, dtype=x.dtype, device=dev)
             pre = gg.pre_buffer(capacity, h, n_expert, x.dtype, dev) if code != 0 else a
@@ -436,7 +448,7 @@ class _FusedEPMLP(Function):
         send = dict(x=dout, pos=pos, my_offs=my_offs, dst_base=tb.dst_base, seg_base=tb.seg_base,
                     blk_base=tb.blk_base, scale=score, rows_ptrs=rows_ptrs, meta_ptrs=None,
                     flag_ptrs=flag_ptrs, n_expert=n_expert, k=k, capacity=capacity,
-                    n_ctas=config.send_ctas())
+                    item_prefix=tb.item_prefix, item_count=ws.item_counters(capacity, n_expert))
         da = torch.empty(capacity, h, dtype=dout.dtype, device=dout.device)
         ws.ctx.gemm_ep(gg.MODE_NN, dys, w2, tb.expert_offs, out=da, aux=pre if code != 0 else None,
                        act=code, epi=gg.EPI_DACT if code != 0 else gg.EPI_BIAS_ACT, send=send,

@@ -12,7 +12,9 @@ launch overhead, which for a single MoE layer is as large as the GPU time itself
 
 Rules for the captured function: no ``.item()`` / ``.cpu()`` / printing of device values, the
 optimizer must be capturable (``torch.optim.Adam(..., capturable=True)``), and shapes must not
-change between calls.  Gates that need host decisions (``SwipeGate``, ``FasterGate``) cannot be
+change between calls.  Run the model's first backward pass inside this helper (or on a side
+stream): autograd binds every parameter's gradient-accumulation node to the stream of its first
+use, and a node bound to the default stream cannot join a capture.  Gates that need host decisions (``SwipeGate``, ``FasterGate``) cannot be
 captured.
 """
 import torch

@@ -209,14 +209,38 @@ def case_multi_layer():
         return ([y.detach().float().clone(), xx.grad.float().clone()]
                 + [p.grad.float().clone() for p in model.parameters()])
 
-    fused = [grads_of(x) for x in xs]
-    os.environ["FMOE_FUSED"] = "0"
-    plain = [grads_of(x) for x in xs]
-    os.environ["FMOE_FUSED"] = "1"
+    # Everything before the capture runs on a side stream as well: autograd binds a parameter's
+    # gradient-accumulation node to the stream of its first use, and a node bound to the
+    # default stream cannot take part in a capture later.
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fused = [grads_of(x) for x in xs]
+        os.environ["FMOE_FUSED"] = "0"
+        plain = [grads_of(x) for x in xs]
+        os.environ["FMOE_FUSED"] = "1"
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    # Through three layers a rounding difference between the two paths can flip a token's top-k
+    # choice in a later layer, so single rows may differ a lot: the paths have to agree on all
+    # but a few per cent of the elements ...
+    names = ["y", "grad_x"] + [n for n, _ in model.named_parameters()]
     for a, b in zip(fused, plain):
-        for t, u in zip(a, b):
-            err = float((t - u).abs().max())
-            assert err <= 0.05 * float(u.abs().max()) + 2e-3, err
+        for name, t, u in zip(names, a, b):
+            tol = 0.05 * float(u.abs().max()) + 2e-3
+            bad = float(((t - u).abs() > tol).float().mean())
+            assert bad <= 0.03, (name, bad)
+    # ... and the peer-to-peer path has to reproduce itself bit for bit: a buffer overwritten
+    # early or read late by one of the three layers would show up here
+    with torch.cuda.stream(side):
+        again = [grads_of(x) for x in xs]
+    torch.cuda.synchronize()
+    for a, b in zip(fused, again):
+        for name, t, u in zip(names, a, b):
+            if ".gate." in name:   # the gate's weight gradient is summed with fp32 atomics
+                assert torch.allclose(t, u, rtol=1e-4, atol=1e-5), (name, float((t - u).abs().max()))
+            else:
+                assert torch.equal(t, u), (name, float((t - u).abs().max()))
 
     # the same three-layer step under graph replay: outputs must match the eager fused run
     static_grads = {}
@@ -265,6 +289,8 @@ def case_recv_overflow():
     except RuntimeError as exc:
         assert str(nat.STATUS_RECV_OVERFLOW) in str(exc), str(exc)
     dist.barrier()
+    # a near-uniform gate and a buffer with 60 % head-room: nothing is dropped any more
+    os.environ["FMOE_RECV_CAPACITY_FACTOR"] = "1.6"
     with torch.no_grad():
         layer.gate.gate.bias.zero_()
         layer.gate.gate.weight.normal_(0, 0.02)
@@ -273,8 +299,8 @@ def case_recv_overflow():
     os.environ["FMOE_FUSED"] = "0"
     y2, gx2, _ = _run(layer, x, gy)
     os.environ["FMOE_FUSED"] = "1"
-    del os.environ["FMOE_RECV_CAPACITY_FACTOR"]
     assert check_device_status(_dev()) == 0
+    del os.environ["FMOE_RECV_CAPACITY_FACTOR"]
     # balanced routing fits into the bounded buffer with probability ~1 only when nothing is
     # dropped; compare where the bounded run kept everything
     if float((y1 - y2).abs().max()) > 2e-2:
