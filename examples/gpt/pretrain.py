@@ -32,6 +32,7 @@ from _common import Stopwatch, init_distributed, max_over_ranks  # noqa: E402
 from fastmoe_b200.megatron import stub  # noqa: E402
 from fastmoe_b200.megatron.optimizer import clip_grad_norm_moe  # noqa: E402
 from fastmoe_b200.megatron.utils import add_fmoe_args  # noqa: E402
+from fastmoe_b200.utils import check_device_status  # noqa: E402
 from fastmoe_b200.models.gpt import GPTConfig, GPTModel, gpt_flops_per_token  # noqa: E402
 
 
@@ -142,6 +143,7 @@ def main():
         opt.step()
         window += 1
         if it % args.log_interval == 0 or it == args.train_iters:
+            check_device_status()   # raises if any kernel reported a peer time-out or an overflow
             watch.__exit__()
             ms = max_over_ranks(watch.ms, device) / window
             if rank == 0:
@@ -204,6 +206,7 @@ def run_pipeline(args, model, ddp, opt, runner_cls, stage, pp, prev_rank, next_r
         opt.step()
         window += 1
         if it % args.log_interval == 0 or it == args.train_iters:
+            check_device_status()   # raises if any kernel reported a peer time-out or an overflow
             watch.__exit__()
             ms = max_over_ranks(watch.ms, device) / window
             if rank == world - 1:

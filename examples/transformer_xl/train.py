@@ -37,6 +37,7 @@ from data_utils import default_cutoffs, get_lm_corpus  # noqa: E402
 from fastmoe_b200 import DistributedGroupedDataParallel, checkpoint  # noqa: E402
 from fastmoe_b200.megatron.optimizer import clip_grad_norm_moe  # noqa: E402
 from fastmoe_b200.models import MemTransformerLM  # noqa: E402
+from fastmoe_b200.utils import check_device_status  # noqa: E402
 
 
 def get_args(argv=None):
@@ -234,6 +235,7 @@ def main(argv=None):
             window += 1
             window_loss += loss_value
             if step % args.log_interval == 0 or step == args.max_step:
+                check_device_status()   # raises if any kernel reported a peer time-out or an overflow
                 watch.__exit__()
                 ms = max_over_ranks(watch.ms, device) / window
                 if rank == 0:

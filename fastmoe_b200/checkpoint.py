@@ -70,6 +70,10 @@ def step_dir(directory, step):
 
 def save(directory, step, module, optimizer=None, group=None, extra=None):
     r"""Write one checkpoint; collective over ``group`` (the expert-parallel group)."""
+    # A kernel that gave up on a peer (bounded wait) or dropped rows (bounded receive buffer)
+    # only leaves a code in the device status word: never write a checkpoint of such a run.
+    from .utils import check_device_status
+    check_device_status()
     rank, _world = _rank_world(group)
     path = step_dir(directory, step)
     os.makedirs(path, exist_ok=True)

@@ -48,12 +48,18 @@ class DistributedGroupedDataParallel(nn.Module):
     every bucket from the first member of its group at construction.
     """
 
-    def __init__(self, module, auto_allreduce=False, need_sync=True, **kwargs):
+    def __init__(self, module, auto_allreduce=False, need_sync=True, status_check_interval=100,
+                 **kwargs):
         assert not auto_allreduce, "Automatic all-reduce is not implemented yet"
         super().__init__()
         self.module = module
         self.comms = {}
         self._side_stream = None
+        # Every `status_check_interval` reductions the device status word is read (one
+        # synchronisation): a peer time-out or a receive-buffer overflow reported by any kernel
+        # since the last check raises here instead of training on.  0 switches the check off.
+        self.status_check_interval = status_check_interval
+        self._reductions = 0
         for name, group in kwargs.items():
             if name.endswith("_group"):
                 self.comms[name[:-len("_group")]] = group
@@ -90,6 +96,11 @@ class DistributedGroupedDataParallel(nn.Module):
             self.allreduce_gradients(no_scale, reduce_after, fp32_allreduce)
             return _ReduceHandle(None)
         from .ops import allreduce as _ar
+        self._reductions += 1
+        if (self.status_check_interval and self._reductions % self.status_check_interval == 0
+                and torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing()):
+            from .utils import check_device_status
+            check_device_status()
         for (dp_comm, dtype), group_params in _bucket_params(self.module.parameters(), True).items():
             if dp_comm not in self.comms:
                 continue

@@ -34,7 +34,8 @@ class DCGate(NaiveGate):
         self.set_loss(_gshard.gshard_balance_loss(logits.view(-1, self.tot_expert), first_choice,
                                                   self.tot_expert, self.num_expert))
         _, _, experts = limit_by_capacity(experts, self.num_expert, self.world_size,
-                                          self.global_capacity(x.shape[0]))
+                                          self.global_capacity(x.shape[0]),
+                                          group=getattr(self, "moe_group", None))
         if self.random_routing:
             experts = _gshard.drop_second_expert_randomly(experts, weights)
         return experts, weights

@@ -50,6 +50,7 @@ class SwitchGate(NaiveGate):
         prob = torch.softmax(self._jitter(self.gate(inp)).float(), dim=-1)
         score, winner = prob.max(dim=-1, keepdim=True)
         _, _, winner = limit_by_capacity(winner, self.num_expert, self.world_size,
-                                         self._slots_per_expert(inp.shape[0]))
+                                         self._slots_per_expert(inp.shape[0]),
+                                         group=getattr(self, "moe_group", None))
         self.set_loss(self._balance_loss(prob, winner))
         return winner, score.to(inp.dtype)

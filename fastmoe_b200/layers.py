@@ -116,6 +116,9 @@ class FMoE(nn.Module):
         self.mask = mask
         self.mask_dict = mask_dict
         self.moe_group = moe_group
+        # Gates that exchange counts (capacity limits) must do so inside the layer's own
+        # expert-parallel group.  Kept out of the module tree: a group is not a sub-module.
+        object.__setattr__(self.gate, "moe_group", moe_group)
 
     # ------------------------------------------------------------------ expert calls
     def expert_fn(self, inp, fwd_expert_count):
