@@ -593,6 +593,83 @@ __global__ void allgather_kernel(const __grid_constant__ ExchangeCtx c, const ui
   for (long i = tid; i < total; i += stride) out[i] = __ldcg(mine + i);
 }
 
+// Broadcast from `root`: the owner pushes its data into every peer's symmetric buffer — one
+// write per peer, (W - 1) x n bytes over NVLink in total — after every peer has reported that
+// its buffer may be overwritten; everybody then copies its own buffer out.  This is the
+// shadow-expert parameter broadcast (cuda/fastermoe/smart_schedule.h:182, ncclBcast there).
+__global__ void broadcast_kernel(const __grid_constant__ ExchangeCtx c, const uint4* __restrict__ src,
+                                 const __grid_constant__ PeerPtrs bufs, uint4* __restrict__ out, long nvec,
+                                 int root) {
+  const int target = 2 * c.epoch[kReduceEpochWord];
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    __threadfence_system();
+    st_release_sys(flag_of(c.flags.p[root], kChanReduce, c.me), target);
+  }
+  const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  if (c.me == root) {
+    block_wait_all(c, kChanReduce, target);
+    for (long i = tid; i < nvec; i += stride) {
+      const uint4 v = __ldg(src + i);
+      for (int p = 0; p < c.world; ++p) reinterpret_cast<uint4*>(bufs.p[p])[i] = v;
+    }
+    if (last_block(c.epoch + 5)) {
+      if (threadIdx.x == 0) signal_all(c, kChanReduce, target + 1);
+    }
+  }
+  if (threadIdx.x == 0) wait_flag(c, kChanReduce, root, target + 1);
+  __syncthreads();
+  const uint4* mine = reinterpret_cast<const uint4*>(bufs.p[c.me]);
+  for (long i = tid; i < nvec; i += stride) out[i] = __ldcg(mine + i);
+}
+
+// Reduce to `root`: every rank has put its contribution into its own symmetric buffer; the
+// owner sums all of them in rank order (fp32 accumulation) into `out`; the others only wait
+// until the owner is done reading.  This is the gradient reduction of a shadowed expert
+// (cuda/fastermoe/smart_schedule.cpp:41-63, ncclReduce there).
+template <typename T, typename Vec, int PER>
+__global__ void reduce_to_root_kernel(const __grid_constant__ ExchangeCtx c, const __grid_constant__ PeerPtrs bufs,
+                                      T* __restrict__ out, long n, int root) {
+  const int target = 2 * c.epoch[kReduceEpochWord];
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    __threadfence_system();
+    st_release_sys(flag_of(c.flags.p[root], kChanReduce, c.me), target);
+  }
+  if (c.me == root) {
+    block_wait_all(c, kChanReduce, target);
+    const long nvec = n / PER;
+    for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<long>(gridDim.x) * blockDim.x) {
+      float acc[PER];
+#pragma unroll
+      for (int q = 0; q < PER; ++q) acc[q] = 0.f;
+      for (int p = 0; p < c.world; ++p) {
+        Vec v = __ldcg(reinterpret_cast<const Vec*>(bufs.p[p]) + i);
+        const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int q = 0; q < PER; ++q) acc[q] += as_float(e[q]);
+      }
+      Vec r;
+      T* e = reinterpret_cast<T*>(&r);
+#pragma unroll
+      for (int q = 0; q < PER; ++q) e[q] = from_float<T>(acc[q]);
+      reinterpret_cast<Vec*>(out)[i] = r;
+    }
+    for (long i = nvec * PER + blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<long>(gridDim.x) * blockDim.x) {
+      float acc = 0.f;
+      for (int p = 0; p < c.world; ++p) acc += as_float(static_cast<const T*>(bufs.p[p])[i]);
+      out[i] = from_float<T>(acc);
+    }
+    if (last_block(c.epoch + 5)) {
+      if (threadIdx.x == 0) signal_all(c, kChanReduce, target + 1);
+    }
+  } else {
+    if (threadIdx.x == 0) wait_flag(c, kChanReduce, root, target + 1);
+    __syncthreads();
+  }
+}
+
 // Waits until every peer has published the current epoch on `channel` (its rows have landed in
 // this rank's staging buffer); the kernels behind it in the stream may then read the buffer in
 // place.
@@ -777,6 +854,38 @@ cudaError_t launch_allgather(const ExchangeCtx& ctx, const void* src, const Peer
   if (blocks < 1) blocks = 1;
   allgather_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
       ctx, static_cast<const uint4*>(src), bufs, static_cast<uint4*>(out), nvec);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_broadcast(const ExchangeCtx& ctx, const void* src, const PeerPtrs& bufs, void* out,
+                             long bytes, int root, cudaStream_t stream) {
+  if (bytes % 16 != 0 || root < 0 || root >= ctx.world) return cudaErrorInvalidValue;
+  const long nvec = bytes / 16;
+  long blocks = (nvec + 255) / 256;
+  if (blocks > 148 * 2) blocks = 148 * 2;  // whole grid resident: every block waits mid-kernel
+  if (blocks < 1) blocks = 1;
+  broadcast_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+      ctx, static_cast<const uint4*>(src), bufs, static_cast<uint4*>(out), nvec, root);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_to_root(const ExchangeCtx& ctx, int dtype, const PeerPtrs& bufs, void* out,
+                                  long n, int root, cudaStream_t stream) {
+  if (root < 0 || root >= ctx.world) return cudaErrorInvalidValue;
+  long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks < 1) blocks = 1;
+  const int grid = static_cast<int>(blocks);
+  if (dtype == 0) {
+    reduce_to_root_kernel<__nv_bfloat16, uint4, 8><<<grid, 256, 0, stream>>>(
+        ctx, bufs, static_cast<__nv_bfloat16*>(out), n, root);
+  } else if (dtype == 1) {
+    reduce_to_root_kernel<__half, uint4, 8><<<grid, 256, 0, stream>>>(ctx, bufs, static_cast<__half*>(out), n, root);
+  } else if (dtype == 2) {
+    reduce_to_root_kernel<float, uint4, 4><<<grid, 256, 0, stream>>>(ctx, bufs, static_cast<float*>(out), n, root);
+  } else {
+    return cudaErrorInvalidValue;
+  }
   return cudaGetLastError();
 }
 

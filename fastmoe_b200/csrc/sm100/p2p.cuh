@@ -118,6 +118,18 @@ cudaError_t launch_allreduce_two_shot(const ExchangeCtx& ctx, int dtype, const P
 cudaError_t launch_allgather(const ExchangeCtx& ctx, const void* src, const PeerPtrs& bufs,
                              void* out, long bytes_per_rank, cudaStream_t stream);
 
+// Broadcast of `bytes` (a multiple of 16) from rank `root`: the owner stores its `src` into every
+// peer's symmetric buffer once; every rank copies its buffer to `out`.  `src` is read on the
+// root only.  Call launch_begin_reduce_epoch right before.
+cudaError_t launch_broadcast(const ExchangeCtx& ctx, const void* src, const PeerPtrs& bufs, void* out,
+                             long bytes, int root, cudaStream_t stream);
+
+// Sum over ranks of the symmetric buffers (n elements; dtype 0 bf16, 1 f16, 2 f32), formed by
+// rank `root` alone into its `out`; other ranks' `out` is not written.  Call
+// launch_begin_reduce_epoch right before.
+cudaError_t launch_reduce_to_root(const ExchangeCtx& ctx, int dtype, const PeerPtrs& bufs, void* out,
+                                  long n, int root, cudaStream_t stream);
+
 // Rank-ordered capacity grants from one exchange of request counts and capacities.
 // lec: int32 [world * n_expert] requests of this rank; cap: int32 [n_expert] capacities of this
 // rank's experts; cnt: symmetric int32 buffers of 2 * world * (world + 1) * n_expert entries.

@@ -166,6 +166,35 @@ class ExchangeContext {
     }
   }
 
+  // out = rank `root`'s `src` on every rank (flat bytes, a multiple of 16).
+  void broadcast(torch::Tensor src, std::vector<int64_t> buf_ptrs, torch::Tensor out, int64_t root) {
+    TORCH_CHECK(src.is_cuda() && src.is_contiguous() && out.is_contiguous(), "broadcast operands");
+    const int64_t bytes = out.numel() * out.element_size();
+    TORCH_CHECK(src.numel() * src.element_size() == bytes && bytes % 16 == 0, "broadcast sizes");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(src.data_ptr()) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0,
+                "broadcast operands must be 16-byte aligned");
+    c10::cuda::CUDAGuard guard(out.device());
+    FMOE_P2P_CHECK(fmoe::launch_begin_reduce_epoch(ctx_, stream()));
+    FMOE_P2P_CHECK(fmoe::launch_broadcast(ctx_, src.data_ptr(), to_ptrs(buf_ptrs), out.data_ptr(),
+                                          bytes, static_cast<int>(root), stream()));
+  }
+
+  // out (on `root` only) = sum over ranks of the symmetric buffers' first n elements.
+  void reduce_to_root(std::vector<int64_t> buf_ptrs, torch::Tensor out, int64_t n, int64_t root) {
+    c10::cuda::CUDAGuard guard(out.device());
+    int code;
+    switch (out.scalar_type()) {
+      case torch::kBFloat16: code = 0; break;
+      case torch::kHalf: code = 1; break;
+      case torch::kFloat: code = 2; break;
+      default: TORCH_CHECK(false, "reduce_to_root: bf16, fp16 or fp32"); code = -1;
+    }
+    FMOE_P2P_CHECK(fmoe::launch_begin_reduce_epoch(ctx_, stream()));
+    FMOE_P2P_CHECK(fmoe::launch_reduce_to_root(ctx_, code, to_ptrs(buf_ptrs), out.data_ptr(), n,
+                                               static_cast<int>(root), stream()));
+  }
+
   // out[r * n : (r + 1) * n] = rank r's `src` (flat bytes; src.nbytes a multiple of 16).
   void allgather(torch::Tensor src, std::vector<int64_t> buf_ptrs, torch::Tensor out) {
     TORCH_CHECK(src.is_cuda() && src.is_contiguous() && out.is_contiguous(), "allgather operands");
@@ -327,6 +356,8 @@ void bind_p2p(pybind11::module& m) {
       .def("return_push", &ExchangeContext::return_push)
       .def("wait_combine", &ExchangeContext::wait_combine)
       .def("allgather", &ExchangeContext::allgather)
+      .def("broadcast", &ExchangeContext::broadcast)
+      .def("reduce_to_root", &ExchangeContext::reduce_to_root)
       .def("allreduce", &ExchangeContext::allreduce, py::arg("buf_ptrs"), py::arg("out"),
            py::arg("n"), py::arg("scale"), py::arg("two_shot") = false)
       .def("gemm_ep", &ExchangeContext::gemm_ep, py::arg("mode"), py::arg("a"), py::arg("b"),

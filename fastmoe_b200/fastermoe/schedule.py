@@ -67,17 +67,22 @@ class _ChunkAllToAll(Function):
 
 
 class _BroadcastParams(Function):
-    r"""Owner's flat parameters to every rank; backward sums the gradients at the owner."""
+    r"""Owner's flat parameters to every rank; backward sums the gradients at the owner.
+
+    On B200s both directions are single peer-to-peer kernels: the owner pushes the parameters
+    into every peer's symmetric buffer (one write per peer), and in backward the owner alone
+    reads and sums the peers' gradient buffers.  Elsewhere: the collective library."""
 
     @staticmethod
     def forward(ctx, flat, anchor, owner_global_rank, is_owner, group):
         ctx.args = owner_global_rank, is_owner, group
         from ..parallel import symm
-        # On B200s: one peer-to-peer kernel (non-owners contribute zeros, the sum is the
-        # owner's parameters); otherwise the collective library's broadcast.
-        summed = symm.allreduce_flat(flat.detach() if is_owner else torch.zeros_like(flat), group)
-        if summed is not None:
-            return summed
+        owner_in_group = dist.get_group_rank(group, owner_global_rank) if group is not None \
+            else owner_global_rank
+        ctx.owner_in_group = owner_in_group
+        pushed = symm.broadcast_flat(flat, owner_in_group, group)
+        if pushed is not None:
+            return pushed
         buf = flat.detach().clone()
         dist.broadcast(buf, owner_global_rank, group=group)
         return buf
@@ -86,9 +91,9 @@ class _BroadcastParams(Function):
     def backward(ctx, grad):
         owner, is_owner, group = ctx.args
         from ..parallel import symm
-        summed = symm.allreduce_flat(grad.contiguous(), group)
+        summed = symm.reduce_flat_to_owner(grad.contiguous(), ctx.owner_in_group, group)
         if summed is not None:
-            return (summed if is_owner else torch.zeros_like(summed)), None, None, None, None
+            return summed, None, None, None, None
         grad = grad.contiguous().clone()
         dist.reduce(grad, owner, op=dist.ReduceOp.SUM, group=group)
         return (grad if is_owner else torch.zeros_like(grad)), None, None, None, None

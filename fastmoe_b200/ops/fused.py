@@ -146,6 +146,32 @@ def expert_mlp(layer, xs, offs):
     return _GroupedLinear.apply(hid.contiguous(), e.h4toh.weight, e.h4toh.bias, offs)
 
 
+def expert_mlp_weights(xs, offs, w1, b1, w2, b2, activation):
+    r"""Both expert linears with explicit weights ``[G, h, d]`` / ``[G, d, h]`` (``activation`` is
+    the module between them)."""
+    act = activation_kind(activation)
+    if act is not None:
+        return _ExpertMLP.apply(xs, w1, b1, w2, b2, offs, act)
+    hid = _GroupedLinear.apply(xs, w1, b1, offs)
+    hid = activation(hid)
+    return _GroupedLinear.apply(hid.contiguous(), w2, b2, offs)
+
+
+def moe_mlp_local(x, gate_idx, gate_score, w1, b1, w2, b2, activation):
+    r"""The single-GPU fused MoE MLP over the ``G = w1.shape[0]`` experts given by explicit weights
+    (``gate_idx`` in ``[0, G)`` or ``-1`` for slots that take no part).  Used for shadow
+    experts, whose parameters arrive by broadcast and are not module parameters."""
+    nat = native.get()
+    k = gate_idx.shape[1]
+    idx = gate_idx.contiguous().view(-1)
+    score = gate_score.reshape(-1).to(x.dtype)
+    _counts, rank, offs = nat.route_offs(idx, w1.shape[0])
+    xs = _Dispatch.apply(x.contiguous(), idx, rank, offs, k)
+    ys = expert_mlp_weights(xs, offs, w1.contiguous(), b1.contiguous(), w2.contiguous(), b2.contiguous(),
+                            activation)
+    return _Combine.apply(ys, score, idx, rank, offs, k)
+
+
 def moe_mlp_forward(layer, x, gate_idx, gate_score):
     r"""``[B, d] → [B, d]`` for one ``FMoETransformerMLP`` call on the GPU."""
     if layer.world_size > 1 or _forced_ep():

@@ -585,6 +585,56 @@ def allreduce_flat(flat, comm, scale=1.0):
     return out
 
 
+def broadcast_flat(flat, owner, comm):
+    r"""The owner's 1-D tensor on every rank of ``comm`` (``owner`` is a rank inside the group),
+    pushed by the owner with one peer-to-peer write per peer; ``None`` when that path is not
+    available.  ``flat`` must have the same length and dtype everywhere; its values only matter
+    on the owner.  Parity: the ``ncclBcast`` of shadow-expert parameters,
+    ``cuda/fastermoe/smart_schedule.h:182``."""
+    if not flat.is_cuda or not config.fused_enabled():
+        return None
+    if comm is None:
+        comm = dist.group.WORLD
+    nbytes = flat.numel() * flat.element_size()
+    if dist.get_backend(comm) != "nccl" or nbytes == 0 or nbytes > _AR_MAX_BYTES:
+        return None
+    ws = get_workspace(comm, flat.device)
+    if ws is None:
+        return None
+    padded = _ar_buffer_bytes(nbytes)
+    _buf, ptrs = ws.buffer("broadcast", padded)
+    src = flat.detach().reshape(-1).contiguous()
+    if padded != nbytes or src.data_ptr() % 16 != 0:
+        grown = torch.zeros(padded // flat.element_size(), dtype=flat.dtype, device=flat.device)
+        grown[:flat.numel()] = src
+        src = grown
+    out = torch.empty_like(src)
+    ws.ctx.broadcast(src, ptrs, out, int(owner))
+    return out[:flat.numel()]
+
+
+def reduce_flat_to_owner(flat, owner, comm):
+    r"""Sum of the ranks' 1-D tensors, formed on ``owner`` only (peer-to-peer loads by the owner);
+    returns the sum there and zeros elsewhere, or ``None`` when the path is not available.
+    Parity: ``reduce_grad`` (``cuda/fastermoe/smart_schedule.cpp:41-63``)."""
+    if not flat.is_cuda or not config.fused_enabled() or flat.dtype not in _AR_DTYPES:
+        return None
+    if comm is None:
+        comm = dist.group.WORLD
+    nbytes = flat.numel() * flat.element_size()
+    if dist.get_backend(comm) != "nccl" or nbytes == 0 or nbytes > _AR_MAX_BYTES:
+        return None
+    ws = get_workspace(comm, flat.device)
+    if ws is None:
+        return None
+    n = flat.numel()
+    buf, ptrs = ws.buffer("allreduce", _ar_buffer_bytes(nbytes))
+    buf[:nbytes].view(flat.dtype).copy_(flat.reshape(-1))
+    out = torch.zeros(n, dtype=flat.dtype, device=flat.device)
+    ws.ctx.reduce_to_root(ptrs, out, n, int(owner))
+    return out
+
+
 def allgather_rows(inp, comm, out=None):
     r"""``out = cat([inp of rank 0, inp of rank 1, ...])`` with peer-to-peer stores, or ``None``
     when that path is not available (caller uses the collective library).

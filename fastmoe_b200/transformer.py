@@ -122,11 +122,15 @@ class FMoETransformerMLP(FMoE):
         if not torch.is_tensor(moe_inp) or not moe_inp.is_cuda:
             return None
         from . import config
-        if config.faster_schedule_enabled() and config.faster_shadow_enabled():
-            return None  # shadow experts are served by the smart schedule
         from .ops import fused
         if not fused.supports(self, moe_inp, gate_top_k_idx):
             return None
+        if (config.faster_schedule_enabled() and config.faster_shadow_enabled()
+                and self.world_size > 1):
+            # shadow experts stay on the fused path: masked out of the exchange, computed
+            # locally with broadcast parameters
+            from .fastermoe import fused_shadow
+            return fused_shadow.moe_mlp_forward(self, moe_inp, gate_top_k_idx, gate_score)
         return fused.moe_mlp_forward(self, moe_inp, gate_top_k_idx, gate_score)
 
     def forward(self, inp: torch.Tensor):

@@ -481,6 +481,47 @@ def case_smart_schedule():
                 assert float((a - b).abs().max()) <= 0.05 * float(a.abs().max()) + 1e-3
 
 
+def case_shadow_fused():
+    r"""Shadow experts on the fused path: masked out of the exchange, parameters pushed by their
+    owners, computed locally, gradients reduced to the owners — against the plain fused path."""
+    from fastmoe_b200.fastermoe import fused_shadow
+    from fastmoe_b200.ops import fused
+    rank, world = dist.get_rank(), dist.get_world_size()
+    n_exp = 2
+    layer = _make_layer(world, rank, num_expert=n_exp, d=256, h=512, top_k=2)
+    torch.manual_seed(6000 + rank)
+    x = torch.randn(600 + 16 * rank, 256, device=_dev(), dtype=torch.bfloat16)
+    gy = torch.randn_like(x)
+    stored = torch.zeros(world * n_exp, dtype=torch.bool)
+    stored[1] = True                      # expert 1 of rank 0
+    stored[(world - 1) * n_exp] = True    # expert 0 of the last rank
+    symm.reserve_tokens(dist.group.WORLD, 600 + 16 * world, _dev())
+
+    def run(fn):
+        layer.zero_grad()
+        xx = x.detach().clone().requires_grad_(True)
+        idx, score = layer.gate(xx)
+        y = fn(layer, xx, idx, score)
+        y.backward(gy)
+        return (y.detach().float(), xx.grad.float().clone(),
+                {n: p.grad.float().clone() for n, p in layer.named_parameters()})
+
+    y0, gx0, g0 = run(fused.moe_mlp_forward)
+    y1, gx1, g1 = run(lambda l, a, i, sc: fused_shadow.moe_mlp_forward(l, a, i, sc, stored=stored))
+    assert torch.allclose(y0, y1, atol=3e-2, rtol=3e-2), float((y0 - y1).abs().max())
+    assert torch.allclose(gx0, gx1, atol=3e-2, rtol=3e-2), float((gx0 - gx1).abs().max())
+    for name in g0:
+        err = float((g0[name] - g1[name]).abs().max())
+        assert err <= 0.04 * float(g0[name].abs().max()) + 2e-3, (name, err)
+    # the policy-driven entry (whatever it decides) must agree as well
+    os.environ["FMOE_FASTER_SCHEDULE_ENABLE"] = "1"
+    os.environ["FMOE_FASTER_SHADOW_ENABLE"] = "1"
+    y2, _gx2, _g2 = run(lambda l, a, i, sc: fused_shadow.moe_mlp_forward(l, a, i, sc))
+    del os.environ["FMOE_FASTER_SCHEDULE_ENABLE"], os.environ["FMOE_FASTER_SHADOW_ENABLE"]
+    assert torch.allclose(y0, y2, atol=3e-2, rtol=3e-2)
+    assert native.get().read_status(_dev().index) == 0
+
+
 def case_graph_step():
     r"""A whole expert-parallel training step replays from a CUDA graph."""
     from fastmoe_b200.utils.graph import GraphedStep

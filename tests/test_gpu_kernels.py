@@ -345,3 +345,41 @@ def test_gate_linear_topk_softmax(dtype, n_exp, k, d, bias):
     lr2 = torch.nn.functional.linear(xr2, wr.detach(), None if br is None else br.detach())
     torch.softmax(torch.gather(lr2, 1, idx), -1).backward(gp.float())
     assert close(x2.grad, xr2.grad)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n_exp,k,d,bias", [(16, 2, 1024, True), (64, 4, 512, True), (100, 8, 256, False),
+                                            (256, 2, 1024, True)])
+def test_gate_tensor_core_many_experts(dtype, n_exp, k, d, bias):
+    r"""The linear gate above 8 experts: logits on the tcgen05 kernel (one group, expert
+    dimension padded), top-k / softmax kernel, against fp32 ``linear`` -> ``topk`` -> ``softmax``,
+    forward and backward through probabilities and logits."""
+    from fastmoe_b200.ops import gating
+    torch.manual_seed(12)
+    n = 1531
+    x = torch.randn(n, d, device=DEV, dtype=dtype).requires_grad_(True)
+    w = (torch.randn(n_exp, d, device=DEV) / d ** 0.5).to(dtype).requires_grad_(True)
+    b = (torch.randn(n_exp, device=DEV) * 0.1).to(dtype).requires_grad_(True) if bias else None
+    assert gating._gate_gemm_ok(x, w, b)
+    logits, idx, prob = gating.linear_topk_softmax(x, w, b, k)
+    assert logits.shape == (n, n_exp) and idx.shape == (n, k) and int(idx.max()) < n_exp
+
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    br = b.detach().float().requires_grad_(True) if bias else None
+    lr = torch.nn.functional.linear(xr, wr, br)
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    assert torch.allclose(logits.float(), lr, atol=tol, rtol=tol)
+    rv, _ = torch.topk(logits.detach().float(), k, dim=-1)
+    assert torch.equal(torch.gather(logits.detach().float(), 1, idx), rv)
+    rp = torch.softmax(torch.gather(lr, 1, idx), -1)
+    assert torch.allclose(prob.float(), rp, atol=tol)
+
+    gp = torch.randn_like(prob)
+    gl = torch.randn(n, n_exp, device=DEV, dtype=dtype) * 0.1
+    torch.autograd.backward([prob, logits], [gp, gl])
+    torch.autograd.backward([rp, lr], [gp.float(), gl.float()])
+    for got, ref in ((x.grad, xr.grad), (w.grad, wr.grad)) + (((b.grad, br.grad),) if bias else ()):
+        scale = ref.abs().max().item() + 1e-6
+        assert (got.float() - ref).abs().max().item() <= 3e-2 * scale
+    assert _native().read_status(0) == 0
