@@ -293,6 +293,113 @@ def case_smart_schedule():
                     assert torch.allclose(a, b, atol=1e-4), (group_size, shadow, (a - b).abs().max())
 
 
+class _CallbackMoEForward(torch.autograd.Function):
+    r"""The calling sequence of the reference's ``MoEForward`` (fmoe/fastermoe/schedule.py:15-114)
+    around ``fmoe_cuda.smart_sch_forward`` / ``smart_sch_backward`` / ``reduce_grad``."""
+
+    @staticmethod
+    def forward(ctx, expert_fn, experts, inp, pos_s, pos_g, lec, gec, stored, fwd_batch, out_batch,
+                num_expert, world):
+        import fmoe_cuda
+        from fastmoe_b200.fastermoe import expert_utils
+        from fastmoe_b200.functions import _local_gather, _local_scatter
+        local_in = _local_scatter(inp, pos_s)
+        ctx.gibs, ctx.gobs = {}, {}
+
+        def run(x, y, expert_idx, store_idx):
+            x = x.detach().requires_grad_(True)
+            keep = lambda t: t  # noqa: E731
+            # parameters are overwritten in place when a shadow is stashed and restored: the
+            # identity hooks keep autograd's version check out of the way, as in the reference
+            with torch.enable_grad(), torch.autograd.graph.saved_tensors_hooks(keep, keep):
+                y0 = expert_fn(x, torch.tensor([x.shape[0]], dtype=torch.int64), expert_idx)
+            ctx.gibs[store_idx], ctx.gobs[store_idx] = x, y0
+            y.copy_(y0.detach())
+
+        ctx.experts = experts
+        ctx.expert_size = expert_utils.get_expert_param_size(experts, 0)
+        ctx.shadows = {}
+
+        def stash(params, store_idx, expert_idx):
+            expert_utils.stash_expert_params(experts, params, expert_idx)
+            ctx.shadows[store_idx] = params
+
+        out_buf, gib = fmoe_cuda.smart_sch_forward(
+            local_in, lec, gec, stored, fwd_batch, ctx.expert_size, world, run,
+            lambda out, idx: expert_utils.get_expert_params(experts, out, idx), stash,
+            lambda idx: expert_utils.pop_expert_params(experts, idx))
+        ctx.args = fwd_batch, inp.shape[0], num_expert, world
+        ctx.save_for_backward(pos_s, pos_g, lec, gec, stored, gib, local_in)
+        return _local_gather(out_buf, pos_g, out_batch, maybe_overlap=False)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        import fmoe_cuda
+        from fastmoe_b200.fastermoe import expert_utils
+        from fastmoe_b200.functions import _local_gather, _local_scatter
+        pos_s, pos_g, lec, gec, stored, _gib, _lin = ctx.saved_tensors
+        fwd_batch, inp_batch, _num_expert, world = ctx.args
+        experts = ctx.experts
+
+        def back(grad_y, grad_x, expert_idx, store_idx):
+            y, x = ctx.gobs[store_idx], ctx.gibs[store_idx]
+            torch.autograd.backward([y], [grad_y])
+            grad_x.copy_(x.grad if x.grad is not None else torch.zeros_like(x))
+
+        def collect(store_idx, root, expert_idx):
+            grad = ctx.shadows[store_idx]
+            expert_utils.collect_expert_grads(experts, grad, expert_idx)
+            fmoe_cuda.reduce_grad(grad, root, ctx.expert_size)
+
+        grad_buf = _local_scatter(grad_out.contiguous(), pos_g)
+        grad_in_buf = fmoe_cuda.smart_sch_backward(
+            grad_buf, lec, gec, stored, pos_s.shape[0], fwd_batch, world, back,
+            lambda store_idx, idx: expert_utils.stash_expert_params(experts, ctx.shadows[store_idx], idx),
+            lambda idx: expert_utils.pop_expert_params(experts, idx), collect,
+            lambda store_idx, idx: expert_utils.set_grads(experts, ctx.shadows[store_idx], idx))
+        grad_in = _local_gather(grad_in_buf, pos_s, inp_batch)
+        return (None, None, grad_in) + (None,) * 9
+
+
+def case_smart_sch_entry_points():
+    r"""``fmoe_cuda.smart_sch_forward`` / ``smart_sch_backward`` / ``reduce_grad`` driven with the
+    reference's callbacks (per-expert modules, parameters stashed into expert 0 for shadows)
+    == the general path."""
+    from fastmoe_b200 import FMoE
+    from fastmoe_b200.functions import ensure_comm, prepare_forward
+    from fastmoe_b200.layers import _fmoe_general_global_forward as naive_forward
+    from oracle import LinearExpert
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ensure_comm(torch.zeros(1), None)
+    for group_size in (1, 2):
+        for shadow in (False, True):
+            os.environ["FMOE_FASTER_GROUP_SIZE"] = str(group_size)
+            torch.manual_seed(31 + rank)
+            layer = FMoE(num_expert=2, d_model=8, world_size=world, top_k=2, expert=LinearExpert)
+            x = torch.randn(11 + rank, 8)
+            idx = torch.randint(0, 2 * world, (x.shape[0], 2))
+            torch.manual_seed(78)
+            stored = torch.rand(2 * world) < 0.4 if shadow else torch.zeros(2 * world, dtype=torch.bool)
+
+            xa = x.clone().requires_grad_(True)
+            ya = naive_forward(xa, idx, layer.expert_fn, 2, world)
+            ya.pow(2).sum().backward()
+            ga = [p.grad.clone() for p in layer.experts.parameters()]
+            layer.zero_grad()
+
+            xb = x.clone().requires_grad_(True)
+            pos, lec, gec, _fec, fwd_batch = prepare_forward(idx, 2, world)
+            yb = _CallbackMoEForward.apply(
+                layer.expert_fn_single, layer.experts, xb, torch.div(pos, 2, rounding_mode="floor"), pos,
+                lec, gec, stored, fwd_batch, x.shape[0] * 2, 2, world)
+            yb.pow(2).sum().backward()
+            gb = [torch.zeros_like(p) if p.grad is None else p.grad.clone() for p in layer.experts.parameters()]
+            assert torch.allclose(ya, yb, atol=1e-5), (group_size, shadow, float((ya - yb).abs().max()))
+            assert torch.allclose(xa.grad, xb.grad, atol=1e-5)
+            for a, b in zip(ga, gb):
+                assert torch.allclose(a, b, atol=1e-4), (group_size, shadow, float((a - b).abs().max()))
+
+
 def case_shadow_policy():
     r"""The policy shadows the overloaded expert and nothing when the load is flat."""
     from fastmoe_b200.fastermoe.shadow_policy import shadow_plan

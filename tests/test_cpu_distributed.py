@@ -7,7 +7,7 @@ from dist_launch import run_ranks
 
 @pytest.mark.parametrize("case", ["ep_matches_bruteforce", "capacity_gates", "swipe_gate",
                                   "grouped_ddp", "slice_group", "smart_schedule",
-                                  "shadow_policy"])
+                                  "smart_sch_entry_points", "shadow_policy"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_cpu_ranks(case, world):
     codes = run_ranks("dist_cpu_worker.py", case, world, timeout=240)
