@@ -41,13 +41,37 @@ CONFIGS = {
     "skewed": dict(tokens=8192, d_model=2048, d_hidden=8192, experts=8, top_k=2, gate="GShardGate",
                    zipf=1.2, label="FMoETransformerMLP (GShardGate top-2, capacity 1.2, Zipf(1.2) gate bias, GELU)"),
 }
+# Whole language models (pure torch.nn around the MoE layer class of the arm being measured, so
+# that both arms run the same dense code and differ only in the MoE implementation).
+CONFIGS.update({
+    "txl": dict(kind="lm", layers=12, d_model=512, heads=8, d_hidden=2048, experts=8, top_k=2,
+                gate="NaiveGate", vocab=256, seq=512, mem=512, batch=22, zipf=0.0, shadow=False,
+                label="Transformer-XL-style MoE LM (12 layers, d 512, 8 heads, every FFN an "
+                      "FMoETransformerMLP with 8 experts/GPU, top-2 NaiveGate, seq 512 + mem 512)"),
+    "gpt": dict(kind="lm", layers=24, d_model=1024, heads=16, d_hidden=4096, experts=2, top_k=1,
+                gate="SwitchGate", vocab=50257, seq=1024, mem=0, batch=8, zipf=1.2, shadow=False,
+                label="GPT with every FFN an FMoETransformerMLP (24 layers, h 1024, 16 heads, FFN 4096, "
+                      "2 experts/GPU, SwitchGate top-1, Zipf(1.2) gate bias)"),
+})
+CONFIGS["gpt_shadow"] = dict(CONFIGS["gpt"], shadow=True,
+                             label=CONFIGS["gpt"]["label"] + ", FasterMoE smart schedule + shadow experts on")
+for _name in ("ep_mlp", "skewed"):
+    CONFIGS[_name]["kind"] = "layer"
 TOKENS_PER_GPU = D_MODEL = D_HIDDEN = EXPERTS_PER_GPU = TOP_K = None
+CFG = None
 GATE_NAME = ZIPF = MODEL_LABEL = None
 
 
 def select_config(name):
-    global TOKENS_PER_GPU, D_MODEL, D_HIDDEN, EXPERTS_PER_GPU, TOP_K, GATE_NAME, ZIPF, MODEL_LABEL
+    global TOKENS_PER_GPU, D_MODEL, D_HIDDEN, EXPERTS_PER_GPU, TOP_K, GATE_NAME, ZIPF, MODEL_LABEL, CFG
     c = CONFIGS[name]
+    CFG = c
+    if c["kind"] == "lm":
+        c["tokens"] = c["batch"] * c["seq"]
+        if c["shadow"]:
+            # read by both implementations (the reference decides at import time)
+            os.environ["FMOE_FASTER_SCHEDULE_ENABLE"] = "1"
+            os.environ["FMOE_FASTER_SHADOW_ENABLE"] = "1"
     TOKENS_PER_GPU, D_MODEL, D_HIDDEN = c["tokens"], c["d_model"], c["d_hidden"]
     EXPERTS_PER_GPU, TOP_K, GATE_NAME, ZIPF, MODEL_LABEL = c["experts"], c["top_k"], c["gate"], c["zipf"], c["label"]
 
@@ -138,6 +162,89 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+# ------------------------------------------------------------------------------ LM around the MoE layer
+def make_lm(moe_cls, gate_cls, world, cfg):
+    r"""A decoder-only LM in plain torch.nn; ``moe_cls`` / ``gate_cls`` come from the implementation
+    under test.  With ``mem > 0`` every layer attends over [previous segment's hidden states;
+    current segment] (Transformer-XL recurrence; learned absolute positions instead of the
+    relative encoding, the same in both arms)."""
+    import torch
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            d = cfg["d_model"]
+            self.ln1, self.ln2 = nn.LayerNorm(d), nn.LayerNorm(d)
+            self.qkv, self.proj = nn.Linear(d, 3 * d), nn.Linear(d, d)
+            self.moe = moe_cls(num_expert=cfg["experts"], d_model=d, d_hidden=cfg["d_hidden"],
+                               world_size=world, top_k=cfg["top_k"], gate=gate_cls,
+                               activation=nn.GELU())
+
+        def forward(self, x, mem):
+            b, s, d = x.shape
+            h = self.ln1(x)
+            ctx = h if mem is None else torch.cat([mem, h], 1)
+            q = self.qkv(h)[..., :d]
+            kv = self.qkv(ctx)[..., d:]
+            nh = cfg["heads"]
+            q = q.view(b, s, nh, d // nh).transpose(1, 2)
+            k, v = kv.view(b, ctx.shape[1], 2, nh, d // nh).permute(2, 0, 3, 1, 4)
+            if mem is None:
+                att = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            else:
+                m = ctx.shape[1] - s
+                mask = torch.ones(s, ctx.shape[1], dtype=torch.bool, device=x.device).tril(m)
+                att = F.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+            x = x + self.proj(att.transpose(1, 2).reshape(b, s, d))
+            return x + self.moe(self.ln2(x)), h.detach()
+
+    class LM(nn.Module):
+        def __init__(self):
+            super().__init__()
+            d = cfg["d_model"]
+            self.emb = nn.Embedding(cfg["vocab"], d)
+            self.pos = nn.Embedding(cfg["seq"], d)
+            self.blocks = nn.ModuleList([Block() for _ in range(cfg["layers"])])
+            self.ln = nn.LayerNorm(d)
+            self.head = nn.Linear(d, cfg["vocab"], bias=False)
+            self.mems = None
+
+        def forward(self, tokens):
+            b, s = tokens.shape
+            x = self.emb(tokens) + self.pos(torch.arange(s, device=tokens.device))
+            new_mems = []
+            for i, blk in enumerate(self.blocks):
+                mem = self.mems[i] if (cfg["mem"] > 0 and self.mems is not None) else None
+                x, h = blk(x, mem)
+                new_mems.append(h[:, -cfg["mem"]:] if cfg["mem"] > 0 else None)
+            if cfg["mem"] > 0:
+                self.mems = new_mems
+            logits = self.head(self.ln(x))
+            loss = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), tokens.view(-1))
+            for blk in self.blocks:
+                if getattr(blk.moe.gate, "has_loss", False):
+                    loss = loss + blk.moe.gate.get_loss().sum().float()
+            return loss
+
+    return LM()
+
+
+def finish_lm(model, world, cfg, device, ddp_cls):
+    import torch
+    if cfg["zipf"] > 0:
+        tot = cfg["experts"] * world
+        bias = -cfg["zipf"] * torch.log(torch.arange(1, tot + 1, dtype=torch.float32))
+        with torch.no_grad():
+            for blk in model.blocks:
+                blk.moe.gate.gate.weight.mul_(0.1)
+                blk.moe.gate.gate.bias.copy_(bias)
+    model = model.to(device).to(torch.bfloat16)
+    wrapped = ddp_cls(model) if world > 1 else model
+    return model, wrapped
+
+
 # ------------------------------------------------------------------------------ the two arms
 def build_ours(rank, world, device):
     import torch
@@ -147,6 +254,10 @@ def build_ours(rank, world, device):
     from fastmoe_b200.ops import native
     native.get()  # fail loudly if the extension is missing
     torch.manual_seed(1234 + rank)
+    if CFG["kind"] == "lm":
+        lm = make_lm(FMoETransformerMLP, getattr(gates, GATE_NAME), world, CFG)
+        lm, model = finish_lm(lm, world, CFG, device, DistributedGroupedDataParallel)
+        return lm, model, (lambda: native.get().launch_count())
     layer = FMoETransformerMLP(num_expert=EXPERTS_PER_GPU, d_model=D_MODEL, d_hidden=D_HIDDEN,
                                world_size=world, top_k=TOP_K, gate=getattr(gates, GATE_NAME),
                                activation=torch.nn.GELU())
@@ -171,6 +282,10 @@ def build_reference(rank, world, device):
     from fmoe import gates
     assert os.path.realpath(sys.modules["fmoe"].__file__).startswith(os.path.realpath(ref_dir))
     torch.manual_seed(1234 + rank)
+    if CFG["kind"] == "lm":
+        lm = make_lm(FMoETransformerMLP, getattr(gates, GATE_NAME), world, CFG)
+        lm, model = finish_lm(lm, world, CFG, device, DistributedGroupedDataParallel)
+        return lm, model, (lambda: 0)
     layer = FMoETransformerMLP(num_expert=EXPERTS_PER_GPU, d_model=D_MODEL, d_hidden=D_HIDDEN,
                                world_size=world, top_k=TOP_K, gate=getattr(gates, GATE_NAME),
                                activation=torch.nn.GELU())
@@ -214,8 +329,14 @@ def main():
             return
         raise
 
-    graphed = args.impl == "ours" and os.environ.get("FMOE_BENCH_GRAPH", "1") == "1"
-    overlap = args.impl == "ours" and world > 1 and os.environ.get("FMOE_BENCH_OVERLAP", "1") == "1"
+    is_lm = CFG["kind"] == "lm"
+    # The layer configs replay the step from a CUDA graph (the fused path never reads a count on
+    # the host); whole models run eagerly: their gates (capacity limits, shadow policy) and the
+    # recurrence memory are not capture-safe in general.
+    graphed = (args.impl == "ours" and not is_lm
+               and os.environ.get("FMOE_BENCH_GRAPH", "1") == "1")
+    overlap = (args.impl == "ours" and world > 1 and not is_lm
+               and os.environ.get("FMOE_BENCH_OVERLAP", "1") == "1")
     if overlap:
         # Same Adam over the same parameters, as two optimizer objects: the expert parameters
         # need no gradient reduction, so their update runs while the gate gradients are being
@@ -230,8 +351,12 @@ def main():
         opt = torch.optim.Adam(layer.parameters(), lr=1e-4, fused=True, capturable=graphed)
     n_inputs = 4
     gen = torch.Generator(device="cpu").manual_seed(99 + rank)
-    host_inputs = [torch.randn(TOKENS_PER_GPU, D_MODEL, generator=gen).to(torch.bfloat16).pin_memory()
-                   for _ in range(n_inputs)]
+    if is_lm:
+        host_inputs = [torch.randint(0, CFG["vocab"], (CFG["batch"], CFG["seq"]), generator=gen).pin_memory()
+                       for _ in range(n_inputs)]
+    else:
+        host_inputs = [torch.randn(TOKENS_PER_GPU, D_MODEL, generator=gen).to(torch.bfloat16).pin_memory()
+                       for _ in range(n_inputs)]
     dev_inputs = [h.to(device) for h in host_inputs]
     flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=device)
 
@@ -239,11 +364,14 @@ def main():
         opt.zero_grad(set_to_none=True)
         if opt_local is not None:
             opt_local.zero_grad(set_to_none=True)
-        x = x.detach().requires_grad_(True)
-        y = model(x)
-        loss = y.sum()
-        if layer.gate.has_loss:
-            loss = loss + layer.gate.get_loss().sum().to(loss.dtype)
+        if is_lm:
+            loss = model(x)
+        else:
+            x = x.detach().requires_grad_(True)
+            y = model(x)
+            loss = y.sum()
+            if layer.gate.has_loss:
+                loss = loss + layer.gate.get_loss().sum().to(loss.dtype)
         loss.backward()
         if opt_local is not None:
             pending = model.allreduce_params(async_op=True)
@@ -421,7 +549,7 @@ def main():
 
     clocks = sampler.stop() if rank == 0 else None
 
-    kept = kept_slot_fraction(layer, dev_inputs[0])
+    kept = 1.0 if is_lm else kept_slot_fraction(layer, dev_inputs[0])
     times = torch.tensor([dev_ms, e2e_ms, eager_ms or 0.0, max(step_ms), -min(step_ms)],
                          dtype=torch.float64, device=device)
     sums = torch.tensor([kept], dtype=torch.float64, device=device)
@@ -438,22 +566,30 @@ def main():
         e2e_value = tokens / (e2e_ms / 1e3)
         # Slots a capacity limit dropped do no work in the expert GEMMs: count the kept ones.
         flops_per_step = 3 * 2 * 2 * TOKENS_PER_GPU * TOP_K * kept * D_MODEL * D_HIDDEN * world
+        if is_lm:
+            # model FLOPs of fwd + bwd: attention projections and scores, top-k expert MLPs, LM head
+            d, kv = D_MODEL, CFG["seq"] + CFG["mem"]
+            per_token = CFG["layers"] * (8 * d * d + 4 * kv * d + TOP_K * 4 * d * D_HIDDEN) + 2 * d * CFG["vocab"]
+            flops_per_step = 3 * per_token * TOKENS_PER_GPU * world
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": warm_steps,
             "ms_per_step": dev_ms / args.steps, "ms_per_step_min": step_min,
             "ms_per_step_median": statistics.median(step_ms), "ms_per_step_max": step_max,
             "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1) inputs, random-init weights",
+            "vs_baseline": None, "dtype": "bf16",
+            "data": ("synthetic tokens, uniform over the vocabulary, random-init weights" if is_lm
+                     else "synthetic N(0,1) inputs, random-init weights"),
             "impl": args.impl,
             "tflops": flops_per_step / (dev_ms / args.steps / 1e3) / 1e12,
             "config": {
                 "name": args.config, "model": MODEL_LABEL,
                 "tokens_per_gpu": TOKENS_PER_GPU, "global_batch": TOKENS_PER_GPU * world,
-                "seq_len": 1, "d_model": D_MODEL, "d_hidden": D_HIDDEN,
+                "seq_len": CFG["seq"] if is_lm else 1, "d_model": D_MODEL, "d_hidden": D_HIDDEN,
                 "experts_per_gpu": EXPERTS_PER_GPU, "top_k": TOP_K,
                 "parallelism": "ep%d" % world,
-                "step": "fwd+bwd+gate-grad-allreduce+fused-adam",
+                "step": ("fwd+bwd+grad-allreduce+fused-adam" if is_lm
+                         else "fwd+bwd+gate-grad-allreduce+fused-adam"),
                 "l2": "flushed between timed steps (256 MiB fill outside the per-step events; "
                       "in the end-to-end region a 160 MiB fill per step inside the region)",
             },
@@ -469,7 +605,7 @@ def main():
             },
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s",
-                    "h2d_bytes_per_step": TOKENS_PER_GPU * D_MODEL * 2,
+                    "h2d_bytes_per_step": host_inputs[0].numel() * host_inputs[0].element_size(),
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps,
                     "last_loss": loss_host},
             "gpu_launches": int(launches),
