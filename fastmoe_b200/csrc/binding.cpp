@@ -166,6 +166,32 @@ torch::Tensor prune_gate_by_capacity(torch::Tensor idx, torch::Tensor cap, int64
   return out;
 }
 
+// SWIPE on the device: balanced ids of one choice column from the quota the exchange kernel
+// computed.  No count reaches the host.
+torch::Tensor swipe_reassign(torch::Tensor idx, torch::Tensor quota, int64_t n_expert, int64_t bias) {
+  check_cuda_contig(idx, "idx");
+  check_cuda_contig(quota, "quota");
+  TORCH_CHECK(idx.scalar_type() == torch::kLong && quota.scalar_type() == torch::kInt,
+              "swipe_reassign: int64 ids, int32 quota");
+  c10::cuda::CUDAGuard guard(idx.device());
+  const int n = static_cast<int>(idx.numel());
+  const int n_worker = static_cast<int>(quota.numel());
+  auto worker = torch::div(idx, n_expert, "floor");
+  auto r1 = route(worker.contiguous(), n_worker, false);          // counts per worker, slot ranks
+  auto key = torch::empty_like(idx);
+  FMOE_CUDA_CHECK(fmoe::launch_swipe_mark(idx.data_ptr<int64_t>(), r1[1].data_ptr<int>(),
+                                          quota.data_ptr<int>(), n, static_cast<int>(n_expert),
+                                          n_worker, key.data_ptr<int64_t>(), cur_stream()));
+  auto r2 = route(key, 1, false);                                  // ordinal among the moved tokens
+  auto out = torch::empty_like(idx);
+  FMOE_CUDA_CHECK(fmoe::launch_swipe_assign(idx.data_ptr<int64_t>(), key.data_ptr<int64_t>(),
+                                            r2[1].data_ptr<int>(), r1[0].data_ptr<int>(),
+                                            quota.data_ptr<int>(), n, static_cast<int>(n_expert),
+                                            n_worker, static_cast<int>(bias),
+                                            out.data_ptr<int64_t>(), cur_stream()));
+  return out;
+}
+
 // ------------------------------------------------------------------------------ grouped GEMM
 // Generic entry: see sm100/grouped_gemm.cuh for the meaning of mode / act / epi.
 void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor offs,
@@ -470,6 +496,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   // counts, rank, offs and pos (slot ids sorted by expert then rank: the send order of the
   // fused dispatch)
   m.def("route_pos", [](torch::Tensor idx, int64_t tot) { return route(idx, tot, true, true); });
+  m.def("swipe_reassign", &swipe_reassign);
   m.def("grouped_gemm", &grouped_gemm, py::arg("mode"), py::arg("a"), py::arg("b"), py::arg("offs"),
         py::arg("out"), py::arg("bias") = py::none(), py::arg("pre_out") = py::none(),
         py::arg("aux") = py::none(), py::arg("act") = 0, py::arg("epi") = 0,

@@ -291,6 +291,66 @@ capacity_grant_kernel(const __grid_constant__ ExchangeCtx c, const int* __restri
 }
 
 
+// One SWIPE round's exchange and plan (cuda/balancing.cu:83-186 in the reference: two count
+// exchanges, an all-reduce and an all-gather with a host sync after each).  Every rank writes
+// [tokens it wants to send to each worker | capacity it has left] into every peer's table;
+// with the full table each rank computes the same plan: workers accept requests in rank order
+// until full, the overflow is handed to workers with room in rank order.  Outputs for this
+// rank: quota[j] = tokens it may send to worker j, cap_left = its own remaining capacity.
+// Two tables alternate with the epoch, as for the capacity grants.
+__global__ void __launch_bounds__(256, 1)
+swipe_exchange_kernel(const __grid_constant__ ExchangeCtx c, const int* __restrict__ want,
+                      const int64_t* __restrict__ cap, const __grid_constant__ PeerPtrs tab,
+                      int* __restrict__ quota, int64_t* __restrict__ cap_left) {
+  __shared__ long sh[kMaxPeers * (kMaxPeers + 1)];
+  __shared__ long left[kMaxPeers];
+  __shared__ long dropped[kMaxPeers];
+  const int W = c.world;
+  const int width = W + 1;
+  const int epoch = c.epoch[0];
+  const long half = static_cast<long>(epoch & 1) * W * width;
+  if (static_cast<int>(threadIdx.x) < width) {
+    const long v = static_cast<int>(threadIdx.x) < W ? want[threadIdx.x] : cap[0];
+    for (int p = 0; p < W; ++p) {
+      static_cast<long*>(tab.p[p])[half + c.me * width + threadIdx.x] = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < W) {
+    st_release_sys(flag_of(c.flags.p[threadIdx.x], kChanCounts, c.me), epoch);
+  }
+  block_wait_all(c, kChanCounts, epoch);
+  const volatile long* mine = static_cast<const volatile long*>(tab.p[c.me]) + half;
+  for (int i = threadIdx.x; i < W * width; i += blockDim.x) sh[i] = mine[i];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int j = 0; j < W; ++j) left[j] = sh[j * width + W];
+    for (int i = 0; i < W; ++i) dropped[i] = 0;
+    for (int j = 0; j < W; ++j) {
+      for (int i = 0; i < W; ++i) {
+        const long w = sh[i * width + j];
+        const long take = w < left[j] ? w : left[j];
+        sh[i * width + j] = take;          // the table now holds the accepted counts
+        left[j] -= take;
+        dropped[i] += w - take;
+      }
+    }
+    int j = 0;
+    for (int i = 0; i < W; ++i) {
+      while (dropped[i] > 0 && j < W) {
+        const long take = dropped[i] < left[j] ? dropped[i] : left[j];
+        sh[i * width + j] += take;
+        left[j] -= take;
+        dropped[i] -= take;
+        if (left[j] == 0) ++j;
+      }
+    }
+    for (int q = 0; q < W; ++q) quota[q] = static_cast<int>(sh[c.me * width + q]);
+    cap_left[0] = left[c.me];
+  }
+}
+
 // ------------------------------------------------------------------------------ dispatch
 // One warp per slot, persistent grid.  Stores go to the owner's staging buffer over NVLink.
 template <typename T>
@@ -725,6 +785,13 @@ cudaError_t launch_capacity_grant(const ExchangeCtx& ctx, const int* lec, const 
     if (e != cudaSuccess) return e;
   }
   capacity_grant_kernel<<<1, 1024, smem, stream>>>(ctx, lec, cap, cnt, n_expert, new_lec, new_gec);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swipe_exchange(const ExchangeCtx& ctx, const int* want, const int64_t* cap,
+                                  const PeerPtrs& tab, int* quota, int64_t* cap_left,
+                                  cudaStream_t stream) {
+  swipe_exchange_kernel<<<1, 256, 0, stream>>>(ctx, want, cap, tab, quota, cap_left);
   return cudaGetLastError();
 }
 

@@ -139,6 +139,14 @@ cudaError_t launch_capacity_grant(const ExchangeCtx& ctx, const int* lec, const 
                                   const PeerPtrs& cnt, int n_expert, int64_t* new_lec,
                                   int64_t* new_gec, cudaStream_t stream);
 
+// Exchange and plan of one SWIPE round.  want: int32 [world] tokens this rank routes to every
+// worker; cap: int64 [1] capacity this rank has left; tab: symmetric int64 buffers of
+// 2 * world * (world + 1) entries.  quota: int32 [world] tokens this rank may send to every
+// worker after balancing; cap_left: int64 [1].  Call launch_begin_epoch right before.
+cudaError_t launch_swipe_exchange(const ExchangeCtx& ctx, const int* want, const int64_t* cap,
+                                  const PeerPtrs& tab, int* quota, int64_t* cap_left,
+                                  cudaStream_t stream);
+
 // Waits (bounded) for all peers' current-epoch flags on `channel` without touching any data.
 cudaError_t launch_wait_arrival(const ExchangeCtx& ctx, int channel, cudaStream_t stream);
 

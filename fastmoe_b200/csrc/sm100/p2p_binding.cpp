@@ -89,6 +89,22 @@ class ExchangeContext {
     return {new_lec, new_gec};
   }
 
+  std::vector<torch::Tensor> swipe_exchange(torch::Tensor want, torch::Tensor cap,
+                                            std::vector<int64_t> tab_ptrs) {
+    TORCH_CHECK(want.scalar_type() == torch::kInt && want.numel() == ctx_.world && want.is_cuda(),
+                "swipe_exchange: int32 [world] request counts on the GPU");
+    TORCH_CHECK(cap.scalar_type() == torch::kLong && cap.numel() == 1 && cap.is_cuda(),
+                "swipe_exchange: int64 [1] capacity on the GPU");
+    c10::cuda::CUDAGuard guard(want.device());
+    auto quota = torch::empty({ctx_.world}, torch::dtype(torch::kInt).device(want.device()));
+    auto left = torch::empty({1}, torch::dtype(torch::kLong).device(want.device()));
+    FMOE_P2P_CHECK(fmoe::launch_begin_epoch(ctx_, stream()));
+    FMOE_P2P_CHECK(fmoe::launch_swipe_exchange(ctx_, want.data_ptr<int>(), cap.data_ptr<int64_t>(),
+                                               to_ptrs(tab_ptrs), quota.data_ptr<int>(),
+                                               left.data_ptr<int64_t>(), stream()));
+    return {quota, left};
+  }
+
   void begin_epoch() {
     c10::cuda::CUDAGuard guard(epoch_.device());
     FMOE_P2P_CHECK(fmoe::launch_begin_epoch(ctx_, stream()));
@@ -350,6 +366,7 @@ void bind_p2p(pybind11::module& m) {
       .def("count_exchange", &ExchangeContext::count_exchange)
       .def("capacity_grant", &ExchangeContext::capacity_grant)
       .def("begin_epoch", &ExchangeContext::begin_epoch)
+      .def("swipe_exchange", &ExchangeContext::swipe_exchange)
       .def("dispatch_push", &ExchangeContext::dispatch_push)
       .def("wait_copy", &ExchangeContext::wait_copy)
       .def("wait_arrival", &ExchangeContext::wait_arrival)

@@ -142,6 +142,44 @@ __global__ void fill_pos_kernel(const int64_t* __restrict__ idx, const int* __re
   pos[base + rank[s]] = s;
 }
 
+// SWIPE reassignment, two passes around a ranking of the moved tokens.  A token keeps its
+// expert while its worker's quota lasts (slot order); `swipe_mark` writes key 0 for the others
+// (and -1 for the kept ones), the routing kernel ranks them, and `swipe_assign` sends the i-th
+// moved token to expert `bias` of the worker that owns the i-th unit of spare quota.
+__global__ void swipe_mark_kernel(const int64_t* __restrict__ idx, const int* __restrict__ rank,
+                                  const int* __restrict__ quota, int n, int n_expert, int n_worker,
+                                  int64_t* __restrict__ key) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n) return;
+  const long e = idx[s];
+  const int w = static_cast<int>(e / n_expert);
+  const bool valid = e >= 0 && w < n_worker;
+  key[s] = (valid && rank[s] >= quota[w]) ? 0 : -1;
+}
+
+__global__ void swipe_assign_kernel(const int64_t* __restrict__ idx, const int64_t* __restrict__ key,
+                                    const int* __restrict__ mrank, const int* __restrict__ count,
+                                    const int* __restrict__ quota, int n, int n_expert, int n_worker,
+                                    int bias, int64_t* __restrict__ out) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n) return;
+  if (key[s] < 0) {
+    out[s] = idx[s];
+    return;
+  }
+  const int o = mrank[s];
+  int run = 0, target = -1;
+  for (int j = 0; j < n_worker; ++j) {
+    const int kept = count[j] < quota[j] ? count[j] : quota[j];
+    run += quota[j] - kept;
+    if (o < run) {
+      target = j;
+      break;
+    }
+  }
+  out[s] = target < 0 ? -1 : static_cast<int64_t>(target) * n_expert + bias;
+}
+
 // ------------------------------------------------------------------------------ row movement
 template <typename T> struct V2;
 template <> struct V2<__nv_bfloat16> {
@@ -788,6 +826,22 @@ cudaError_t launch_route(const int64_t* idx, int n_slots, int tot, int* counts, 
     if (e != cudaSuccess) return e;
   }
   route_kernel<<<1, kRouteThreads, smem, stream>>>(idx, n_slots, tot, nw, counts, rank, offs, pos);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swipe_mark(const int64_t* idx, const int* rank, const int* quota, int n,
+                              int n_expert, int n_worker, int64_t* key, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  swipe_mark_kernel<<<(n + 255) / 256, 256, 0, stream>>>(idx, rank, quota, n, n_expert, n_worker, key);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swipe_assign(const int64_t* idx, const int64_t* key, const int* mrank,
+                                const int* count, const int* quota, int n, int n_expert,
+                                int n_worker, int bias, int64_t* out, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  swipe_assign_kernel<<<(n + 255) / 256, 256, 0, stream>>>(idx, key, mrank, count, quota, n, n_expert,
+                                                          n_worker, bias, out);
   return cudaGetLastError();
 }
 

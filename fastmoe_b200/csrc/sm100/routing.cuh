@@ -16,6 +16,16 @@ cudaError_t launch_route(const int64_t* idx, int n_slots, int tot, int* counts, 
 cudaError_t launch_prune(const int64_t* idx, const int* rank, const int* cap, int n_slots, int tot,
                          int64_t* new_idx, cudaStream_t stream);
 
+// SWIPE reassignment of one choice column (idx: global expert ids; rank: slot rank of every
+// token inside its worker; count / quota: int32 [n_worker] tokens routed to / accepted by every
+// worker).  `mark` writes key 0 for tokens beyond their worker's quota and -1 otherwise; after
+// ranking the moved tokens (mrank), `assign` writes the balanced ids.
+cudaError_t launch_swipe_mark(const int64_t* idx, const int* rank, const int* quota, int n,
+                              int n_expert, int n_worker, int64_t* key, cudaStream_t stream);
+cudaError_t launch_swipe_assign(const int64_t* idx, const int64_t* key, const int* mrank,
+                                const int* count, const int* quota, int n, int n_expert,
+                                int n_worker, int bias, int64_t* out, cudaStream_t stream);
+
 // Rank-ordered capacity grant; ec/eca are [n_worker, n_expert] int64, cap[n_expert] int32 (in/out).
 cudaError_t launch_limit_by_capacity(const int64_t* ec, int* cap, int64_t* eca, int n_expert,
                                      int n_worker, cudaStream_t stream);

@@ -30,7 +30,7 @@ class SwipeGate(NaiveGate):
 
     def _balanced_choices(self, preferred):
         r"""``preferred [B, k]`` (descending preference) → balanced ids ``[B, k]``."""
-        left = torch.scalar_tensor(preferred.shape[0] * self.top_k, dtype=torch.long)
+        left = torch.full((1,), preferred.shape[0] * self.top_k, dtype=torch.long, device=preferred.device)
         columns = []
         for choice in range(self.top_k):
             ids, left = self.swipe_once(preferred[:, choice], left, choice % self.num_expert)

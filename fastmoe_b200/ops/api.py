@@ -103,12 +103,22 @@ def swipe_once(gate_idx, capacity, n_expert, n_worker, bias, group=None):
     r"""One SWIPE round (parity: ``cuda/balancing.cu:83-186``): returns ``(new_idx_cpu, capacity_left)``.
 
     The reference does two count exchanges, an all-reduce and an all-gather with a host
-    sync after each; here one all-gather of the ``n_worker`` request counts and of the
-    capacities gives every rank the whole picture and the plan is computed redundantly.
+    sync after each.  On B200s one kernel exchanges the request counts and capacities through
+    the symmetric heap and computes the plan on every rank, and two small kernels rewrite the
+    ids: no host read at all (``parallel/symm.py::swipe_round``).  Elsewhere (CPU tensors,
+    ``gloo``): one all-gather gives every rank the whole picture and the plan is computed
+    redundantly on the host.
     """
     import torch.distributed as dist
     group = group if group is not None else _comm.get_moe_group()
     idx = gate_idx.reshape(-1)
+    if idx.is_cuda and n_worker > 1 and torch.is_tensor(capacity):
+        # B200 path: count exchange, plan and reassignment as kernels over the symmetric heap,
+        # nothing read on the host (results stay on the device)
+        from ..parallel import symm as _symm
+        done = _symm.swipe_round(idx, capacity, n_expert, n_worker, bias, group)
+        if done is not None:
+            return done[0].view_as(gate_idx), done[1]
     worker = torch.div(idx, n_expert, rounding_mode="floor")
     mine = torch.bincount(worker, minlength=n_worker)[:n_worker].to(torch.int64)
     cap = capacity.reshape(1).to(device=idx.device, dtype=torch.int64)

@@ -663,6 +663,32 @@ def allgather_rows(inp, comm, out=None):
     return out
 
 
+def swipe_round(idx, capacity, n_expert, n_worker, bias, comm=None):
+    r"""One SWIPE round entirely on the device: ``(balanced ids, capacity left)`` — both CUDA
+    tensors — or ``None`` when the peer-to-peer path is not available.
+
+    ``idx``: int64 global expert ids of one choice column; ``capacity``: int64 ``[1]`` tokens this
+    worker can still accept.  Parity: ``cuda/balancing.cu:83-186``; no count is read on the host,
+    so a gate built on it can be captured in a CUDA graph."""
+    if not idx.is_cuda or not config.fused_enabled():
+        return None
+    if comm is None:
+        comm = dist.group.WORLD
+    if dist.get_backend(comm) != "nccl" or dist.get_world_size(comm) != n_worker:
+        return None
+    ws = get_workspace(comm, idx.device)
+    if ws is None:
+        return None
+    nat = native.get()
+    idx = idx.reshape(-1).contiguous()
+    worker = torch.div(idx, n_expert, rounding_mode="floor")
+    want, _rank = nat.route(worker, n_worker)
+    cap = capacity.reshape(1).to(device=idx.device, dtype=torch.int64)
+    _buf, ptrs = ws.buffer("swipe", 2 * ws.world * (ws.world + 1) * 8)
+    quota, left = ws.ctx.swipe_exchange(want, cap, ptrs)
+    return nat.swipe_reassign(idx, quota, n_expert, int(bias)), left
+
+
 def capacity_grant(lec, cap, n_expert, comm=None):
     r"""``(new_lec, new_gec)`` (int64) of a global capacity limit with ONE peer-to-peer exchange,
     or ``None`` when that path is not available.

@@ -522,6 +522,42 @@ def case_shadow_fused():
     assert native.get().read_status(_dev().index) == 0
 
 
+def case_swipe_device():
+    r"""SWIPE rounds computed by the device kernels (exchange + plan + reassignment, no host read)
+    against the all-gather + host plan; then a SwipeGate forward in training mode."""
+    from fastmoe_b200 import gates
+    from fastmoe_b200.functions import ensure_comm
+    from fastmoe_b200.ops import api
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ensure_comm(torch.zeros(1, device=_dev()), None)
+    n_expert = 3
+    for trial in range(4):
+        torch.manual_seed(700 + 11 * trial + rank)
+        n = 500 + 37 * rank
+        # skewed preferences: most tokens want worker 0
+        idx = torch.randint(0, n_expert * world, (n,), device=_dev())
+        idx = torch.where(torch.rand(n, device=_dev()) < 0.6, idx % n_expert, idx)
+        cap = torch.tensor([n * 2 - 100 * trial], dtype=torch.long, device=_dev())
+        os.environ["FMOE_FUSED"] = "1"
+        a_idx, a_left = api.swipe_once(idx, cap, n_expert, world, trial % n_expert)
+        assert a_idx.is_cuda and a_left.is_cuda
+        os.environ["FMOE_FUSED"] = "0"
+        b_idx, b_left = api.swipe_once(idx, cap, n_expert, world, trial % n_expert)
+        os.environ["FMOE_FUSED"] = "1"
+        assert torch.equal(a_idx.cpu(), b_idx.cpu()), (trial, int((a_idx.cpu() != b_idx.cpu()).sum()))
+        assert int(a_left.cpu()) == int(b_left), (int(a_left.cpu()), int(b_left))
+    gate = gates.SwipeGate(64, n_expert, world, top_k=2).to(_dev())
+    gate.train()
+    x = torch.randn(256, 64, device=_dev())
+    ids, score = gate(x)
+    assert ids.shape == (256, 2) and torch.isfinite(score).all()
+    loads = torch.bincount(torch.div(ids.reshape(-1), n_expert, rounding_mode="floor").clamp_min(0),
+                           minlength=world).float()
+    dist.all_reduce(loads)
+    assert float(loads.max()) <= 256 * 2 + 1e-3      # no worker takes more than B * top_k tokens
+    assert native.get().read_status(_dev().index) == 0
+
+
 def case_graph_step():
     r"""A whole expert-parallel training step replays from a CUDA graph."""
     from fastmoe_b200.utils.graph import GraphedStep
