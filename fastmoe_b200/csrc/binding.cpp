@@ -110,9 +110,17 @@ std::vector<torch::Tensor> route(torch::Tensor idx, int64_t tot, bool want_offs,
     pos = torch::empty({n_slots > 0 ? n_slots : 1}, opt);
     pos_ptr = pos.data_ptr<int>();
   }
+  torch::Tensor part;
+  int* part_ptr = nullptr;
+  const int nb = fmoe::route_blocks(n_slots);
+  if (nb > 1) {
+    part = torch::empty({static_cast<int64_t>(nb) * tot}, opt);
+    part_ptr = part.data_ptr<int>();
+    g_launches.fetch_add(1, std::memory_order_relaxed);  // the second launch of the pair
+  }
   FMOE_CUDA_CHECK(fmoe::launch_route(idx.data_ptr<int64_t>(), n_slots, static_cast<int>(tot),
                                      counts.data_ptr<int>(), rank.data_ptr<int>(), offs_ptr,
-                                     pos_ptr, cur_stream()));
+                                     pos_ptr, part_ptr, cur_stream()));
   if (want_pos) return {counts, rank, offs, pos};
   if (want_offs) return {counts, rank, offs};
   return {counts, rank};

@@ -21,11 +21,16 @@ __device__ __forceinline__ unsigned lanemask_lt() {
   return m;
 }
 
-// One CTA.  Warp w owns the contiguous slot range [w * chunk, (w + 1) * chunk): pass 1 builds
-// per-warp histograms, the CTA turns them into exclusive prefixes over warps, pass 2 hands
-// every slot its rank.  Within a warp slots are visited in order, 32 at a time.
+// CTA b owns the contiguous slot range [b * cta_slots, (b + 1) * cta_slots), warp w of it the
+// sub-range [w * chunk, (w + 1) * chunk): pass 1 builds per-warp histograms, the CTA turns them
+// into exclusive prefixes over warps, pass 2 hands every slot its rank.  Within a warp slots
+// are visited in order, 32 at a time.  One CTA does everything in one launch.  For many slots
+// the work is spread over several CTAs and two launches: the first (`part_out`) only writes
+// every CTA's per-expert totals, the second (`part_in`) starts each CTA's prefixes at the sum
+// of the totals of the CTAs before it, so ranks stay those of a single ordered scan.
 __global__ void __launch_bounds__(kRouteThreads, 1)
-route_kernel(const int64_t* __restrict__ idx, int n_slots, int tot, int nw, int* __restrict__ counts,
+route_kernel(const int64_t* __restrict__ idx, int n_slots, int tot, int nw, int cta_slots,
+             const int* __restrict__ part_in, int* __restrict__ part_out, int* __restrict__ counts,
              int* __restrict__ rank, int* __restrict__ offs, int* __restrict__ pos) {
   extern __shared__ int hist[];  // [nw][tot], then [tot + 1] expert offsets when `pos` is wanted
   int* eoff = hist + nw * tot;
@@ -34,10 +39,12 @@ route_kernel(const int64_t* __restrict__ idx, int n_slots, int tot, int nw, int*
   for (int i = threadIdx.x; i < nw * tot; i += blockDim.x) hist[i] = 0;
   __syncthreads();
 
-  int chunk = (n_slots + nw - 1) / nw;
+  const int cta_begin = blockIdx.x * cta_slots;
+  const int cta_end = min(n_slots, cta_begin + cta_slots);
+  int chunk = (cta_slots + nw - 1) / nw;
   chunk = (chunk + 31) & ~31;
-  const int begin = warp * chunk;
-  const int end = min(n_slots, begin + chunk);
+  const int begin = cta_begin + warp * chunk;
+  const int end = min(cta_end, begin + chunk);
 
   if (warp < nw) {
     int* h = hist + warp * tot;
@@ -52,18 +59,35 @@ route_kernel(const int64_t* __restrict__ idx, int n_slots, int tot, int nw, int*
     }
   }
   __syncthreads();
+  if (part_out != nullptr) {
+    // first launch of the multi-CTA scheme: this CTA's totals, nothing else
+    for (int e = threadIdx.x; e < tot; e += blockDim.x) {
+      int run = 0;
+      for (int w = 0; w < nw; ++w) run += hist[w * tot + e];
+      part_out[blockIdx.x * tot + e] = run;
+    }
+    return;
+  }
   for (int e = threadIdx.x; e < tot; e += blockDim.x) {
-    int run = 0;
+    int run = 0, total = 0;
+    if (part_in != nullptr) {
+      for (int b = 0; b < static_cast<int>(gridDim.x); ++b) {
+        const int t = part_in[b * tot + e];
+        if (b < static_cast<int>(blockIdx.x)) run += t;
+        total += t;
+      }
+    }
     for (int w = 0; w < nw; ++w) {
       const int t = hist[w * tot + e];
       hist[w * tot + e] = run;
       run += t;
     }
-    counts[e] = run;
-    if (pos != nullptr) eoff[e + 1] = run;
+    if (part_in == nullptr) total = run;
+    if (blockIdx.x == 0) counts[e] = total;
+    if (pos != nullptr || offs != nullptr) eoff[e + 1] = total;
   }
   __syncthreads();
-  if (pos != nullptr) {
+  if (pos != nullptr || offs != nullptr) {
     // exclusive prefix of the counts: where the slots of every expert start in `pos`
     if (threadIdx.x == 0) {
       int run = 0;
@@ -93,18 +117,8 @@ route_kernel(const int64_t* __restrict__ idx, int n_slots, int tot, int nw, int*
       if (pos != nullptr && valid) pos[eoff[key] + r] = s;
     }
   }
-  if (offs != nullptr) {
-    __syncthreads();
-    if (pos != nullptr) {
-      for (int e = threadIdx.x; e <= tot; e += blockDim.x) offs[e] = eoff[e];
-    } else if (threadIdx.x == 0) {
-      int run = 0;
-      for (int e = 0; e < tot; ++e) {
-        offs[e] = run;
-        run += counts[e];
-      }
-      offs[tot] = run;
-    }
+  if (offs != nullptr && blockIdx.x == 0) {
+    for (int e = threadIdx.x; e <= tot; e += blockDim.x) offs[e] = eoff[e];
   }
 }
 
@@ -750,60 +764,137 @@ __device__ __forceinline__ int group_of_row(const int* offs, int num_groups, int
   return lo;
 }
 
-// One thread per output element; mode 0: NT, mode 1: NN (row modes).
-template <typename T>
-__global__ void simt_rows_kernel(int mode, int num_groups, int n, int k, const T* __restrict__ a,
-                                 const T* __restrict__ b, const int* __restrict__ offs,
-                                 const T* __restrict__ bias, T* __restrict__ out) {
-  using A = typename Acc<T>::type;
-  const int col = blockIdx.y * blockDim.x + threadIdx.x;
-  const int row = blockIdx.x;
-  if (col >= n || row >= offs[num_groups]) return;
-  const int g = group_of_row(offs, num_groups, row);
-  A acc = 0;
-  const T* ar = a + static_cast<long>(row) * k;
-  if (mode == 0) {
-    const T* br = b + (static_cast<long>(g) * n + col) * k;
-    for (int i = 0; i < k; ++i) acc += ldv<T>(ar, i) * ldv<T>(br, i);
-  } else {
-    const T* bg = b + static_cast<long>(g) * k * n + col;
-    for (int i = 0; i < k; ++i) acc += ldv<T>(ar, i) * ldv<T>(bg, static_cast<long>(i) * n);
-  }
-  if (bias != nullptr) acc += ldv<T>(bias, static_cast<long>(g) * n + col);
-  stv<T>(out, static_cast<long>(row) * n + col, acc);
-}
+// Shared-memory tiled SIMT GEMM for the reference-precision types (fp32, fp64) and for 16-bit
+// shapes the tensor-core kernel does not take.  One CTA of 256 threads computes a 64 x 64 tile
+// of C = A B with a K step of 16; every thread owns a 4 x 4 block of the tile and accumulates in
+// fp32 (fp64 for doubles).  The three products of a grouped linear differ only in where A(i, kk)
+// and B(kk, j) live:
+//   mode 0 (NT)   rows of expert g:  A = a[row, kk],   B = b[g, j, kk]
+//   mode 1 (NN)   rows of expert g:  A = a[row, kk],   B = b[g, kk, j]
+//   mode 2 (wgrad) out[g, i, j]:     A = p[r0 + kk, i], B = q[r0 + kk, j], K = rows of expert g
+// (the reference calls cublasSgemm / cublasDgemm per expert here, cuda/utils/cublas_wrapper.h:51-72).
+constexpr int kSimtTile = 64;
+constexpr int kSimtK = 16;
 
-// out[g, mi, ni] = sum_r P[r, mi] * Q[r, ni]
-template <typename T>
-__global__ void simt_wgrad_kernel(int m, int n, const T* __restrict__ p, const T* __restrict__ q,
-                                  const int* __restrict__ offs, T* __restrict__ out) {
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+simt_tiled_kernel(int num_groups, int m, int n, int k, const T* __restrict__ a, const T* __restrict__ b,
+                  const int* __restrict__ offs, const T* __restrict__ bias, T* __restrict__ out) {
   using A = typename Acc<T>::type;
-  const int ni = blockIdx.x * blockDim.x + threadIdx.x;
-  const int mi = blockIdx.y;
-  const int g = blockIdx.z;
-  if (ni >= n) return;
-  A acc = 0;
-  for (int r = offs[g]; r < offs[g + 1]; ++r) {
-    acc += ldv<T>(p, static_cast<long>(r) * m + mi) * ldv<T>(q, static_cast<long>(r) * n + ni);
+  __shared__ A As[kSimtK][kSimtTile + 4];
+  __shared__ A Bs[kSimtK][kSimtTile + 4];
+  int g, i0, rows_i, kk_total, row_base;
+  const int j0 = blockIdx.y * kSimtTile;
+  if (MODE == 2) {
+    g = blockIdx.z;
+    i0 = blockIdx.x * kSimtTile;
+    rows_i = m;
+    row_base = offs[g];
+    kk_total = offs[g + 1] - row_base;
+  } else {
+    // blockIdx.x walks the 64-row pieces of all experts: find the expert this piece belongs to
+    int piece = blockIdx.x;
+    bool found = false;
+    for (g = 0; g < num_groups; ++g) {
+      const int cnt = offs[g + 1] - offs[g];
+      const int pieces = (cnt + kSimtTile - 1) / kSimtTile;
+      if (piece < pieces) {
+        found = true;
+        break;
+      }
+      piece -= pieces;
+    }
+    if (!found) return;
+    row_base = offs[g];
+    i0 = piece * kSimtTile;
+    rows_i = offs[g + 1] - row_base;
+    kk_total = k;
   }
-  stv<T>(out, (static_cast<long>(g) * m + mi) * n + ni, acc);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  A acc[4][4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) acc[u][v] = 0;
+  }
+  for (int kk0 = 0; kk0 < kk_total; kk0 += kSimtK) {
+    // 16 x 64 elements of each operand, 4 per thread
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      const int e = threadIdx.x + l * 256;
+      int kk, ii;
+      if (MODE == 2) { kk = e / kSimtTile; ii = e % kSimtTile; }    // A is row-major over (kk, i)
+      else { ii = e / kSimtK; kk = e % kSimtK; }                    // A is row-major over (i, kk)
+      A va = 0;
+      if (kk0 + kk < kk_total && i0 + ii < rows_i) {
+        va = MODE == 2 ? ldv<T>(a, static_cast<long>(row_base + kk0 + kk) * m + i0 + ii)
+                       : ldv<T>(a, static_cast<long>(row_base + i0 + ii) * k + kk0 + kk);
+      }
+      As[kk][ii] = va;
+      int kb, jj;
+      if (MODE == 0) { jj = e / kSimtK; kb = e % kSimtK; }          // B is row-major over (j, kk)
+      else { kb = e / kSimtTile; jj = e % kSimtTile; }              // B is row-major over (kk, j)
+      A vb = 0;
+      if (kk0 + kb < kk_total && j0 + jj < n) {
+        if (MODE == 0) vb = ldv<T>(b, (static_cast<long>(g) * n + j0 + jj) * k + kk0 + kb);
+        else if (MODE == 1) vb = ldv<T>(b, (static_cast<long>(g) * k + kk0 + kb) * n + j0 + jj);
+        else vb = ldv<T>(b, static_cast<long>(row_base + kk0 + kb) * n + j0 + jj);
+      }
+      Bs[kb][jj] = vb;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kSimtK; ++kk) {
+      A ra[4], rb[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) ra[u] = As[kk][ty * 4 + u];
+#pragma unroll
+      for (int v = 0; v < 4; ++v) rb[v] = Bs[kk][tx * 4 + v];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) acc[u][v] += ra[u] * rb[v];
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int ii = i0 + ty * 4 + u;
+    if (ii >= rows_i) continue;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int jj = j0 + tx * 4 + v;
+      if (jj >= n) continue;
+      A val = acc[u][v];
+      if (MODE != 2 && bias != nullptr) val += ldv<T>(bias, static_cast<long>(g) * n + jj);
+      const long o = MODE == 2 ? (static_cast<long>(g) * m + ii) * n + jj
+                               : static_cast<long>(row_base + ii) * n + jj;
+      stv<T>(out, o, val);
+    }
+  }
 }
 
 template <typename T>
 cudaError_t simt_typed(int mode, int num_groups, long rows_cap, int m, int n, int k, const void* a,
                        const void* b, const int* offs, const void* bias, void* out,
                        cudaStream_t stream) {
+  const T* ap = static_cast<const T*>(a);
+  const T* bp = static_cast<const T*>(b);
+  const T* biasp = static_cast<const T*>(bias);
+  T* op = static_cast<T*>(out);
+  const unsigned nt = (n + kSimtTile - 1) / kSimtTile;
   if (mode == 2) {
-    dim3 grid((n + 127) / 128, m, num_groups);
-    simt_wgrad_kernel<T><<<grid, 128, 0, stream>>>(m, n, static_cast<const T*>(a),
-                                                   static_cast<const T*>(b), offs,
-                                                   static_cast<T*>(out));
+    dim3 grid((m + kSimtTile - 1) / kSimtTile, nt, num_groups);
+    simt_tiled_kernel<T, 2><<<grid, 256, 0, stream>>>(num_groups, m, n, k, ap, bp, offs, biasp, op);
   } else {
     if (rows_cap == 0) return cudaSuccess;
-    dim3 grid(static_cast<unsigned>(rows_cap), (n + 127) / 128);
-    simt_rows_kernel<T><<<grid, 128, 0, stream>>>(mode, num_groups, n, k, static_cast<const T*>(a),
-                                                  static_cast<const T*>(b), offs,
-                                                  static_cast<const T*>(bias), static_cast<T*>(out));
+    dim3 grid(static_cast<unsigned>((rows_cap + kSimtTile - 1) / kSimtTile + num_groups), nt);
+    if (mode == 0) {
+      simt_tiled_kernel<T, 0><<<grid, 256, 0, stream>>>(num_groups, m, n, k, ap, bp, offs, biasp, op);
+    } else {
+      simt_tiled_kernel<T, 1><<<grid, 256, 0, stream>>>(num_groups, m, n, k, ap, bp, offs, biasp, op);
+    }
   }
   return cudaGetLastError();
 }
@@ -811,13 +902,24 @@ cudaError_t simt_typed(int mode, int num_groups, long rows_cap, int m, int n, in
 }  // namespace
 
 // ------------------------------------------------------------------------------ launchers
+int route_blocks(int n_slots) {
+  // one CTA up to 32 K slots (a single launch, about 8 us); beyond that 16 K slots per CTA
+  if (n_slots <= 32768) return 1;
+  int nb = (n_slots + 16383) / 16384;
+  return nb > 148 ? 148 : nb;
+}
+
 cudaError_t launch_route(const int64_t* idx, int n_slots, int tot, int* counts, int* rank,
-                         int* offs, int* pos, cudaStream_t stream) {
+                         int* offs, int* pos, int* part, cudaStream_t stream) {
   if (tot <= 0) return cudaErrorInvalidValue;
   int nw = (kRouteSmemLimit - 4 * (tot + 1)) / (4 * tot);
   if (nw < 1) return cudaErrorInvalidValue;
   if (nw > 32) nw = 32;
-  const int by_work = (n_slots + 31) / 32;
+  const int nb = part != nullptr ? route_blocks(n_slots) : 1;
+  int cta_slots = (n_slots + nb - 1) / nb;
+  cta_slots = (cta_slots + 31) & ~31;
+  if (cta_slots < 32) cta_slots = 32;
+  const int by_work = (cta_slots + 31) / 32;
   if (nw > by_work) nw = by_work > 0 ? by_work : 1;
   const size_t smem = static_cast<size_t>(nw) * tot * 4 + static_cast<size_t>(tot + 1) * 4;
   if (smem > 48 * 1024) {
@@ -825,7 +927,15 @@ cudaError_t launch_route(const int64_t* idx, int n_slots, int tot, int* counts, 
                                          kRouteSmemLimit);
     if (e != cudaSuccess) return e;
   }
-  route_kernel<<<1, kRouteThreads, smem, stream>>>(idx, n_slots, tot, nw, counts, rank, offs, pos);
+  if (nb > 1) {
+    route_kernel<<<nb, kRouteThreads, smem, stream>>>(idx, n_slots, tot, nw, cta_slots, nullptr, part,
+                                                     counts, rank, offs, pos);
+    route_kernel<<<nb, kRouteThreads, smem, stream>>>(idx, n_slots, tot, nw, cta_slots, part, nullptr,
+                                                     counts, rank, offs, pos);
+  } else {
+    route_kernel<<<1, kRouteThreads, smem, stream>>>(idx, n_slots, tot, nw, cta_slots, nullptr, nullptr,
+                                                    counts, rank, offs, pos);
+  }
   return cudaGetLastError();
 }
 

@@ -9,8 +9,11 @@ namespace fmoe {
 // (exclusive prefix of counts) and optional pos[n_slots] (slot ids sorted by expert, then by
 // rank: pos[offs[e] + rank[s]] = s; entries past offs[tot] are not written).  Deterministic:
 // slots of one expert are ranked by slot id.
+// `part` (optional): int32 scratch of route_blocks(n_slots) * tot entries; with it, more than
+// 32 K slots are ranked by several CTAs in two launches instead of by one CTA.
+int route_blocks(int n_slots);
 cudaError_t launch_route(const int64_t* idx, int n_slots, int tot, int* counts, int* rank,
-                         int* offs, int* pos, cudaStream_t stream);
+                         int* offs, int* pos, int* part, cudaStream_t stream);
 
 // new_idx[s] = (idx[s] >= 0 && rank[s] < cap[idx[s]]) ? idx[s] : -1
 cudaError_t launch_prune(const int64_t* idx, const int* rank, const int* cap, int n_slots, int tot,

@@ -191,11 +191,13 @@ def test_grouped_gemm_wgrad(dtype, counts, m, n):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
-def test_simt_grouped_linear(dtype):
+@pytest.mark.parametrize("counts,k,n", [([5, 0, 9, 3], 16, 24), ([300, 65, 0, 130], 200, 150)])
+def test_simt_grouped_linear(dtype, counts, k, n):
+    r"""The shared-memory tiled kernel for fp32 / fp64, ragged in every dimension."""
     from fastmoe_b200.ops import grouped_gemm as gg
     torch.manual_seed(3)
-    counts = [5, 0, 9, 3]
-    rows, k, n = sum(counts), 16, 24
+    torch.backends.cuda.matmul.allow_tf32 = False
+    rows = sum(counts)
     x = torch.randn(rows, k, device=DEV, dtype=dtype)
     w = torch.randn(len(counts), n, k, device=DEV, dtype=dtype)
     b = torch.randn(len(counts), n, device=DEV, dtype=dtype)
@@ -204,18 +206,26 @@ def test_simt_grouped_linear(dtype):
     out = gg.linear_forward_host_counts(x, cnt, w, b)
     gi, gw, gb = gg.linear_backward_host_counts(go, x, cnt, w, b)
     for e, lo, hi in _segments(counts):
-        assert torch.allclose(out[lo:hi], x[lo:hi] @ w[e].t() + b[e], atol=1e-4)
-        assert torch.allclose(gi[lo:hi], go[lo:hi] @ w[e], atol=1e-4)
-        assert torch.allclose(gw[e], go[lo:hi].t() @ x[lo:hi], atol=1e-4)
-        assert torch.allclose(gb[e], go[lo:hi].sum(0), atol=1e-4)
+        assert torch.allclose(out[lo:hi], x[lo:hi] @ w[e].t() + b[e], atol=2e-3, rtol=1e-4)
+        assert torch.allclose(gi[lo:hi], go[lo:hi] @ w[e], atol=2e-3, rtol=1e-4)
+        assert torch.allclose(gw[e], go[lo:hi].t() @ x[lo:hi], atol=2e-3, rtol=1e-4)
+        assert torch.allclose(gb[e], go[lo:hi].sum(0), atol=2e-3, rtol=1e-4)
 
 
-@pytest.mark.parametrize("n_slots,tot", [(7, 3), (64, 4), (8192, 16), (50001, 64), (4096, 1024)])
+@pytest.mark.parametrize("n_slots,tot", [(7, 3), (64, 4), (8192, 16), (50001, 64), (4096, 1024),
+                                         (1000003, 256), (300000, 8)])
 def test_route_matches_cpu(n_slots, tot):
+    r"""Counts, ranks, offsets and the sorted slot list; above 32 K slots several CTAs share the
+    ranking (two launches) and must reproduce the single ordered scan."""
     from fastmoe_b200.ops import torch_impl
     torch.manual_seed(4)
     idx = torch.randint(-1, tot, (n_slots,), device=DEV)
     counts, rank, offs = _native().route_offs(idx, tot)
+    c2, r2, o2, pos = _native().route_pos(idx, tot)
+    assert torch.equal(c2, counts) and torch.equal(r2, rank) and torch.equal(o2, offs)
+    kept = int(offs[-1])
+    order = torch.argsort(torch.where(idx >= 0, idx, tot).cpu(), stable=True)[:kept]
+    assert torch.equal(pos[:kept].cpu().long(), order)
     ref_counts = torch_impl.expert_count(idx.cpu(), tot)
     ref_rank = torch_impl.slot_rank(idx.cpu(), tot)
     assert torch.equal(counts.cpu(), ref_counts)
