@@ -113,6 +113,15 @@ def emit(obj):
     print(json.dumps(obj), flush=True)
 
 
+def give_up_reference(reason, rank, world):
+    r"""The reference arm could not run: say why in the one JSON line, then leave quietly (process
+    group closed first, so that the JSON line stays the last line of the output)."""
+    if rank == 0:
+        emit({"impl": "reference", "unavailable": reason[:400]})
+    sys.stdout.flush()
+    os._exit(0)  # pylint: disable=protected-access
+
+
 # ------------------------------------------------------------------------------ clocks
 class ClockSampler:
     r"""Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
@@ -324,9 +333,7 @@ def main():
         layer, model, launch_counter = build(rank, world, device)
     except Exception as exc:  # pylint: disable=broad-except
         if args.impl == "reference":
-            if rank == 0:
-                emit({"impl": "reference", "unavailable": "reference failed to start: %r" % (exc,)})
-            return
+            give_up_reference("reference failed to start: %r" % (exc,), rank, world)
         raise
 
     is_lm = CFG["kind"] == "lm"
@@ -440,9 +447,7 @@ def main():
         if rank == 0:
             sampler.stop()
         if args.impl == "reference":
-            if rank == 0:
-                emit({"impl": "reference", "unavailable": "reference step failed: %r" % (exc,)})
-            return
+            give_up_reference("reference step failed: %r" % (exc,), rank, world)
         raise
 
     warm_steps = max(args.warmup, 3)
@@ -454,9 +459,7 @@ def main():
         if rank == 0:
             sampler.stop()
         if args.impl == "reference":
-            if rank == 0:
-                emit({"impl": "reference", "unavailable": "reference step failed: %r" % (exc,)})
-            return
+            give_up_reference("reference step failed: %r" % (exc,), rank, world)
         raise
 
     # ------------------------------------------------ device-timed region (inputs resident)

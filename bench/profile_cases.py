@@ -31,10 +31,11 @@ def gemm_case(repeats=2):
     w2 = torch.randn(n_exp, d, h, device=dev, dtype=torch.bfloat16) * 0.02
     offs = torch.arange(0, rows + 1, rows_per, device=dev, dtype=torch.int32)
     hid = torch.randn(rows, h, device=dev, dtype=torch.bfloat16)
+    pre = gg.pre_buffer(rows, h, n_exp, torch.bfloat16, dev).normal_()   # tile-blocked pre-activation
     for _ in range(repeats):
         gg.forward(x, w1, offs, b1, act="gelu", want_pre=True)   # GEMM 1: NT + bias + GELU + pre-activation
         gg.forward(hid, w2, offs, None)                          # GEMM 2: NT plain
-        gg.dgrad(x, w2, offs, pre=hid, act="gelu")               # dgrad 2: NN + GELU derivative
+        gg.dgrad(x, w2, offs, pre=pre, act="gelu")               # dgrad 2: NN + GELU derivative
         gg.dgrad(hid, w1, offs)                                  # dgrad 1: NN plain
         gg.wgrad(hid, x, offs, n_exp, with_bias_grad=True)       # wgrad 1 (+ bias gradient)
         gg.wgrad(x, hid, offs, n_exp, with_bias_grad=True)       # wgrad 2 (+ bias gradient)
