@@ -108,6 +108,18 @@ def ep_layer_case(repeats=3, n_tok=4096, d=1024, h=4096, n_exp=2, k=2):
     for g, w in zip(got, want):
         err = float((g - w).abs().max())
         assert err <= 0.05 * float(w.abs().max()) + 1e-2, err
+    # device time of every grouped-GEMM launch of the two paths (fused dispatch / return push
+    # against the plain single-GPU kernels)
+    from torch.profiler import ProfilerActivity, profile
+    for name, fn in (("expert-parallel kernels", symm.moe_mlp_forward), ("single-GPU path", fused.moe_mlp_forward)):
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(5):
+                run(fn)
+            torch.cuda.synchronize()
+        for ev in sorted(prof.key_averages(), key=lambda e: e.key):
+            if "grouped_gemm" in ev.key or "scatter" in ev.key or "combine" in ev.key:
+                print("%-24s %-58s %8.1f us x %d" % (name, ev.key[:58], ev.device_time_total / ev.count,
+                                                     ev.count // 5))
     dist.destroy_process_group()
 
 
