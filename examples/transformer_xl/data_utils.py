@@ -3,7 +3,8 @@ Corpora, vocabulary and batch iterators for the Transformer-XL example.
 
 Counterpart of the reference's ``examples/transformer-xl/data_utils.py`` and
 ``utils/vocabulary.py``: word-level corpora with an ``<eos>`` per line (``ptb``, ``wt2``,
-``wt103``), character-level corpora stored as space-separated symbols (``enwik8``, ``text8``),
+``wt103``), the sharded One Billion Word corpus with its published vocabulary (``lm1b``),
+character-level corpora stored as space-separated symbols (``enwik8``, ``text8``),
 contiguous batching for truncated back-propagation through time with an optional extended
 context, an optional variable target length, and a binary cache next to the text files.
 ``synthetic`` needs no files: a Zipf-distributed token stream of a given vocabulary size.
@@ -58,12 +59,32 @@ class Vocab:
         assert hasattr(self, "unk_idx"), "symbol %r is not in the vocabulary and there is no <unk>" % sym
         return self.unk_idx
 
-    def encode_file(self, path, add_eos=True):
+    def encode_file(self, path, add_eos=True, sentence_marks=None):
+        r"""Token ids of a text file.  ``sentence_marks``: a symbol put before and after every line
+        (the One Billion Word corpus is a set of shuffled sentences, each wrapped in ``<S>``)."""
         ids = []
         with open(path, "r", encoding="utf-8") as f:
             for line in f:
-                ids.extend(self.index(s) for s in self.tokenize(line, add_eos))
+                symbols = self.tokenize(line, add_eos)
+                if sentence_marks is not None:
+                    symbols = [sentence_marks] + symbols + [sentence_marks]
+                ids.extend(self.index(s) for s in symbols)
         return torch.tensor(ids, dtype=torch.long)
+
+    def build_from_file(self, path):
+        r"""Vocabulary from a file with one symbol per line (first column), in file order."""
+        self.idx2sym, self.sym2idx = [], {}
+        for sym in self.special:
+            self._add(sym)
+        with open(path, "r", encoding="utf-8") as f:
+            for line in f:
+                parts = line.split()
+                if parts:
+                    self._add(parts[0])
+        if "<UNK>" in self.sym2idx:
+            self.unk_idx = self.sym2idx["<UNK>"]
+        elif "<unk>" in self.sym2idx:
+            self.unk_idx = self.sym2idx["<unk>"]
 
     def __len__(self):
         return len(self.idx2sym)
@@ -136,6 +157,20 @@ class Corpus:
         elif dataset in self.CHAR_LEVEL:
             self.vocab = Vocab()
             names, add_eos = "%s.txt", False
+        elif dataset == "lm1b":
+            # One Billion Word: a published vocabulary file, 100 shuffled training shards and
+            # 50 held-out shards (shard 0 is the customary validation / test set)
+            import glob
+            self.vocab = Vocab()
+            self.vocab.build_from_file(os.path.join(path, "1b_word_vocab.txt"))
+            root = os.path.join(path, "1-billion-word-language-modeling-benchmark-r13output")
+            shards = sorted(glob.glob(os.path.join(root, "training-monolingual.tokenized.shuffled", "news.en-*")))
+            held = os.path.join(root, "heldout-monolingual.tokenized.shuffled", "news.en.heldout-00000-of-00050")
+            self.train = torch.cat([self.vocab.encode_file(f, add_eos=False, sentence_marks="<S>") for f in shards])
+            self.valid = self.vocab.encode_file(held, add_eos=False, sentence_marks="<S>")
+            self.test = self.valid
+            self.n_token = len(self.vocab)
+            return
         else:
             raise ValueError("unknown dataset %r" % dataset)
         files = {split: os.path.join(path, names % split) for split in ("train", "valid", "test")}
@@ -155,6 +190,8 @@ def default_cutoffs(dataset, n_token):
     r"""Cluster boundaries of the adaptive softmax per corpus (frequency-sorted vocabulary)."""
     if dataset == "wt103":
         return [20000, 40000, 200000]
+    if dataset == "lm1b":
+        return [60000, 100000, 640000]
     if dataset == "synthetic" and n_token >= 4096:
         return [n_token // 16, n_token // 4]
     return []

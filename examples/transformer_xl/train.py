@@ -44,7 +44,7 @@ def get_args(argv=None):
     p = argparse.ArgumentParser(description="Transformer-XL with MoE feed-forward blocks")
     p.add_argument("--data", default=".", help="directory of the corpus files")
     p.add_argument("--dataset", default="synthetic",
-                   choices=["synthetic", "wt103", "wt2", "ptb", "enwik8", "text8"])
+                   choices=["synthetic", "wt103", "wt2", "ptb", "enwik8", "text8", "lm1b"])
     p.add_argument("--n_token", type=int, default=256, help="vocabulary size of the synthetic corpus")
     p.add_argument("--n_layer", type=int, default=12)
     p.add_argument("--n_head", type=int, default=8)

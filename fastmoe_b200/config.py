@@ -78,11 +78,6 @@ def fused_enabled():
     return switch_from_env("FMOE_FUSED", True)
 
 
-def deterministic():
-    r"""Slot assignment is always scan-based (deterministic); kept as a switch for API stability."""
-    return switch_from_env("FMOE_DETERMINISTIC", True)
-
-
 def wait_timeout_ms():
     r"""Upper bound of every device-side wait on a peer, in milliseconds.
 
@@ -103,16 +98,6 @@ def nvtx_enabled():
     r"""``FMOE_NVTX=1``: NVTX ranges around the fused paths (forward, backward, exchange,
     gradient all-reduce) for timeline tools."""
     return switch_from_env("FMOE_NVTX", False)
-
-
-def use_nvls():
-    r"""``FMOE_USE_NVLS``: ``auto`` (default) tries NVSwitch multimem and falls back to peer loads."""
-    v = os.environ.get("FMOE_USE_NVLS", "auto")
-    if v in _TRUE:
-        return True
-    if v in ("0", "OFF", "off", "false", "False"):
-        return False
-    return None
 
 
 def recv_capacity_factor():
