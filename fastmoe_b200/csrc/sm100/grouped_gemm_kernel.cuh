@@ -208,73 +208,6 @@ __device__ __forceinline__ float tanh_approx(float x) {
   return y;
 }
 
-// The same GELU pieces for two values at once with the packed fp32 instructions of sm_100
-// (add / mul / fma .f32x2 on 64-bit register pairs): the polynomial, the argument of the
-// exponential and the sign handling cost half the instructions; only the two MUFU operations
-// (rcp, ex2) stay per element.
-__device__ __forceinline__ uint64_t pk2(float a, float b) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void upk2(uint64_t v, float& a, float& b) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-struct GeluParts2 {
-  uint64_t cdf;    // Phi(x) of both values
-  uint64_t gauss;  // exp(-x^2 / 2) of both values
-};
-__device__ __forceinline__ GeluParts2 gelu_parts2(uint64_t x) {
-  const uint64_t ax = x & 0x7fffffff7fffffffull;
-  // t = 1 / (1 + 0.3275911 |x| / sqrt 2)
-  float d0, d1, t0, t1;
-  upk2(fma2(ax, pk2(0.23164190f, 0.23164190f), pk2(1.f, 1.f)), d0, d1);
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t0) : "f"(d0));
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t1) : "f"(d1));
-  const uint64_t t = pk2(t0, t1);
-  uint64_t p = fma2(t, pk2(0.5f * 1.061405429f, 0.5f * 1.061405429f), pk2(0.5f * -1.453152027f, 0.5f * -1.453152027f));
-  p = fma2(p, t, pk2(0.5f * 1.421413741f, 0.5f * 1.421413741f));
-  p = fma2(p, t, pk2(0.5f * -0.284496736f, 0.5f * -0.284496736f));
-  p = fma2(p, t, pk2(0.5f * 0.254829592f, 0.5f * 0.254829592f));
-  p = mul2(p, t);
-  float e0, e1, g0, g1;
-  upk2(mul2(mul2(x, x), pk2(-0.72134752044448170f, -0.72134752044448170f)), e0, e1);
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(g0) : "f"(e0));
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(g1) : "f"(e1));
-  GeluParts2 r;
-  r.gauss = pk2(g0, g1);
-  // 0.5 erfc(|x| / sqrt 2) = p * gauss <= 0.5;  Phi(x) = 0.5 + copysign(0.5 - that, x)
-  uint64_t s = fma2(mul2(p, r.gauss), pk2(-1.f, -1.f), pk2(0.5f, 0.5f));
-  s |= x & 0x8000000080000000ull;
-  r.cdf = add2(s, pk2(0.5f, 0.5f));
-  return r;
-}
-__device__ __forceinline__ void gelu_fwd2(float& a, float& b) {
-  const uint64_t x = pk2(a, b);
-  upk2(mul2(x, gelu_parts2(x).cdf), a, b);
-}
-// Phi(x) + x phi(x) for both values
-__device__ __forceinline__ void gelu_grad2(float sa, float sb, float& ga, float& gb) {
-  const uint64_t x = pk2(sa, sb);
-  const GeluParts2 g = gelu_parts2(x);
-  upk2(fma2(mul2(x, pk2(0.3989422804014327f, 0.3989422804014327f)), g.gauss, g.cdf), ga, gb);
-}
-
 template <int ACT> __device__ __forceinline__ float act_fwd(float x) {
   if (ACT == kActRelu) return fmaxf(x, 0.f);
   if (ACT == kActGelu) return x * gelu_parts(x).cdf;
@@ -588,16 +521,10 @@ __device__ __forceinline__ void rows_chunk(const RowTile& rt, int i, bool with_p
     if (rt.use_aux) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float sa, sb, ga, gb;
+        float sa, sb;
         Cvt<T>::unpack(side_cur.w[q * 8 + j], sa, sb);
-        if (ACT == kActGelu) {
-          gelu_grad2(sa, sb, ga, gb);
-        } else {
-          ga = act_grad<ACT>(sa);
-          gb = act_grad<ACT>(sb);
-        }
-        const float a = __uint_as_float(r[q * 16 + 2 * j]) * ga;
-        const float b = __uint_as_float(r[q * 16 + 2 * j + 1]) * gb;
+        const float a = __uint_as_float(r[q * 16 + 2 * j]) * act_grad<ACT>(sa);
+        const float b = __uint_as_float(r[q * 16 + 2 * j + 1]) * act_grad<ACT>(sb);
         wo[j] = Cvt<T>::pack(a, b);
       }
     } else {
@@ -621,12 +548,8 @@ __device__ __forceinline__ void rows_chunk(const RowTile& rt, int i, bool with_p
         }
         if (ACT != kActNone) {
           wp[j] = Cvt<T>::pack(a, b);
-          if (ACT == kActGelu) {
-            gelu_fwd2(a, b);
-          } else {
-            a = act_fwd<ACT>(a);
-            b = act_fwd<ACT>(b);
-          }
+          a = act_fwd<ACT>(a);
+          b = act_fwd<ACT>(b);
         }
         wo[j] = Cvt<T>::pack(a, b);
       }
