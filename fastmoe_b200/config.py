@@ -100,6 +100,14 @@ def nvtx_enabled():
     return switch_from_env("FMOE_NVTX", False)
 
 
+def use_nvls():
+    r"""``FMOE_USE_NVLS=1``: gradient all-reduce through NVSwitch (``multimem.ld_reduce`` /
+    ``multimem.st`` on the multicast mapping of the symmetric buffer) when the allocation has
+    one; plain peer loads and stores otherwise.  Off by default: keep it off in runs where a rank
+    may leave while its memory is bound to a multicast object (failure tests)."""
+    return switch_from_env("FMOE_USE_NVLS", False)
+
+
 def recv_capacity_factor():
     r"""Rows reserved in the expert receive buffer, as a multiple of the balanced load.
 

@@ -628,6 +628,92 @@ __global__ void allreduce_two_shot_kernel(const __grid_constant__ ExchangeCtx c,
   }
 }
 
+// NVSwitch (NVLS) variant of the two-shot all-reduce.  `mc` is the multicast address of the
+// symmetric buffers: one `multimem.ld_reduce` on it returns the sum of the same 16 bytes of all
+// ranks' buffers, formed inside the switch (fp32 accumulation for the 16-bit types), and one
+// `multimem.st` writes a value into all of them.  Rank r reduces the r-th slice, scales it and
+// broadcasts it; afterwards every rank copies its own, fully reduced buffer out.  Per GPU only
+// 1 / W of the data is pulled through the switch and 1 / W pushed, against (W - 1) / W read and
+// written by the peer-to-peer two-shot kernel.  Every rank gets the same bits.
+template <int DT> struct MultimemOps;
+template <> struct MultimemOps<0> {  // bf16
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ uint4 scale(uint4 v, float s) {
+    float f[8];
+    unpack8<__nv_bfloat16>(v, f);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) f[q] *= s;
+    return pack8<__nv_bfloat16>(f);
+  }
+};
+template <> struct MultimemOps<1> {  // fp16
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ uint4 scale(uint4 v, float s) {
+    float f[8];
+    unpack8<__half>(v, f);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) f[q] *= s;
+    return pack8<__half>(f);
+  }
+};
+template <> struct MultimemOps<2> {  // fp32
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ uint4 scale(uint4 v, float s) {
+    v.x = __float_as_uint(__uint_as_float(v.x) * s);
+    v.y = __float_as_uint(__uint_as_float(v.y) * s);
+    v.z = __float_as_uint(__uint_as_float(v.z) * s);
+    v.w = __float_as_uint(__uint_as_float(v.w) * s);
+    return v;
+  }
+};
+
+template <int DT>
+__global__ void allreduce_multimem_kernel(const __grid_constant__ ExchangeCtx c, uint8_t* __restrict__ mc,
+                                          const uint8_t* __restrict__ mine, uint8_t* __restrict__ out,
+                                          long nbytes, float scale) {
+  const int target_ready = 2 * c.epoch[kReduceEpochWord];
+  if (blockIdx.x == 0 && threadIdx.x == 0) signal_all(c, kChanReduce, target_ready);
+  block_wait_all(c, kChanReduce, target_ready);
+  const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  const long nvec = (nbytes + 15) / 16;      // the buffers are padded to whole 16-byte pieces
+  const long per_rank = (nvec + c.world - 1) / c.world;
+  const long lo = per_rank * c.me;
+  const long hi = (lo + per_rank < nvec) ? lo + per_rank : nvec;
+  for (long i = lo + tid; i < hi; i += stride) {
+    const uint4 v = MultimemOps<DT>::scale(MultimemOps<DT>::ld_reduce(mc + i * 16), scale);
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc + i * 16),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+  }
+  if (last_block(c.epoch + 3)) {
+    if (threadIdx.x == 0) signal_all(c, kChanReduce, target_ready + 1);
+  }
+  block_wait_all(c, kChanReduce, target_ready + 1);
+  const long nfull = nbytes / 16;
+  for (long i = tid; i < nfull; i += stride) {
+    reinterpret_cast<uint4*>(out)[i] = __ldcg(reinterpret_cast<const uint4*>(mine) + i);
+  }
+  for (long b = nfull * 16 + tid; b < nbytes; b += stride) {
+    out[b] = *(reinterpret_cast<const volatile uint8_t*>(mine) + b);
+  }
+}
+
 // All-gather of equal slices: every rank stores its slice at offset `me` of every peer's
 // symmetric buffer, publishes, waits for all peers and copies the assembled buffer out.
 // The first handshake makes sure no peer is still reading its buffer from an earlier call.
@@ -909,6 +995,23 @@ cudaError_t launch_allreduce_two_shot(const ExchangeCtx& ctx, int dtype, const P
   } else {
     return cudaErrorInvalidValue;
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_allreduce_multimem(const ExchangeCtx& ctx, int dtype, void* mc, const void* mine,
+                                      void* out, long nbytes, float scale, cudaStream_t stream) {
+  if (mc == nullptr || nbytes <= 0) return cudaErrorInvalidValue;
+  long blocks = (nbytes / 16 / ctx.world + 255) / 256;
+  if (blocks > 148 * 2) blocks = 148 * 2;   // whole grid resident: every block waits mid-kernel
+  if (blocks < 1) blocks = 1;
+  const int grid = static_cast<int>(blocks);
+  uint8_t* m = static_cast<uint8_t*>(mc);
+  const uint8_t* l = static_cast<const uint8_t*>(mine);
+  uint8_t* o = static_cast<uint8_t*>(out);
+  if (dtype == 0) allreduce_multimem_kernel<0><<<grid, 256, 0, stream>>>(ctx, m, l, o, nbytes, scale);
+  else if (dtype == 1) allreduce_multimem_kernel<1><<<grid, 256, 0, stream>>>(ctx, m, l, o, nbytes, scale);
+  else if (dtype == 2) allreduce_multimem_kernel<2><<<grid, 256, 0, stream>>>(ctx, m, l, o, nbytes, scale);
+  else return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 

@@ -113,6 +113,12 @@ cudaError_t launch_allreduce(const ExchangeCtx& ctx, int dtype, const PeerPtrs& 
 cudaError_t launch_allreduce_two_shot(const ExchangeCtx& ctx, int dtype, const PeerPtrs& bufs,
                                       void* out, long n, float scale, cudaStream_t stream);
 
+// The same sum through NVSwitch: `mc` is the multicast address of the symmetric buffers (a
+// multiple of 16 bytes long, at least `nbytes`), `mine` this rank's own buffer.  In-switch
+// reduction (`multimem.ld_reduce`) of one slice per rank, result broadcast with `multimem.st`.
+cudaError_t launch_allreduce_multimem(const ExchangeCtx& ctx, int dtype, void* mc, const void* mine,
+                                      void* out, long nbytes, float scale, cudaStream_t stream);
+
 // All-gather of equal slices (`bytes_per_rank` a multiple of 16) through symmetric buffers of
 // at least world * bytes_per_rank bytes: out = [slice of rank 0, slice of rank 1, ...].
 cudaError_t launch_allgather(const ExchangeCtx& ctx, const void* src, const PeerPtrs& bufs,

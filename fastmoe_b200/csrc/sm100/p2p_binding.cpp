@@ -182,6 +182,25 @@ class ExchangeContext {
     }
   }
 
+  // All-reduce through the NVSwitch multicast mapping of the symmetric buffers.
+  void allreduce_multimem(int64_t mc_ptr, int64_t mine_ptr, torch::Tensor out, double scale) {
+    c10::cuda::CUDAGuard guard(out.device());
+    int code;
+    switch (out.scalar_type()) {
+      case torch::kBFloat16: code = 0; break;
+      case torch::kHalf: code = 1; break;
+      case torch::kFloat: code = 2; break;
+      default: TORCH_CHECK(false, "allreduce_multimem: bf16, fp16 or fp32"); code = -1;
+    }
+    TORCH_CHECK(mc_ptr != 0 && mc_ptr % 16 == 0 && mine_ptr % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0,
+                "allreduce_multimem: a multicast mapping and 16-byte aligned buffers are required");
+    FMOE_P2P_CHECK(fmoe::launch_begin_reduce_epoch(ctx_, stream()));
+    FMOE_P2P_CHECK(fmoe::launch_allreduce_multimem(
+        ctx_, code, reinterpret_cast<void*>(mc_ptr), reinterpret_cast<const void*>(mine_ptr),
+        out.data_ptr(), out.numel() * out.element_size(), static_cast<float>(scale), stream()));
+  }
+
   // out = rank `root`'s `src` on every rank (flat bytes, a multiple of 16).
   void broadcast(torch::Tensor src, std::vector<int64_t> buf_ptrs, torch::Tensor out, int64_t root) {
     TORCH_CHECK(src.is_cuda() && src.is_contiguous() && out.is_contiguous(), "broadcast operands");
@@ -373,6 +392,7 @@ void bind_p2p(pybind11::module& m) {
       .def("return_push", &ExchangeContext::return_push)
       .def("wait_combine", &ExchangeContext::wait_combine)
       .def("allgather", &ExchangeContext::allgather)
+      .def("allreduce_multimem", &ExchangeContext::allreduce_multimem)
       .def("broadcast", &ExchangeContext::broadcast)
       .def("reduce_to_root", &ExchangeContext::reduce_to_root)
       .def("allreduce", &ExchangeContext::allreduce, py::arg("buf_ptrs"), py::arg("out"),

@@ -115,6 +115,16 @@ class SymmWorkspace:
             have = self._buffers[name]
         return have[0], have[1]
 
+    def multicast_ptr(self, name):
+        r"""NVSwitch multicast address of a symmetric buffer (0 when the allocation has none)."""
+        have = self._buffers.get(name)
+        if have is None:
+            return 0
+        try:
+            return int(getattr(have[2], "multicast_ptr", 0) or 0)
+        except Exception:  # pylint: disable=broad-except
+            return 0
+
     # ------------------------------------------------------------------ token budget
     def token_budget(self, n_tokens):
         r"""Tokens per rank that every exchange buffer of this group is sized for.
@@ -514,6 +524,18 @@ def _two_shot(nbytes, world):
     return world > 2 and nbytes >= _AR_TWO_SHOT_BYTES or nbytes >= 8 * _AR_TWO_SHOT_BYTES
 
 
+def _run_allreduce(ws, ptrs, out, n, nbytes, scale):
+    r"""The reduction kernel for a filled "allreduce" buffer: through NVSwitch (``multimem``
+    in-switch reduction) when ``FMOE_USE_NVLS=1`` and the buffer has a multicast mapping, else
+    with plain peer loads / stores (one-shot for small buckets, two-shot from 512 KiB)."""
+    if config.use_nvls() and ws.world > 1:
+        mc = ws.multicast_ptr("allreduce")
+        if mc != 0:
+            ws.ctx.allreduce_multimem(mc, ptrs[ws.me], out, float(scale))
+            return
+    ws.ctx.allreduce(ptrs, out, n, float(scale), _two_shot(nbytes, ws.world))
+
+
 def allreduce_grads(grads, comm, scale, fp32_accumulate=False):  # pylint: disable=unused-argument
     r"""Sum ``grads`` over ``comm`` in place with the peer-to-peer kernels (one-shot for small
     buckets, two-shot from 512 KiB).
@@ -549,7 +571,7 @@ def _allreduce_grads(ws, grads, n, nbytes, dtype, scale):
         offset += g.numel()
     torch._foreach_copy_(views, grads)  # pylint: disable=protected-access
     out = torch.empty(n, dtype=dtype, device=grads[0].device)
-    ws.ctx.allreduce(ptrs, out, n, float(scale), _two_shot(nbytes, ws.world))
+    _run_allreduce(ws, ptrs, out, n, nbytes, scale)
     outs = []
     offset = 0
     for g in grads:
@@ -581,7 +603,7 @@ def allreduce_flat(flat, comm, scale=1.0):
     buf, ptrs = ws.buffer("allreduce", _ar_buffer_bytes(nbytes))
     buf[:nbytes].view(flat.dtype).copy_(flat.reshape(-1))
     out = torch.empty(n, dtype=flat.dtype, device=flat.device)
-    ws.ctx.allreduce(ptrs, out, n, float(scale), _two_shot(nbytes, ws.world))
+    _run_allreduce(ws, ptrs, out, n, nbytes, scale)
     return out
 
 

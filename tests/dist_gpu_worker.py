@@ -343,6 +343,33 @@ def case_allreduce():
         assert native.get().read_status(_dev().index) == 0
 
 
+def case_allreduce_nvls():
+    r"""The NVSwitch (multimem) all-reduce against the collective library; skipped with a note
+    when the symmetric allocation has no multicast mapping on this machine."""
+    rank, world = dist.get_rank(), dist.get_world_size()
+    os.environ["FMOE_USE_NVLS"] = "1"
+    ws = symm.get_workspace(dist.group.WORLD, _dev())
+    ws.buffer("allreduce", 1 << 20)
+    if ws.multicast_ptr("allreduce") == 0:
+        print("no multicast mapping on this machine: NVLS path not exercised")
+        return
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for numel in (1000 * 37 + 5, 2048 * 1537 + 3):
+            torch.manual_seed(200 + rank)
+            flat = torch.randn(numel, device=_dev()).to(dtype)
+            ref = flat.float().clone()
+            dist.all_reduce(ref)
+            got = symm.allreduce_flat(flat, dist.group.WORLD, 1.0 / world)
+            assert got is not None
+            assert torch.allclose(got.float(), ref / world, atol=2e-2, rtol=2e-2), \
+                (dtype, numel, float((got.float() - ref / world).abs().max()))
+            other = got.float().clone()
+            dist.broadcast(other, 0)
+            assert torch.equal(got.float(), other)          # bit-identical on all ranks
+    del os.environ["FMOE_USE_NVLS"]
+    assert native.get().read_status(_dev().index) == 0
+
+
 def case_grouped_ddp():
     rank, world = dist.get_rank(), dist.get_world_size()
     layer = _make_layer(world, rank)

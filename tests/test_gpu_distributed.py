@@ -32,6 +32,13 @@ def test_two_ranks(case):
     assert codes == [0, 0], codes
 
 
+def test_nvls_allreduce():
+    r"""Gradient all-reduce through NVSwitch multimem operations (``FMOE_USE_NVLS=1``)."""
+    _need(2)
+    codes = run_ranks("dist_gpu_worker.py", "allreduce_nvls", 2, timeout=TIMEOUT, extra_env=ENV)
+    assert codes == [0, 0], codes
+
+
 @pytest.mark.parametrize("case", ["fused_vs_general", "oracle", "multi_layer", "allreduce",
                                   "slice_group", "capacity", "smart_schedule"])
 def test_many_ranks(case):
