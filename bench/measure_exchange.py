@@ -111,6 +111,16 @@ def main():
     results["library_path_fwd_bwd"] = timed(fwd_bwd, False)
     os.environ["FMOE_FUSED"] = "1"
 
+    # phases inside the fused dispatch + GEMM kernel (eager launches, %globaltimer stamps)
+    from fastmoe_b200.utils import profiling
+    os.environ["FMOE_EP_TRACE"] = "1"
+    for _ in range(5):
+        flush.zero_()
+        align()
+        fwd()
+    del os.environ["FMOE_EP_TRACE"]
+    phases = profiling.ep_trace_summary()[-1]
+
     rows = n_tok * k                         # rows a rank receives on average
     remote_frac = (world - 1) / world
     link_bytes = 2 * rows * d * 2 * remote_frac            # dispatch + return, per direction the same
@@ -121,6 +131,7 @@ def main():
                           "roofline_fwd_us": roof_fwd,
                           "fused_fwd_over_roofline": roof_fwd / results["fused_fwd"],
                           "link_time_us": link_bytes / LINK_BYTES_PER_S * 1e6,
+                          "dispatch_gemm_phases_rank0": phases,
                           "status": int(nat.read_status(local))}, indent=1))
     dist.barrier()
     dist.destroy_process_group()

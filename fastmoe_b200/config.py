@@ -100,6 +100,13 @@ def nvtx_enabled():
     return switch_from_env("FMOE_NVTX", False)
 
 
+def ep_trace():
+    r"""``FMOE_EP_TRACE=1``: the fused dispatch + GEMM kernel of the expert-parallel forward
+    writes four ``%globaltimer`` stamps per CTA (entry, first rows available, sender done, exit);
+    read them with ``utils.profiling.ep_trace_summary()``."""
+    return switch_from_env("FMOE_EP_TRACE", False)
+
+
 def use_nvls():
     r"""``FMOE_USE_NVLS=1``: gradient all-reduce through NVSwitch (``multimem.ld_reduce`` /
     ``multimem.st`` on the multicast mapping of the symmetric buffer) when the allocation has

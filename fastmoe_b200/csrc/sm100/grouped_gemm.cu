@@ -97,6 +97,7 @@ cudaError_t launch_grouped_gemm(const GroupedGemmArgs& a) {
   kp.push_slots = a.push_slots;
   kp.send = a.send;
   kp.gate = a.gate;
+  kp.trace = a.trace;
   if (a.mode == kWgrad) {
     kp.send.enabled = 0;
     kp.gate.flags = nullptr;

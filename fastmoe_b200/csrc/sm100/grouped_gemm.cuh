@@ -107,6 +107,11 @@ struct GroupedGemmArgs {
   long push_slots = 0;           // rows of every return buffer: rows whose meta names a slot beyond it are skipped
   SendArgs send;
   GateArgs gate;
+  // Optional trace, ten int64 per CTA, zeroed by the caller.  %globaltimer stamps (ns): kernel
+  // entry, first tile's rows available to the TMA producer, sender warp 2 done, kernel exit;
+  // for the first unit of sender warp 2: slot ids loaded, stores issued, fence passed, counted.
+  // Then two counters: ns the producer waited for rows over all tiles, tiles that waited > 1 us.
+  unsigned long long* trace = nullptr;
   int num_sms = 148;
   cudaStream_t stream = nullptr;
 };

@@ -79,10 +79,14 @@ constexpr int PRE_CHUNK_BYTES = 32 * 64;
 constexpr int TMEM_COLS = 512;
 
 // Sender warps (warps 2 and 3 of every CTA): a unit of work is SEND_UNIT_ROWS consecutive
-// destination rows of one 128-row block.
-constexpr int SEND_UNIT_ROWS = 16;
+// destination rows of one 128-row block.  Small units put the first arrival flags up early (the
+// tiles of the first wave all wait for them); SEND_ROWS_IN_FLIGHT rows are loaded before any is
+// stored, which is what bounds a warp's bytes in flight.
+constexpr int SEND_UNIT_ROWS = 8;
+constexpr int SEND_ROWS_IN_FLIGHT = 4;
 constexpr int SEND_UNITS_PER_ITEM = BM / SEND_UNIT_ROWS;
 constexpr int FIRST_SEND_WARP = 2;
+constexpr int TRACE_SLOTS = 10;  // time stamps and counters per CTA when tracing is on
 constexpr int NUM_SEND_WARPS = 2;
 constexpr int NUM_WARPS = FIRST_EPI_WARP + NUM_EPI_WARPS;
 
@@ -141,6 +145,7 @@ struct KernelParams {
   long push_slots;
   SendArgs send;
   GateArgs gate;
+  unsigned long long* trace;
 };
 
 struct TileCoord {
@@ -652,6 +657,9 @@ __device__ __forceinline__ int ld_acquire_sys_i32(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void st_release_gpu_i32(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void st_release_sys_i32(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -703,94 +711,165 @@ __device__ __forceinline__ SendItem send_decode(const SendArgs& s, int tot, int 
   return it;
 }
 
-// One sender warp.  Units are dealt round-robin over all sender warps of the grid; the eight
-// units of an item are therefore in flight on eight different warps at once and the item's
-// flag goes up early.  A row travels global -> registers -> (peer) global, 16 bytes per lane
-// and access, two rows in flight per warp; nothing here waits for anything.
+// The per-expert tables of the send order, one entry per lane (used when world * n_expert <= 32):
+// decoding an item then costs one ballot and a few shuffles instead of a chain of dependent
+// loads in front of every unit.
+struct SendLaneTable {
+  int prefix;   // first item of send-order entry `lane`
+  int seg;      // first row of the expert's segment in the owner's receive buffer
+  int off0;     // index into `pos` of this rank's first slot of the expert
+  int cnt;      // this rank's rows for the expert
+  int rel0;     // segment row of this rank's first row
+  int blkb;     // first flag block of the segment on the owner
+  int peer;
+};
+
+__device__ __forceinline__ SendLaneTable send_lane_table(const SendArgs& s, int tot, int lane) {
+  SendLaneTable t;
+  t.prefix = 0x7fffffff;
+  t.seg = t.off0 = t.cnt = t.rel0 = t.blkb = t.peer = 0;
+  if (lane < tot) {
+    const int g = send_order_expert(s, lane);
+    t.prefix = __ldg(s.item_prefix + lane);
+    t.seg = __ldg(s.seg_base + g);
+    t.off0 = __ldg(s.my_offs + g);
+    t.cnt = __ldg(s.my_offs + g + 1) - t.off0;
+    t.rel0 = __ldg(s.dst_base + g) - t.seg;
+    t.blkb = __ldg(s.blk_base + g);
+    t.peer = g / s.n_expert;
+  }
+  return t;
+}
+
+__device__ __forceinline__ SendItem send_decode_lanes(const SendArgs& s, const SendLaneTable& t, int item) {
+  // entries are in send order and their first items never decrease: the entry of `item` is the
+  // last one whose first item is <= item
+  const int lo = __popc(__ballot_sync(0xffffffffu, t.prefix <= item)) - 1;
+  const int first = __shfl_sync(0xffffffffu, t.prefix, lo);
+  const int seg = __shfl_sync(0xffffffffu, t.seg, lo);
+  const int cnt = __shfl_sync(0xffffffffu, t.cnt, lo);
+  const int rel0 = __shfl_sync(0xffffffffu, t.rel0, lo);
+  SendItem it;
+  it.peer = __shfl_sync(0xffffffffu, t.peer, lo);
+  int r_end = rel0 + cnt;
+  if (r_end > s.capacity - seg) r_end = s.capacity - seg;
+  const int b = rel0 / BM + (item - first);
+  it.blk = __shfl_sync(0xffffffffu, t.blkb, lo) + b;
+  it.r_lo = max(rel0, b * BM);
+  it.r_hi = min(r_end, (b + 1) * BM);
+  it.rel0 = rel0;
+  it.seg = seg;
+  it.src0 = __shfl_sync(0xffffffffu, t.off0, lo);
+  return it;
+}
+
+// One sender warp.  Units are dealt round-robin over all sender warps of the grid; the units of
+// an item are therefore in flight on different warps at once and the item's flag goes up
+// early.  A row travels global -> registers -> (peer) global, 16 bytes per lane and access,
+// SEND_ROWS_IN_FLIGHT rows at a time; nothing here waits for anything.
 template <typename T>
 __device__ __forceinline__ void sender_warp(const KernelParams& p, int sender_id, int n_senders,
-                                            int lane) {
+                                            int lane, unsigned long long* stamps) {
   const SendArgs& s = p.send;
+  constexpr int R = SEND_ROWS_IN_FLIGHT;
+  // `stamps` (tracing, one warp per CTA): when the warp's first unit had its slot ids, had issued
+  // its stores, had passed the fence, had counted / signalled
+  int stamp_at = (stamps != nullptr && lane == 0) ? 0 : 4;
+  auto stamp = [&]() {
+    if (stamp_at < 4) stamps[stamp_at++] = ptx::globaltimer();
+  };
   const int tot = s.world * s.n_expert;
   const int total_items = __ldg(s.item_prefix + tot);
   const int total_units = total_items * SEND_UNITS_PER_ITEM;
   const int epoch = *s.epoch;
   const int nv = s.d >> 3;                    // 16-byte pieces per row
   const bool scaled = s.scale != nullptr;
+  const bool lanes_hold_tables = tot <= 32;
+  SendLaneTable table;
+  if (lanes_hold_tables) table = send_lane_table(s, tot, lane);
   for (int u = sender_id; u < total_units; u += n_senders) {
     const int item = u / SEND_UNITS_PER_ITEM;
-    const SendItem it = send_decode(s, tot, item);
+    const SendItem it = lanes_hold_tables ? send_decode_lanes(s, table, item) : send_decode(s, tot, item);
     const int r0 = it.r_lo + (u - item * SEND_UNITS_PER_ITEM) * SEND_UNIT_ROWS;
     const int r1 = min(r0 + SEND_UNIT_ROWS, it.r_hi);
     if (r0 >= r1) continue;
-    // lanes 0..15 fetch the slot ids (and scales) of the unit's rows with one load
+    // the first lanes fetch the slot ids (and scales) of the unit's rows with one load
     int slot_of = -1;
     float scale_of = 1.f;
+    T* dst_rows = static_cast<T*>(s.rows.p[it.peer]);
+    int64_t* dst_meta = static_cast<int64_t*>(s.meta.p[it.peer]);
     if (r0 + lane < r1) {
       slot_of = __ldg(s.pos + it.src0 + (r0 + lane - it.rel0));
       if (scaled) scale_of = Cvt<T>::to_f(static_cast<const T*>(s.scale)[slot_of]);
+      if (dst_meta != nullptr) {
+        dst_meta[it.seg + r0 + lane] = (static_cast<int64_t>(s.me) << 32) | static_cast<int64_t>(slot_of);
+      }
     }
-    T* dst_rows = static_cast<T*>(s.rows.p[it.peer]);
-    int64_t* dst_meta = static_cast<int64_t*>(s.meta.p[it.peer]);
-    for (int r = r0; r < r1; r += 2) {
-      const bool two = r + 1 < r1;
-      const int sl0 = __shfl_sync(0xffffffffu, slot_of, r - r0);
-      const int sl1 = __shfl_sync(0xffffffffu, slot_of, two ? r + 1 - r0 : r - r0);
-      const float sc0 = __shfl_sync(0xffffffffu, scale_of, r - r0);
-      const float sc1 = __shfl_sync(0xffffffffu, scale_of, two ? r + 1 - r0 : r - r0);
-      const uint4* in0 = reinterpret_cast<const uint4*>(static_cast<const T*>(s.x) + static_cast<long>(sl0 / s.k) * s.d);
-      const uint4* in1 = reinterpret_cast<const uint4*>(static_cast<const T*>(s.x) + static_cast<long>(sl1 / s.k) * s.d);
-      uint4* out0 = reinterpret_cast<uint4*>(dst_rows + (it.seg + r) * s.d);
-      uint4* out1 = reinterpret_cast<uint4*>(dst_rows + (it.seg + r + 1) * s.d);
+    if (stamp_at == 0) stamp();
+    for (int r = r0; r < r1; r += R) {
+      const uint4* in[R];
+      uint4* out[R];
+      float sc[R];
+      bool on[R];
+#pragma unroll
+      for (int t = 0; t < R; ++t) {
+        on[t] = r + t < r1;
+        const int from = on[t] ? r + t - r0 : r - r0;
+        const int sl = __shfl_sync(0xffffffffu, slot_of, from);
+        sc[t] = __shfl_sync(0xffffffffu, scale_of, from);
+        in[t] = reinterpret_cast<const uint4*>(static_cast<const T*>(s.x) + static_cast<long>(sl / s.k) * s.d);
+        out[t] = reinterpret_cast<uint4*>(dst_rows + (it.seg + r + t) * s.d);
+      }
       for (int i0 = lane; i0 < nv; i0 += 128) {
-        uint4 v0[4], v1[4];
+        uint4 v[R][4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           if (i0 + q * 32 < nv) {
-            v0[q] = __ldg(in0 + i0 + q * 32);
-            if (two) v1[q] = __ldg(in1 + i0 + q * 32);
+#pragma unroll
+            for (int t = 0; t < R; ++t) {
+              if (on[t]) v[t][q] = __ldg(in[t] + i0 + q * 32);
+            }
           }
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           if (i0 + q * 32 < nv) {
-            if (scaled) {
-              uint32_t* w0 = reinterpret_cast<uint32_t*>(&v0[q]);
-              uint32_t* w1 = reinterpret_cast<uint32_t*>(&v1[q]);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float a, b;
-                Cvt<T>::unpack(w0[j], a, b);
-                w0[j] = Cvt<T>::pack(a * sc0, b * sc0);
-                if (two) {
-                  Cvt<T>::unpack(w1[j], a, b);
-                  w1[j] = Cvt<T>::pack(a * sc1, b * sc1);
+            for (int t = 0; t < R; ++t) {
+              if (!on[t]) continue;
+              if (scaled) {
+                uint32_t* w = reinterpret_cast<uint32_t*>(&v[t][q]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float a, b;
+                  Cvt<T>::unpack(w[j], a, b);
+                  w[j] = Cvt<T>::pack(a * sc[t], b * sc[t]);
                 }
               }
+              out[t][i0 + q * 32] = v[t][q];
             }
-            out0[i0 + q * 32] = v0[q];
-            if (two) out1[i0 + q * 32] = v1[q];
           }
         }
       }
-      if (dst_meta != nullptr && lane < (two ? 2 : 1)) {
-        dst_meta[it.seg + r + lane] =
-            (static_cast<int64_t>(s.me) << 32) | static_cast<int64_t>(lane == 0 ? sl0 : sl1);
-      }
     }
-    // Every lane orders its own stores at system scope; lane 0 then counts the unit's rows.
-    // The warp that completes the item clears the counter and raises the flag on the owner.
-    __threadfence_system();
+    // Every lane orders its own stores, lane 0 then counts the unit's rows; the warp that
+    // completes the item clears the counter and raises the flag on the owner.  Rows that stay
+    // on this GPU need device scope only (writer and reader are both here); a system-scope
+    // fence costs far more and is kept for rows that went to a peer.
+    const bool local = it.peer == s.me;
+    if (stamp_at == 1) stamp();
+    if (local) __threadfence(); else __threadfence_system();
     __syncwarp();
+    if (stamp_at == 2) stamp();
     if (lane == 0) {
       const int n = r1 - r0;
       const int old = atomicAdd(s.item_count + item, n);
       if (old + n == it.r_hi - it.r_lo) {
         s.item_count[item] = 0;
-        __threadfence_system();
         int* flag = static_cast<int*>(s.flags.p[it.peer]) + static_cast<long>(it.blk) * kMaxPeers + s.me;
-        st_release_sys_i32(flag, epoch);
+        if (local) st_release_gpu_i32(flag, epoch); else st_release_sys_i32(flag, epoch);
       }
+      if (stamp_at == 3) stamp();
     }
   }
 }
@@ -815,6 +894,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   // ---------------------------------------------------------------- set-up
   if (threadIdx.x == 0) {
+    if (p.trace != nullptr) p.trace[cta * TRACE_SLOTS + 0] = ptx::globaltimer();
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(&aux->full[s], 1);
       ptx::mbar_init(&aux->empty[s], 1);
@@ -895,6 +975,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           flag_next = gate_flag(tile + num_ctas);
           seen_next = flag_next != nullptr ? ld_acquire_sys_i32(flag_next) : gate_epoch;
           bool here = true;
+          const unsigned long long wait_from = p.trace != nullptr ? ptx::globaltimer() : 0ull;
           if (flag != nullptr && seen - gate_epoch < 0) {
             const unsigned long long t0 = ptx::globaltimer();
             unsigned spins = 0;
@@ -920,6 +1001,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
           }
           // the rows were written by other GPUs and are now read through the async proxy
           ptx::fence_proxy_async_all();
+          if (p.trace != nullptr && lane == 0) {
+            const unsigned long long now = ptx::globaltimer();
+            if (tile == cta) p.trace[cta * TRACE_SLOTS + 1] = now;
+            // time the producer spent waiting for rows, all tiles, and how many tiles waited
+            p.trace[cta * TRACE_SLOTS + 8] += now - wait_from;
+            if (now - wait_from > 1000ull) p.trace[cta * TRACE_SLOTS + 9] += 1ull;
+          }
         }
       }
       for (int kb = 0; kb < num_kb; ++kb) {
@@ -1039,7 +1127,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
     // ============================================================== sender warps (2, 3)
     if constexpr (MODE != kWgrad) {
       if (p.send.enabled) {
-        sender_warp<T>(p, cta * NUM_SEND_WARPS + (warp - FIRST_SEND_WARP), num_ctas * NUM_SEND_WARPS, lane);
+        sender_warp<T>(p, cta * NUM_SEND_WARPS + (warp - FIRST_SEND_WARP), num_ctas * NUM_SEND_WARPS, lane,
+                       (p.trace != nullptr && warp == FIRST_SEND_WARP) ? p.trace + cta * TRACE_SLOTS + 4 : nullptr);
+        if (p.trace != nullptr && lane == 0 && warp == FIRST_SEND_WARP) {
+          p.trace[cta * TRACE_SLOTS + 2] = ptx::globaltimer();
+        }
       }
     }
   } else {
@@ -1263,6 +1355,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[cta * TRACE_SLOTS + 3] = ptx::globaltimer();
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);

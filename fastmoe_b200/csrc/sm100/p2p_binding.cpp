@@ -257,7 +257,8 @@ class ExchangeContext {
                c10::optional<torch::Tensor> pre_out, c10::optional<torch::Tensor> aux, int64_t act,
                int64_t epi, c10::optional<torch::Tensor> push_meta, std::vector<int64_t> ret_ptrs,
                int64_t push_slots, c10::optional<pybind11::dict> send,
-               std::vector<int64_t> gate_flag_ptrs, c10::optional<torch::Tensor> seg_off) {
+               std::vector<int64_t> gate_flag_ptrs, c10::optional<torch::Tensor> seg_off,
+               c10::optional<torch::Tensor> trace) {
     c10::cuda::CUDAGuard guard(a.device());
     TORCH_CHECK(mode == fmoe::kRowsNT || mode == fmoe::kRowsNN, "gemm_ep: row modes only");
     TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && offs.scalar_type() == torch::kInt,
@@ -342,6 +343,12 @@ class ExchangeContext {
       g.gate.me = ctx_.me;
       g.gate.timeout_ns = ctx_.timeout_ns;
     }
+    if (trace.has_value() && trace->defined()) {
+      TORCH_CHECK(trace->scalar_type() == torch::kLong && trace->is_cuda() &&
+                      trace->numel() >= static_cast<int64_t>(sms) * 10,
+                  "gemm_ep: trace must be a zeroed int64 CUDA tensor of 10 entries per SM");
+      g.trace = reinterpret_cast<unsigned long long*>(trace->data_ptr<int64_t>());
+    }
     g.stream = stream();
     TORCH_CHECK(fmoe::grouped_gemm_supported(g.mode, 0, g.n, g.k, g.num_groups),
                 "gemm_ep: shape not supported by the tcgen05 kernel");
@@ -403,7 +410,7 @@ void bind_p2p(pybind11::module& m) {
            py::arg("epi") = 0, py::arg("push_meta") = py::none(),
            py::arg("ret_ptrs") = std::vector<int64_t>(), py::arg("push_slots") = 0,
            py::arg("send") = py::none(), py::arg("gate_flag_ptrs") = std::vector<int64_t>(),
-           py::arg("seg_off") = py::none())
+           py::arg("seg_off") = py::none(), py::arg("trace") = py::none())
       .def("wait_only", &ExchangeContext::wait_only);
   m.def("slot_dot", &slot_dot);
   m.attr("P2P_CHAN_COUNTS") = fmoe::kChanCounts;

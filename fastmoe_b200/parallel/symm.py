@@ -47,7 +47,7 @@ from torch.autograd import Function
 
 from .. import config
 from ..ops import native
-from ..utils.profiling import fused_range
+from ..utils.profiling import fused_range, new_ep_trace
 
 _WORKSPACES = {}
 _FAILED = set()
@@ -412,7 +412,8 @@ class _FusedEPMLP(Function):
             pre = gg.pre_buffer(capacity, h, n_expert, x.dtype, dev) if code != 0 else a
             ws.ctx.gemm_ep(gg.MODE_NT, xs, w1, tb.expert_offs, out=a, bias=b1,
                            pre_out=pre if code != 0 else None, act=code, send=send,
-                           gate_flag_ptrs=flag_ptrs, seg_off=tb.seg_off)
+                           gate_flag_ptrs=flag_ptrs, seg_off=tb.seg_off,
+                           trace=new_ep_trace(dev) if config.ep_trace() else None)
         with fused_range("ep.gemm2_push_combine"):
             n_slots_cap = budget * k
             stage_ret, ret_ptrs = ws.buffer("ret", n_slots_cap * d * es)

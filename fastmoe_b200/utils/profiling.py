@@ -40,6 +40,69 @@ def fused_range(name):
         yield
 
 
+_ep_traces = []
+EP_TRACE_SLOTS = 10
+_EP_TRACE_KEEP = 64
+
+
+def new_ep_trace(device):
+    r"""A zeroed trace buffer (ten int64 per SM) for one launch of the fused dispatch + GEMM
+    kernel; the last ``64`` buffers are kept for :func:`ep_trace_summary`."""
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    buf = torch.zeros(sms * EP_TRACE_SLOTS, dtype=torch.int64, device=device)
+    _ep_traces.append(buf)
+    del _ep_traces[:-_EP_TRACE_KEEP]
+    return buf
+
+
+def summarize_ep_trace(stamps):
+    r"""Phase durations in microseconds from one trace buffer (``[ctas, 10]``: nanosecond stamps
+    entry, first rows available, sender done, exit, then for the first unit of the CTA's first
+    sender warp: slot ids loaded, stores issued, fence passed, rows counted; 0 = the CTA never
+    reached that phase; then the nanoseconds the TMA producer waited for rows over all its tiles
+    and the number of tiles that waited more than a microsecond).
+
+    ``launch_skew``: latest entry − earliest entry; ``first_rows``: how long CTAs waited for the
+    rows of their first tile (median, max); ``sender``: entry → last sender warp done (max);
+    ``kernel``: earliest entry → latest exit; ``first_unit``: medians over CTAs, from CTA entry;
+    ``rows_wait``: producer wait per CTA summed over its tiles (median, max) and tiles that waited.
+    """
+    t = stamps.reshape(-1, EP_TRACE_SLOTS).cpu().double()
+    ran = t[:, 0] > 0
+    if not bool(ran.any()):
+        return None
+    t = t[ran]
+    start = float(t[:, 0].min())
+    out = {"ctas": int(t.shape[0]),
+           "launch_skew_us": (float(t[:, 0].max()) - start) / 1e3,
+           "kernel_us": (float(t[:, :4].max()) - start) / 1e3}
+    gated = t[:, 1] > 0
+    if bool(gated.any()):
+        wait = (t[gated, 1] - t[gated, 0]) / 1e3
+        out["first_rows_us"] = {"median": float(wait.median()), "max": float(wait.max())}
+        out["rows_wait_us"] = {"median": float(t[gated, 8].median()) / 1e3, "max": float(t[gated, 8].max()) / 1e3,
+                               "tiles_waited": int(t[gated, 9].sum())}
+    sent = t[:, 2] > 0
+    if bool(sent.any()):
+        out["sender_us"] = (float(t[sent, 2].max()) - start) / 1e3
+    unit = t[:, 7] > 0
+    if bool(unit.any()):
+        rel = (t[unit, 4:8] - t[unit, 0:1]) / 1e3
+        med = rel.median(dim=0).values
+        out["first_unit_us"] = {"ids_loaded": float(med[0]), "stores_issued": float(med[1]),
+                                "fenced": float(med[2]), "counted": float(med[3])}
+    return out
+
+
+def ep_trace_summary(clear=True):
+    r"""Summaries of the launches traced under ``FMOE_EP_TRACE=1`` (oldest first).  Synchronises."""
+    torch.cuda.synchronize()
+    out = [s for s in (summarize_ep_trace(b) for b in _ep_traces) if s is not None]
+    if clear:
+        _ep_traces.clear()
+    return out
+
+
 def check_routing(idx, rank, counts, tot_expert, offs=None, capacity=None):
     r"""Host-side validation of a routing table (``FMOE_DEBUG_BOUNDS=1``); raises ``ValueError``.
 

@@ -142,6 +142,19 @@ def case_oracle():
         gy = torch.randn(n_tok, d, device=_dev(), dtype=dtype)
         assert symm.fused_available(layer, x), "fused path unavailable"
         _oracle_check(layer, x, gy, world, rank, tol)
+    # the in-kernel time stamps of the fused dispatch + GEMM launch
+    from fastmoe_b200.utils import profiling
+    os.environ["FMOE_EP_TRACE"] = "1"
+    with torch.no_grad():
+        layer(x)
+    del os.environ["FMOE_EP_TRACE"]
+    traced = profiling.ep_trace_summary()
+    assert len(traced) == 1, traced
+    t = traced[0]
+    assert t["ctas"] >= 1 and 0 < t["kernel_us"] < 1e6, t
+    assert 0 <= t["launch_skew_us"] <= t["kernel_us"], t
+    assert t["sender_us"] <= t["kernel_us"] and t["first_rows_us"]["max"] <= t["kernel_us"], t
+    assert 0 < t["first_unit_us"]["ids_loaded"] <= t["first_unit_us"]["counted"] <= t["kernel_us"], t
 
 
 def case_uneven_tokens():
@@ -583,6 +596,55 @@ def case_swipe_device():
     dist.all_reduce(loads)
     assert float(loads.max()) <= 256 * 2 + 1e-3      # no worker takes more than B * top_k tokens
     assert native.get().read_status(_dev().index) == 0
+
+
+def case_pipeline_gpu():
+    r"""Pipeline parallelism on GPUs: the 1F1B runner with one stage per GPU (NCCL send / recv
+    between stages, the fused single-GPU MoE kernels inside a stage, bf16) against the same
+    model run in one process."""
+    from fastmoe_b200.parallel.pipeline import PipelineRunner, build_stage_groups
+    rank, world = dist.get_rank(), dist.get_world_size()
+    n_stages, n_micro, tokens, d, h, n_exp, blocks = world, 3, 128, 256, 512, 2, 2
+    stage, group, prev_rank, next_rank = build_stage_groups(n_stages)
+    dev = _dev()
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = nn.Linear(d, d)
+            self.moe = FMoETransformerMLP(num_expert=n_exp, d_model=d, d_hidden=h, top_k=2, world_size=1)
+
+        def forward(self, x):
+            return x + self.moe(torch.tanh(self.lin(x)))
+
+    torch.manual_seed(17)
+    full = nn.Sequential(*[Block() for _ in range(n_stages * blocks)]).to(dev).to(torch.bfloat16)
+    mine = nn.Sequential(*[Block() for _ in range(blocks)]).to(dev).to(torch.bfloat16)
+    refs = list(full)[stage * blocks:(stage + 1) * blocks]
+    for b, ref in zip(mine, refs):
+        b.load_state_dict(ref.state_dict())
+    gen = torch.Generator().manual_seed(300)
+    xs = [torch.randn(tokens, d, generator=gen).to(dev).to(torch.bfloat16) for _ in range(n_micro)]
+    ts = [torch.randn(tokens, d, generator=gen).to(dev).to(torch.bfloat16) for _ in range(n_micro)]
+
+    def mse(out, target):
+        return (out.float() - target.float()).pow(2).mean()
+
+    runner = PipelineRunner(mine, stage, n_stages, prev_rank, next_rank, (tokens, d), torch.bfloat16,
+                            loss_fn=mse, device=dev)
+    loss = runner.run(micro_batches=xs if stage == 0 else None,
+                      targets=ts if stage == n_stages - 1 else None, n_micro=n_micro)
+    total = 0.0
+    for x, t in zip(xs, ts):
+        total = total + mse(full(x), t) / n_micro
+    total.backward()
+    if stage == n_stages - 1:
+        assert abs(float(loss) - float(total)) <= 2e-2 * abs(float(total)) + 1e-3, (float(loss), float(total))
+    for b, ref in zip(mine, refs):
+        for (name, p), (_n, q) in zip(b.named_parameters(), ref.named_parameters()):
+            err = float((p.grad.float() - q.grad.float()).abs().max())
+            assert err <= 0.06 * float(q.grad.float().abs().max()) + 2e-3, (name, err)
+    assert native.get().read_status(dev.index) == 0
 
 
 def case_graph_step():

@@ -313,6 +313,30 @@ def test_debug_routing_check_and_nvtx_switch(monkeypatch):
     assert config.debug_bounds()
 
 
+def test_ep_trace_summary_arithmetic(monkeypatch):
+    r"""The phase summary of the in-kernel time stamps: CTAs that never ran are ignored, phases a
+    CTA never reached (stamp 0) do not enter the statistics."""
+    from fastmoe_b200 import config
+    from fastmoe_b200.utils.profiling import summarize_ep_trace
+    stamps = torch.tensor([[1000, 3000, 9000, 20000, 1500, 2000, 4000, 5000, 6000, 2],
+                           [2000, 2500, 0, 21000, 0, 0, 0, 0, 4000, 1],
+                           [1500, 0, 0, 19000, 0, 0, 0, 0, 0, 0],
+                           [0, 0, 0, 0, 0, 0, 0, 0, 0, 0]])
+    got = summarize_ep_trace(stamps.reshape(-1))
+    assert got["ctas"] == 3
+    assert got["launch_skew_us"] == pytest.approx(1.0)
+    assert got["kernel_us"] == pytest.approx(20.0)
+    assert got["first_rows_us"]["max"] == pytest.approx(2.0)
+    assert got["sender_us"] == pytest.approx(8.0)
+    assert got["rows_wait_us"] == {"median": pytest.approx(4.0), "max": pytest.approx(6.0), "tiles_waited": 3}
+    assert got["first_unit_us"] == {"ids_loaded": pytest.approx(0.5), "stores_issued": pytest.approx(1.0),
+                                    "fenced": pytest.approx(3.0), "counted": pytest.approx(4.0)}
+    assert summarize_ep_trace(torch.zeros(20, dtype=torch.long)) is None
+    assert not config.ep_trace()
+    monkeypatch.setenv("FMOE_EP_TRACE", "1")
+    assert config.ep_trace()
+
+
 def test_async_gradient_allreduce_handle_without_gpu():
     r"""``allreduce_gradients(async_op=True)`` returns a handle on every device; without CUDA the
     reduction has already happened when it returns."""

@@ -24,7 +24,7 @@ def _need(world):
 
 
 @pytest.mark.parametrize("case", ["fused_vs_general", "oracle", "uneven_tokens", "multi_layer",
-                                  "recv_overflow", "shadow_fused", "swipe_device", "allreduce", "grouped_ddp", "wait_timeout",
+                                  "recv_overflow", "shadow_fused", "swipe_device", "pipeline_gpu", "allreduce", "grouped_ddp", "wait_timeout",
                                   "graph_step", "smart_schedule", "slice_group", "capacity"])
 def test_two_ranks(case):
     _need(2)
