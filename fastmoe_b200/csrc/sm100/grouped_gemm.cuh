@@ -60,6 +60,9 @@ struct SendArgs {
 struct GateArgs {
   const int* flags = nullptr;     // local int32 [blocks][kMaxPeers]; null = not gated
   const int* seg_off = nullptr;   // [num_groups][world + 1] row where the rows of the j-th source begin
+  // Optional: the (group, 128-row block) pairs of the problem in the order the tiles are to be
+  // walked, (group << 20) | block — every pair exactly once.  Null = groups in order.
+  const int* blk_order = nullptr;
   const int* epoch = nullptr;
   int world = 1;
   int me = 0;

@@ -86,6 +86,7 @@ constexpr int SEND_UNIT_ROWS = 8;
 constexpr int SEND_ROWS_IN_FLIGHT = 4;
 constexpr int SEND_UNITS_PER_ITEM = BM / SEND_UNIT_ROWS;
 constexpr int FIRST_SEND_WARP = 2;
+constexpr int BLK_ORDER_SHIFT = 20;   // (group << 20) | block, as written by the count exchange
 constexpr int TRACE_SLOTS = 10;  // time stamps and counters per CTA when tracing is on
 constexpr int NUM_SEND_WARPS = 2;
 constexpr int NUM_WARPS = FIRST_EPI_WARP + NUM_EPI_WARPS;
@@ -166,21 +167,40 @@ __device__ __forceinline__ int tiles_of_group(const KernelParams& p, int rows) {
 template <int MODE>
 __device__ __forceinline__ TileCoord decode_tile(const KernelParams& p, const SharedAux* aux,
                                                  int tile) {
+  TileCoord c;
+  const int n_tiles = (p.n + BN - 1) / BN;
+  if (MODE != kWgrad && p.gate.blk_order != nullptr) {
+    // Row blocks in the order given by the caller (arrival order under expert parallelism).
+    const int i = tile / n_tiles;
+    const int packed = __ldg(p.gate.blk_order + i);
+    c.group = min(packed >> BLK_ORDER_SHIFT, p.num_groups - 1);
+    c.m_tile = packed & ((1 << BLK_ORDER_SHIFT) - 1);
+    c.n_tile = tile - i * n_tiles;
+    c.row_begin = p.offs[c.group];
+    c.row_end = p.offs[c.group + 1];
+    return c;
+  }
   // Binary search of the group whose tile range contains `tile`.
   int lo = 0, hi = p.num_groups;
   while (hi - lo > 1) {
     int mid = (lo + hi) >> 1;
     if (aux->tile_prefix[mid] <= tile) lo = mid; else hi = mid;
   }
-  TileCoord c;
   c.group = lo;
   const int local = tile - aux->tile_prefix[lo];
-  const int n_tiles = (p.n + BN - 1) / BN;
   c.m_tile = local / n_tiles;
   c.n_tile = local - c.m_tile * n_tiles;
   c.row_begin = p.offs[lo];
   c.row_end = p.offs[lo + 1];
   return c;
+}
+
+// Where a tile's block of the tile-blocked pre-activation lives: groups in order, whatever
+// order the tiles are walked in.
+__device__ __forceinline__ long pre_tile_index(const KernelParams& p, const SharedAux* aux,
+                                               const TileCoord& c) {
+  const int n_tiles = (p.n + BN - 1) / BN;
+  return static_cast<long>(aux->tile_prefix[c.group]) + c.m_tile * n_tiles + c.n_tile;
 }
 
 // GELU pieces in about 14 instructions.  Phi(x) = 0.5 (1 + erf(x / sqrt 2)) with erf from
@@ -676,12 +696,13 @@ struct SendItem {
   int src0;     // index into `pos` of this rank's first slot of the expert
 };
 
-// Send order: local expert e outer, peer distance j inner (j = 0 is this rank itself), so
-// that every receiver gets the rows of its first experts first, from all sources at once.
-// The count-exchange kernel builds `item_prefix` in the same order.
+// Send order: peer distance j outer (j = 0 is this rank itself), local expert e inner — first
+// everything that stays on this GPU, then the rows of the next rank, and so on; receivers walk
+// their tiles in the matching order.  The count-exchange kernel builds `item_prefix` in the
+// same order.
 __device__ __forceinline__ int send_order_expert(const SendArgs& s, int q) {
-  const int e = q / s.world;
-  const int j = q - e * s.world;
+  const int j = q / s.n_expert;
+  const int e = q - j * s.n_expert;
   int peer = s.me + j;
   if (peer >= s.world) peer -= s.world;
   return peer * s.n_expert + e;
@@ -1279,9 +1300,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         // The saved pre-activation is tile-blocked: this warp's four chunks of this tile.
         if (use_aux) {
           rt.pre_tile = const_cast<uint8_t*>(static_cast<const uint8_t*>(p.aux)) +
-                        static_cast<long>(tile) * PRE_TILE_BYTES + ew * (CHUNKS_PER_WARP * PRE_CHUNK_BYTES);
+                        pre_tile_index(p, aux, c) * PRE_TILE_BYTES + ew * (CHUNKS_PER_WARP * PRE_CHUNK_BYTES);
         } else if (p.pre_out != nullptr) {
-          rt.pre_tile = static_cast<uint8_t*>(p.pre_out) + static_cast<long>(tile) * PRE_TILE_BYTES +
+          rt.pre_tile = static_cast<uint8_t*>(p.pre_out) + pre_tile_index(p, aux, c) * PRE_TILE_BYTES +
                         ew * (CHUNKS_PER_WARP * PRE_CHUNK_BYTES);
         }
         // It does not depend on the accumulator: fetch the first chunk before waiting for the
@@ -1290,7 +1311,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (use_aux && n_chunks > 0) {
           load_pre_chunk(rt.pre_tile, 0, lane, side_first);
           if (tile + num_ctas < total_tiles) {
-            const uint8_t* nx = rt.pre_tile + static_cast<long>(num_ctas) * PRE_TILE_BYTES + lane * 256;
+            const TileCoord cn = decode_tile<MODE>(p, aux, tile + num_ctas);
+            const uint8_t* nx = static_cast<const uint8_t*>(p.aux) + pre_tile_index(p, aux, cn) * PRE_TILE_BYTES +
+                                ew * (CHUNKS_PER_WARP * PRE_CHUNK_BYTES) + lane * 256;
             asm volatile("prefetch.global.L2 [%0];" ::"l"(nx));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + 128));
           }

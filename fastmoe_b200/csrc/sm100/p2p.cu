@@ -92,8 +92,11 @@ __device__ __forceinline__ bool last_block(int* counter) {
 // ------------------------------------------------------------------------------ counts
 // Receive layout on every rank p: local expert outer; inside an expert segment the rows of
 // source rank w sit at position (p - w) mod world — the rank's own rows first, then those of
-// rank p - 1, p - 2, ...  A sender serves its peers in the order me, me + 1, me + 2, ..., so a
-// receiver's rows arrive roughly in the order in which its GEMM reads them.
+// rank p - 1, p - 2, ...  A sender serves its peers in the order me, me + 1, me + 2, ... (peer
+// distance outer, expert inner), and `blk_order` lists the receiver's 128-row blocks in the
+// matching order — by the source position of a block's last row, then expert, then row — so
+// that a GEMM which walks its tiles through that table reads rows in the order they arrive:
+// first everything that never left the GPU, then what the nearest source sent, and so on.
 __device__ __forceinline__ int source_position(int owner, int src, int world) {
   int j = owner - src;
   return j < 0 ? j + world : j;
@@ -104,8 +107,9 @@ count_exchange_kernel(const __grid_constant__ ExchangeCtx c, const int* __restri
                       int capacity_rows, int* __restrict__ dst_base, int* __restrict__ seg_base,
                       int* __restrict__ blk_base, int* __restrict__ expert_offs,
                       int* __restrict__ seg_off, int* __restrict__ total_rows,
-                      int* __restrict__ item_prefix) {
-  extern __shared__ int sh[];  // [world * width] matrix, [tot] column sums, [tot] items per pair
+                      int* __restrict__ item_prefix, int* __restrict__ blk_order) {
+  extern __shared__ int sh[];  // [world * width] matrix, [tot] column sums, [tot] items per pair,
+                               // [tot] first block and [tot + 1] block prefix per (position, expert)
   const int tot = n_expert * c.world;
   const int width = tot + 1;   // a rank's row: its counts, then its receive capacity
   const int epoch = c.epoch[0] + 1;
@@ -161,7 +165,7 @@ count_exchange_kernel(const __grid_constant__ ExchangeCtx c, const int* __restri
     if (cnt_mine > 0 && r_end > before) items = (r_end - 1) / kRowBlock - before / kRowBlock + 1;
     int j = p - c.me;
     if (j < 0) j += c.world;
-    col[tot + e * c.world + j] = items;
+    col[tot + j * n_expert + e] = items;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -191,6 +195,40 @@ count_exchange_kernel(const __grid_constant__ ExchangeCtx c, const int* __restri
       expert_offs[n_expert] = end;
       total_rows[0] = end;
     }
+  }
+  // 5. my row blocks in the order their rows arrive.  Blocks of expert e whose last row comes
+  // from position j are consecutive: with f(t) = number of blocks whose last row is below t,
+  // they are [f(s_j), f(s_j+1)), s_j being where position j starts inside the segment.
+  __syncthreads();
+  int* ord_lo = col + 2 * tot;
+  int* ord_prefix = col + 3 * tot;
+  for (int q = threadIdx.x; q < tot; q += blockDim.x) {
+    const int j = q / n_expert;
+    const int e = q - j * n_expert;
+    const int* so = seg_off + e * (c.world + 1);
+    const int n_e = so[c.world] - so[0];
+    const int n_blk = (n_e + kRowBlock - 1) / kRowBlock;
+    const int s_lo = so[j] - so[0];
+    const int s_hi = so[j + 1] - so[0];
+    const int f_lo = s_lo >= n_e ? n_blk : s_lo / kRowBlock;
+    const int f_hi = s_hi >= n_e ? n_blk : s_hi / kRowBlock;
+    ord_lo[q] = f_lo;
+    ord_prefix[q + 1] = f_hi - f_lo;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    ord_prefix[0] = 0;
+    for (int q = 0; q < tot; ++q) {
+      run += ord_prefix[q + 1];
+      ord_prefix[q + 1] = run;
+    }
+  }
+  __syncthreads();
+  for (int q = threadIdx.x; q < tot; q += blockDim.x) {
+    const int e = q % n_expert;
+    const int n = ord_prefix[q + 1] - ord_prefix[q];
+    for (int t = 0; t < n; ++t) blk_order[ord_prefix[q] + t] = (e << kBlkOrderShift) | (ord_lo[q] + t);
   }
   // Overflow anywhere is visible to everybody (same matrix): report it on every rank.  So is a
   // peer that sized its receive buffer differently: senders clamp against THEIR capacity, so
@@ -844,9 +882,12 @@ int push_grid(int work_items, int warps_per_block) {
 cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const PeerPtrs& cnt,
                                   int n_expert, int capacity_rows, int* dst_base, int* seg_base,
                                   int* blk_base, int* expert_offs, int* seg_off, int* total_rows,
-                                  int* item_prefix, cudaStream_t stream) {
+                                  int* item_prefix, int* blk_order, cudaStream_t stream) {
   const int tot = n_expert * ctx.world;
-  const size_t smem = (static_cast<size_t>(ctx.world) * (tot + 1) + 2 * tot) * sizeof(int);
+  if (n_expert >= (1 << (31 - kBlkOrderShift)) || capacity_rows / kRowBlock >= (1 << kBlkOrderShift)) {
+    return cudaErrorInvalidValue;
+  }
+  const size_t smem = (static_cast<size_t>(ctx.world) * (tot + 1) + 4 * tot + 1) * sizeof(int);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(count_exchange_kernel,
@@ -855,7 +896,7 @@ cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const 
   }
   count_exchange_kernel<<<1, 1024, smem, stream>>>(ctx, lec, cnt, n_expert, capacity_rows, dst_base,
                                                    seg_base, blk_base, expert_offs, seg_off,
-                                                   total_rows, item_prefix);
+                                                   total_rows, item_prefix, blk_order);
   return cudaGetLastError();
 }
 

@@ -25,6 +25,8 @@ constexpr int kStatusCapacityMismatch = 203; // the ranks of a group sized their
 // Arrival of dispatched rows is tracked per block of this many rows of the receive buffer
 // (the M extent of a GEMM tile).
 constexpr int kRowBlock = 128;
+// An entry of the block-order table: (local expert << kBlkOrderShift) | block inside the expert.
+constexpr int kBlkOrderShift = 20;
 
 // Flag channels inside the symmetric signal buffer: int32 [kNumChannels][kMaxPeers].
 constexpr int kChanCounts = 0;
@@ -60,12 +62,14 @@ struct ExchangeCtx {
 //                       (source j is rank (me - j) mod world)
 //   total_rows[1]
 //   item_prefix[tot + 1]  exclusive prefix of the number of kRowBlock-row blocks my rows touch
-//                       on the owner, per (expert, peer) pair in send order: local expert e
-//                       outer, peer distance j inner, global expert ((me + j) mod world) * E + e
+//                       on the owner, per (peer, expert) pair in send order: peer distance j
+//                       outer, local expert e inner, global expert ((me + j) mod world) * E + e
+//   blk_order[capacity / kRowBlock + E]  my kRowBlock-row blocks in the order their rows arrive:
+//                       source position of the block's last row outer, expert, then row
 cudaError_t launch_count_exchange(const ExchangeCtx& ctx, const int* lec, const PeerPtrs& cnt,
                                   int n_expert, int capacity_rows, int* dst_base, int* seg_base,
                                   int* blk_base, int* expert_offs, int* seg_off, int* total_rows,
-                                  int* item_prefix, cudaStream_t stream);
+                                  int* item_prefix, int* blk_order, cudaStream_t stream);
 
 // Backward passes reuse the forward routing: only the epoch advances.
 cudaError_t launch_begin_epoch(const ExchangeCtx& ctx, cudaStream_t stream);

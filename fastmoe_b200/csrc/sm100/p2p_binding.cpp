@@ -55,20 +55,21 @@ class ExchangeContext {
 
   // `tables` is one int32 tensor holding, back to back: dst_base[tot], seg_base[tot],
   // blk_base[tot], expert_offs[E + 1], seg_off[E * (world + 1)], total_rows[1],
-  // item_prefix[tot + 1].
+  // item_prefix[tot + 1], blk_order[capacity / 128 + E].
   void count_exchange(torch::Tensor lec, std::vector<int64_t> cnt_ptrs, int64_t n_expert,
                       int64_t capacity_rows, torch::Tensor tables) {
     c10::cuda::CUDAGuard guard(lec.device());
     const int64_t tot = n_expert * ctx_.world;
+    const int64_t fixed = 4 * tot + (n_expert + 1) + n_expert * (ctx_.world + 1) + 2;
     TORCH_CHECK(tables.scalar_type() == torch::kInt && tables.is_contiguous() &&
-                    tables.numel() >= 4 * tot + (n_expert + 1) + n_expert * (ctx_.world + 1) + 2,
+                    tables.numel() >= fixed + capacity_rows / fmoe::kRowBlock + n_expert,
                 "count_exchange: table tensor too small");
     int* t = tables.data_ptr<int>();
     FMOE_P2P_CHECK(fmoe::launch_count_exchange(
         ctx_, lec.data_ptr<int>(), to_ptrs(cnt_ptrs), static_cast<int>(n_expert),
         static_cast<int>(capacity_rows), t, t + tot, t + 2 * tot, t + 3 * tot,
         t + 3 * tot + n_expert + 1, t + 3 * tot + n_expert + 1 + n_expert * (ctx_.world + 1),
-        t + 3 * tot + n_expert + 2 + n_expert * (ctx_.world + 1), stream()));
+        t + 3 * tot + n_expert + 2 + n_expert * (ctx_.world + 1), t + fixed, stream()));
   }
 
   std::vector<torch::Tensor> capacity_grant(torch::Tensor lec, torch::Tensor cap,
@@ -249,7 +250,8 @@ class ExchangeContext {
   //     `scale` when given) into the peers' receive buffers in the order of `pos` and publish
   //     arrival flags — the dispatch direction of the exchange inside the GEMM launch;
   //   * `gate_flags` / `seg_off` (optional): the A operand is this rank's receive buffer and
-  //     every tile waits for the arrival flags of its row block;
+  //     every tile waits for the arrival flags of its row block; with `blk_order` the tiles are
+  //     walked in the order in which their row blocks arrive;
   //   * `push_meta` / `ret_ptrs` (optional): result rows go straight into their source ranks'
   //     return buffers and the return flags are raised when the grid is done.
   void gemm_ep(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor offs,
@@ -258,7 +260,7 @@ class ExchangeContext {
                int64_t epi, c10::optional<torch::Tensor> push_meta, std::vector<int64_t> ret_ptrs,
                int64_t push_slots, c10::optional<pybind11::dict> send,
                std::vector<int64_t> gate_flag_ptrs, c10::optional<torch::Tensor> seg_off,
-               c10::optional<torch::Tensor> trace) {
+               c10::optional<torch::Tensor> blk_order, c10::optional<torch::Tensor> trace) {
     c10::cuda::CUDAGuard guard(a.device());
     TORCH_CHECK(mode == fmoe::kRowsNT || mode == fmoe::kRowsNN, "gemm_ep: row modes only");
     TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && offs.scalar_type() == torch::kInt,
@@ -342,6 +344,13 @@ class ExchangeContext {
       g.gate.world = ctx_.world;
       g.gate.me = ctx_.me;
       g.gate.timeout_ns = ctx_.timeout_ns;
+      if (blk_order.has_value() && blk_order->defined()) {
+        // tiles are walked in the arrival order of their row blocks (count_exchange's table)
+        TORCH_CHECK(blk_order->scalar_type() == torch::kInt && blk_order->is_contiguous() &&
+                        blk_order->numel() >= a.size(0) / fmoe::kRowBlock + g.num_groups,
+                    "gemm_ep: block-order table too small for the receive buffer");
+        g.gate.blk_order = blk_order->data_ptr<int>();
+      }
     }
     if (trace.has_value() && trace->defined()) {
       TORCH_CHECK(trace->scalar_type() == torch::kLong && trace->is_cuda() &&
@@ -410,7 +419,8 @@ void bind_p2p(pybind11::module& m) {
            py::arg("epi") = 0, py::arg("push_meta") = py::none(),
            py::arg("ret_ptrs") = std::vector<int64_t>(), py::arg("push_slots") = 0,
            py::arg("send") = py::none(), py::arg("gate_flag_ptrs") = std::vector<int64_t>(),
-           py::arg("seg_off") = py::none(), py::arg("trace") = py::none())
+           py::arg("seg_off") = py::none(), py::arg("blk_order") = py::none(),
+           py::arg("trace") = py::none())
       .def("wait_only", &ExchangeContext::wait_only);
   m.def("slot_dot", &slot_dot);
   m.attr("P2P_CHAN_COUNTS") = fmoe::kChanCounts;

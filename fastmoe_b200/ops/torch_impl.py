@@ -195,7 +195,9 @@ def exchange_offsets(count_matrix, me, n_expert, capacity_rows=None):
     r"""What ``count_exchange_kernel`` derives on rank ``me`` from the full count matrix.
 
     ``count_matrix[w, g]``: slots rank ``w`` routes to global expert ``g`` (``g = owner * E + e``).
-    Receive layout on every rank: local expert outer, source rank inner.  Returns
+    Receive layout on every rank: local expert outer; inside an expert's segment the rows of
+    source rank ``w`` sit at position ``(owner - w) mod world`` — the owner's own rows first, then
+    those of rank ``owner - 1``, ``owner - 2``, ...  Returns
 
     * ``dst_base[g]``: row in the owner's receive buffer where this rank's rows for ``g`` start,
     * ``expert_offs[e]`` (``E + 1`` entries): row ranges of this rank's local experts,
@@ -209,7 +211,8 @@ def exchange_offsets(count_matrix, me, n_expert, capacity_rows=None):
     dst_base = torch.zeros(tot, dtype=torch.int64)
     for g in range(tot):
         owner, e = divmod(g, n_expert)
-        dst_base[g] = col[owner * n_expert:owner * n_expert + e].sum() + mat[:me, g].sum()
+        before = sum(int(mat[(owner - j) % world, g]) for j in range((owner - me) % world))
+        dst_base[g] = col[owner * n_expert:owner * n_expert + e].sum() + before
     mine = col[me * n_expert:(me + 1) * n_expert]
     expert_offs = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(mine, 0)])
     per_rank = col.view(world, n_expert).sum(1)
@@ -217,6 +220,65 @@ def exchange_offsets(count_matrix, me, n_expert, capacity_rows=None):
     if capacity_rows is not None:
         expert_offs = expert_offs.clamp(max=capacity_rows)
     return dst_base, expert_offs, int(expert_offs[-1]), overflow
+
+
+def exchange_block_order(count_matrix, me, n_expert, capacity_rows=None, block=128):
+    r"""The order in which rank ``me`` walks the ``block``-row blocks of its receive buffer
+    (``count_exchange_kernel``'s ``blk_order``): by the source position of a block's last row —
+    own rows first, then the rows of rank ``me - 1``, ... — then local expert, then row.  Blocks
+    of expert ``e`` whose last row comes from position ``j`` are consecutive: with ``f(t)`` the
+    number of blocks whose last row lies below row ``t`` of the segment they are
+    ``[f(s_j), f(s_{j+1}))``, ``s_j`` being where position ``j`` starts.  Returns a list of
+    ``(local expert, block inside the expert)``."""
+    mat = torch.as_tensor(count_matrix, dtype=torch.int64)
+    world = mat.shape[0]
+    cap = capacity_rows if capacity_rows is not None else int(mat.sum())
+    starts = []          # starts[e][j]: row where position j of expert e begins, clamped
+    run = 0
+    for e in range(n_expert):
+        row = []
+        for j in range(world + 1):
+            row.append(min(run, cap))
+            if j < world:
+                run += int(mat[(me - j) % world, me * n_expert + e])
+        starts.append(row)
+    order = []
+    for j in range(world):
+        for e in range(n_expert):
+            n_e = starts[e][world] - starts[e][0]
+            n_blk = (n_e + block - 1) // block
+
+            def below(t, n_e=n_e, n_blk=n_blk):
+                return n_blk if t >= n_e else t // block
+            lo = below(starts[e][j] - starts[e][0])
+            hi = below(starts[e][j + 1] - starts[e][0])
+            order.extend((e, m) for m in range(lo, hi))
+    return order
+
+
+def send_item_prefix(count_matrix, me, n_expert, capacity_rows=None, block=128):
+    r"""``item_prefix`` of ``count_exchange_kernel``: exclusive prefix of the number of
+    ``block``-row blocks of the owner's buffer that this rank's rows touch, per (peer distance
+    ``j``, local expert ``e``) pair in send order — ``j`` outer, ``e`` inner, global expert
+    ``((me + j) mod world) * E + e``."""
+    mat = torch.as_tensor(count_matrix, dtype=torch.int64)
+    world = mat.shape[0]
+    cap = capacity_rows if capacity_rows is not None else int(mat.sum())
+    col = mat.sum(0)
+    prefix = [0]
+    for j in range(world):
+        owner = (me + j) % world
+        for e in range(n_expert):
+            g = owner * n_expert + e
+            seg = int(col[owner * n_expert:owner * n_expert + e].sum())
+            before = sum(int(mat[(owner - i) % world, g]) for i in range((owner - me) % world))
+            n = int(mat[me, g])
+            end = min(before + n, cap - seg)
+            items = 0
+            if n > 0 and end > before:
+                items = (end - 1) // block - before // block + 1
+            prefix.append(prefix[-1] + items)
+    return prefix
 
 
 def capacity_grants(count_matrix, capacities, n_expert):

@@ -281,7 +281,8 @@ class _Tables:
     def __init__(self, ws, lec, n_expert, capacity):
         tot = n_expert * ws.world
         w1 = ws.world + 1
-        self.buf = torch.empty(4 * tot + (n_expert + 1) + n_expert * w1 + 2, dtype=torch.int32,
+        n_blk = capacity // 128 + n_expert
+        self.buf = torch.empty(4 * tot + (n_expert + 1) + n_expert * w1 + 2 + n_blk, dtype=torch.int32,
                                device=lec.device)
         ws.ctx.count_exchange(lec, ws.cnt_ptrs, n_expert, capacity, self.buf)
         o = 0
@@ -291,7 +292,8 @@ class _Tables:
         self.expert_offs = self.buf[o:o + n_expert + 1]; o += n_expert + 1  # noqa: E702
         self.seg_off = self.buf[o:o + n_expert * w1]; o += n_expert * w1    # noqa: E702
         self.total = self.buf[o:o + 1]; o += 1                 # noqa: E702
-        self.item_prefix = self.buf[o:o + tot + 1]
+        self.item_prefix = self.buf[o:o + tot + 1]; o += tot + 1  # noqa: E702
+        self.blk_order = self.buf[o:o + n_blk]
 
 
 def _rows_view(byte_tensor, rows, d, dtype):
@@ -412,7 +414,7 @@ class _FusedEPMLP(Function):
             pre = gg.pre_buffer(capacity, h, n_expert, x.dtype, dev) if code != 0 else a
             ws.ctx.gemm_ep(gg.MODE_NT, xs, w1, tb.expert_offs, out=a, bias=b1,
                            pre_out=pre if code != 0 else None, act=code, send=send,
-                           gate_flag_ptrs=flag_ptrs, seg_off=tb.seg_off,
+                           gate_flag_ptrs=flag_ptrs, seg_off=tb.seg_off, blk_order=tb.blk_order,
                            trace=new_ep_trace(dev) if config.ep_trace() else None)
         with fused_range("ep.gemm2_push_combine"):
             n_slots_cap = budget * k
@@ -463,7 +465,7 @@ class _FusedEPMLP(Function):
         da = torch.empty(capacity, h, dtype=dout.dtype, device=dout.device)
         ws.ctx.gemm_ep(gg.MODE_NN, dys, w2, tb.expert_offs, out=da, aux=pre if code != 0 else None,
                        act=code, epi=gg.EPI_DACT if code != 0 else gg.EPI_BIAS_ACT, send=send,
-                       gate_flag_ptrs=flag_ptrs, seg_off=tb.seg_off)
+                       gate_flag_ptrs=flag_ptrs, seg_off=tb.seg_off, blk_order=tb.blk_order)
         dw2, db2 = gg.wgrad(dys, a, tb.expert_offs, n_expert, with_bias_grad=True)
         dw1, db1 = gg.wgrad(da, xs, tb.expert_offs, n_expert, with_bias_grad=True)
         dx = None

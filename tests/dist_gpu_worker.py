@@ -278,6 +278,45 @@ def case_multi_layer():
     assert native.get().read_status(_dev().index) == 0
 
 
+def case_exchange_tables():
+    r"""The tables the count-exchange kernel leaves on every rank (destination rows, expert
+    offsets, the senders' item prefix, the walk order of the row blocks) against the host
+    restatement of the same arithmetic on the gathered count matrix; uneven and empty counts, a
+    receive buffer that fits and one that clamps."""
+    from fastmoe_b200.ops import torch_impl
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = _dev()
+    n_expert = 3
+    tot = n_expert * world
+    symm.reserve_tokens(dist.group.WORLD, 4096, dev)
+    ws = symm.get_workspace(dist.group.WORLD, dev)
+    for call, capacity in enumerate((4096, 4096, 640)):
+        gen = torch.Generator().manual_seed(7000 + 31 * call + rank)
+        lec = torch.randint(0, 400, (tot,), generator=gen)
+        lec[torch.randint(0, tot, (2,), generator=gen)] = 0
+        if call == 1:
+            lec = (lec // 100) * 128            # block-aligned boundaries
+        lec_dev = lec.to(dev).int()
+        tb = symm._Tables(ws, lec_dev, n_expert, capacity)    # pylint: disable=protected-access
+        gathered = [torch.empty_like(lec_dev) for _ in range(world)]
+        dist.all_gather(gathered, lec_dev)
+        mat = torch.stack(gathered).cpu().long()
+        dst_base, offs, total, overflow = torch_impl.exchange_offsets(mat, rank, n_expert, capacity)
+        assert torch.equal(tb.dst_base.cpu().long(), dst_base), (tb.dst_base, dst_base)
+        assert torch.equal(tb.expert_offs.cpu().long(), offs), (tb.expert_offs, offs)
+        assert int(tb.total) == total
+        prefix = torch_impl.send_item_prefix(mat, rank, n_expert, capacity)
+        assert tb.item_prefix.cpu().tolist() == prefix, (tb.item_prefix, prefix)
+        order = torch_impl.exchange_block_order(mat, rank, n_expert, capacity)
+        got = tb.blk_order.cpu().tolist()[:len(order)]
+        assert [(v >> 20, v & 0xFFFFF) for v in got] == order, (got, order)
+        status = native.get().read_status(dev.index)
+        assert (status != 0) == overflow, (status, overflow)
+        if status != 0:
+            native.get().clear_status(dev.index)
+        dist.barrier()
+
+
 def case_recv_overflow():
     r"""A bounded receive buffer (FMOE_RECV_CAPACITY_FACTOR) and a gate that sends everything to
     rank 0: rows beyond the capacity are dropped, every rank finds STATUS_RECV_OVERFLOW in its

@@ -102,8 +102,8 @@ def test_grouped_linear_matches_restatement(n_expert, seed):
 def test_exchange_offsets_tile_every_receive_buffer_exactly(world, n_expert, seed):
     r"""The offsets every rank derives from the shared count matrix are consistent: on each
     receiving rank the row ranges of all (source, expert) pairs are disjoint, ordered by local
-    expert then source rank, and cover ``[0, total)``; grants obey the capacities and equal the
-    two-step exchange of the collective-library path."""
+    expert then source position (own rows first), and cover ``[0, total)``; grants obey the
+    capacities and equal the two-step exchange of the collective-library path."""
     gen = torch.Generator().manual_seed(seed)
     tot = world * n_expert
     mat = torch.randint(0, 7, (world, tot), generator=gen)
@@ -119,11 +119,44 @@ def test_exchange_offsets_tile_every_receive_buffer_exactly(world, n_expert, see
                 n = int(mat[src, g])
                 assert int(offs[e]) <= start and start + n <= int(offs[e + 1])
                 covered.append((start, start + n))
+            # inside the segment: own rows first, then the rows of rank owner - 1, owner - 2, ...
+            by_pos = [int(views[(owner - j) % world][0][g]) for j in range(world)]
+            assert by_pos == sorted(by_pos) and by_pos[0] == int(offs[e])
         covered = [c for c in covered if c[1] > c[0]]
         covered.sort()
         assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
         if covered:
             assert covered[0][0] == 0 and covered[-1][1] == total
+    # the walk order of the row blocks: every block once, source position of the last row never
+    # decreasing; and the senders' item lists cover, per owner, every (block, source) pair that
+    # the owner's arrival flags wait for
+    block = 4
+    for owner in range(world):
+        _base, offs, total, _ov = views[owner]
+        order = torch_impl.exchange_block_order(mat, owner, n_expert, block=block)
+        want = [(e, m) for e in range(n_expert)
+                for m in range((int(offs[e + 1]) - int(offs[e]) + block - 1) // block)]
+        assert sorted(order) == want
+        stages = []
+        for e, m in order:
+            last = min(int(offs[e]) + (m + 1) * block, int(offs[e + 1])) - 1
+            g = owner * n_expert + e
+            pos = [j for j in range(world)
+                   if int(views[(owner - j) % world][0][g]) <= last
+                   < int(views[(owner - j) % world][0][g]) + int(mat[(owner - j) % world, g])]
+            assert len(pos) == 1
+            stages.append(pos[0])
+        assert stages == sorted(stages)
+    for me in range(world):
+        prefix = torch_impl.send_item_prefix(mat, me, n_expert, block=block)
+        assert len(prefix) == tot + 1 and prefix[0] == 0
+        for j in range(world):
+            owner = (me + j) % world
+            for e in range(n_expert):
+                g = owner * n_expert + e
+                start, n = int(views[me][0][g]) - int(views[owner][1][e]), int(mat[me, g])
+                touched = len({r // block for r in range(start, start + n)})
+                assert prefix[j * n_expert + e + 1] - prefix[j * n_expert + e] == touched
     # a bounded receive buffer: totals are clamped and the overflow is flagged on every rank
     small = max(0, int(mat.sum()) // (2 * world))
     flags = [torch_impl.exchange_offsets(mat, me, n_expert, small)[3] for me in range(world)]

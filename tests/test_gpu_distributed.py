@@ -23,7 +23,7 @@ def _need(world):
         pytest.skip("needs %d GPUs" % world)
 
 
-@pytest.mark.parametrize("case", ["fused_vs_general", "oracle", "uneven_tokens", "multi_layer",
+@pytest.mark.parametrize("case", ["fused_vs_general", "oracle", "exchange_tables", "uneven_tokens", "multi_layer",
                                   "recv_overflow", "shadow_fused", "swipe_device", "pipeline_gpu", "allreduce", "grouped_ddp", "wait_timeout",
                                   "graph_step", "smart_schedule", "slice_group", "capacity"])
 def test_two_ranks(case):
@@ -39,7 +39,7 @@ def test_nvls_allreduce():
     assert codes == [0, 0], codes
 
 
-@pytest.mark.parametrize("case", ["fused_vs_general", "oracle", "multi_layer", "allreduce",
+@pytest.mark.parametrize("case", ["fused_vs_general", "oracle", "exchange_tables", "multi_layer", "allreduce",
                                   "slice_group", "capacity", "smart_schedule"])
 def test_many_ranks(case):
     world = int(os.environ.get("FMOE_TEST_WORLD", "4"))
