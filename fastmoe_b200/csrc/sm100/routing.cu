@@ -272,9 +272,10 @@ __global__ void scatter_rows_kernel(const T* __restrict__ src, const int64_t* __
   if (row_slot != nullptr && lane == 0) row_slot[row] = s;
 }
 
-// One warp per token; d % 8 == 0.
+// One warp per token; d % 8 == 0.  At most 64 registers, so that four blocks fit on an SM and a
+// batch of 4096 tokens is one wave on 148 SMs.
 template <typename T>
-__global__ void gather_combine_kernel(const T* __restrict__ rows, const int64_t* __restrict__ idx,
+__global__ void __launch_bounds__(256, 4) gather_combine_kernel(const T* __restrict__ rows, const int64_t* __restrict__ idx,
                                       const int* __restrict__ rank, const int* __restrict__ base,
                                       const T* __restrict__ weight, int n_tokens, int k, int d,
                                       T* __restrict__ out) {
@@ -283,8 +284,8 @@ __global__ void gather_combine_kernel(const T* __restrict__ rows, const int64_t*
   if (t >= n_tokens) return;
   const int nv = d >> 3;
   uint4* o = reinterpret_cast<uint4*>(out + static_cast<long>(t) * d);
-  // Rows and weights of the k slots first, then two 16-byte chunks of every row in flight.
-  constexpr int kMaxInline = 8;
+  // Rows and weights of the k slots first, then four 16-byte chunks of every row in flight.
+  constexpr int kMaxInline = 4;
   long rows_of[kMaxInline];
   float w_of[kMaxInline];
   const int kk = k < kMaxInline ? k : kMaxInline;
@@ -693,6 +694,7 @@ gate_bwd_dw_kernel(const float* __restrict__ dl, const T* __restrict__ x, int n_
   float a0[TOT], a1[TOT], bsum[TOT];
 #pragma unroll
   for (int e = 0; e < TOT; ++e) a0[e] = a1[e] = bsum[e] = 0.f;
+#pragma unroll 4
   for (int t = t0 + warp; t < t1; t += 8) {
     float x0 = 0.f, x1 = 0.f;
     if (col < d) {
@@ -1074,7 +1076,9 @@ cudaError_t launch_gate_topk_softmax_bwd(int logit_dtype, const void* dprob, con
 }
 
 #define FMOE_GATE_TOT(tot, ...)                          \
-  if ((tot) <= 8) { constexpr int TOT = 8; __VA_ARGS__; }       \
+  if ((tot) <= 2) { constexpr int TOT = 2; __VA_ARGS__; }       \
+  else if ((tot) <= 4) { constexpr int TOT = 4; __VA_ARGS__; }  \
+  else if ((tot) <= 8) { constexpr int TOT = 8; __VA_ARGS__; }  \
   else if ((tot) <= 16) { constexpr int TOT = 16; __VA_ARGS__; } \
   else if ((tot) <= 32) { constexpr int TOT = 32; __VA_ARGS__; } \
   else { constexpr int TOT = 64; __VA_ARGS__; }
@@ -1115,7 +1119,10 @@ cudaError_t launch_gate_bwd(int dtype, const void* dprob, const int64_t* idx, co
   if (splits < 1) splits = 1;
   if (splits > 64) splits = 64;
   dim3 g2((d + 63) / 64, splits);
-  if (tot <= 8) {
+  if (tot <= 2) {
+    FMOE_DISPATCH_16(dtype, (gate_bwd_dw_kernel<T, 2><<<g2, 256, 0, stream>>>(
+        dl_scratch, static_cast<const T*>(x), n_rows, d, tot, dw, db)));
+  } else if (tot <= 8) {
     FMOE_DISPATCH_16(dtype, (gate_bwd_dw_kernel<T, 8><<<g2, 256, 0, stream>>>(
         dl_scratch, static_cast<const T*>(x), n_rows, d, tot, dw, db)));
   } else {

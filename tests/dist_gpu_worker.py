@@ -132,7 +132,9 @@ def case_oracle():
     rank, world = dist.get_rank(), dist.get_world_size()
     cases = ((torch.bfloat16, 2, 2, 512, 256, 512, None, 6e-2),
              (torch.float16, 3, 1, 333, 128, 320, nn.ReLU(), 2e-2),
-             (torch.bfloat16, 2, 2, 1200, 256, 1024, nn.GELU(approximate="tanh"), 6e-2))
+             (torch.bfloat16, 2, 2, 1200, 256, 1024, nn.GELU(approximate="tanh"), 6e-2),
+             # more (peer, expert) pairs than a warp has lanes: the senders decode from memory
+             (torch.bfloat16, 40, 2, 900, 128, 256, nn.ReLU(), 6e-2))
     symm.reserve_tokens(dist.group.WORLD, max(c[3] for c in cases), _dev())
     for dtype, num_expert, top_k, n_tok, d, h, act, tol in cases:
         layer = _make_layer(world, rank, num_expert=num_expert, d=d, h=h, top_k=top_k, dtype=dtype,
