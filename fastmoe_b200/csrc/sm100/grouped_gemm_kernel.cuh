@@ -368,7 +368,7 @@ __device__ __forceinline__ void store32(T* dst, const float (&v)[32]) {
 
 __device__ __forceinline__ void fail(SharedAux* aux, int* status, int code) {
   aux->abort = 1;
-  if (status != nullptr) atomicCAS(status, 0, code);
+  if (status != nullptr) record_failure(status, code);
 }
 
 struct EpiTile {
@@ -1006,7 +1006,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                 // a failure already recorded on this GPU (by any kernel) ends the wait at once:
                 // one lost peer must not cost a full time-out in every tile that follows
                 const bool failed_before =
-                    p.status != nullptr && *reinterpret_cast<const volatile int*>(p.status) != 0;
+                    p.status != nullptr && status_is_failure(*reinterpret_cast<const volatile int*>(p.status));
                 if (*abort_flag != 0 || failed_before || ptx::globaltimer() - t0 > p.gate.timeout_ns) {
                   here = false;
                   break;
@@ -1327,7 +1327,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
             if (src >= 0 && src < p.push_world && slot < p.push_slots) {
               rt.out_row = static_cast<uint8_t*>(p.push_dst.p[src]) + slot * p.n * 2;
             } else if (p.status != nullptr) {
-              atomicCAS(p.status, 0, STATUS_BAD_PUSH_META);
+              record_failure(p.status, STATUS_BAD_PUSH_META);
             }
           }
         } else {

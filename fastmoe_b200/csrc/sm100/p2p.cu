@@ -45,9 +45,9 @@ __device__ __forceinline__ bool wait_flag(const ExchangeCtx& c, int channel, int
   while (true) {
     if (ld_acquire_sys(f) - target >= 0) return true;
     if ((++spins & 0xff) == 0) {
-      if (*reinterpret_cast<volatile int*>(c.status) != 0) return false;
+      if (status_is_failure(*reinterpret_cast<volatile int*>(c.status))) return false;
       if (now_ns() - t0 > c.timeout_ns) {
-        atomicCAS(c.status, 0, kStatusPeerTimeout);
+        record_failure(c.status, kStatusPeerTimeout);
         return false;
       }
     }
@@ -502,8 +502,9 @@ __global__ void __launch_bounds__(1024, 1) return_push_kernel(const __grid_const
 template <typename T>
 __global__ void wait_combine_kernel(const __grid_constant__ ExchangeCtx c, const T* __restrict__ ret,
                                     const int64_t* __restrict__ idx, const T* __restrict__ weight,
-                                    int n_tokens, int k, int d, T* __restrict__ out,
-                                    T* __restrict__ keep) {
+                                    const int* __restrict__ rank, const int* __restrict__ dst_base,
+                                    int capacity_rows, int n_tokens, int k, int d,
+                                    T* __restrict__ out, T* __restrict__ keep) {
   block_wait_all(c, kChanReturn, c.epoch[0]);
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
@@ -520,12 +521,17 @@ __global__ void wait_combine_kernel(const __grid_constant__ ExchangeCtx c, const
       }
       for (int j = 0; j < k; ++j) {
         const long s = static_cast<long>(t) * k + j;
-        if (idx[s] < 0) continue;
+        const long e = idx[s];
+        if (e < 0) continue;
+        // A slot whose row did not fit into the owner's receive buffer was never sent and
+        // nothing came back for it: it counts as zero (in `keep` too).
+        const bool sent = rank == nullptr || __ldg(dst_base + e) + __ldg(rank + s) < capacity_rows;
         const float w = weight != nullptr ? V2<T>::to_f(weight[s]) : 1.f;
         uint4 v[2];
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-          if (i0 + u * 32 < nv) v[u] = __ldcg(reinterpret_cast<const uint4*>(ret + s * d) + i0 + u * 32);
+          v[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (sent && i0 + u * 32 < nv) v[u] = __ldcg(reinterpret_cast<const uint4*>(ret + s * d) + i0 + u * 32);
         }
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
@@ -974,13 +980,14 @@ cudaError_t launch_return_push(const ExchangeCtx& ctx, int dtype, const void* ro
 }
 
 cudaError_t launch_wait_combine(const ExchangeCtx& ctx, int dtype, const void* ret,
-                                const int64_t* idx, const void* weight, int n_tokens, int k, int d,
+                                const int64_t* idx, const void* weight, const int* rank,
+                                const int* dst_base, int capacity_rows, int n_tokens, int k, int d,
                                 void* out, void* keep, cudaStream_t stream) {
   if (d % 8 != 0) return cudaErrorInvalidValue;
   const int wpb = 8;
   FMOE_P2P_16(dtype, (wait_combine_kernel<T><<<push_grid(n_tokens, wpb), wpb * 32, 0, stream>>>(
-      ctx, static_cast<const T*>(ret), idx, static_cast<const T*>(weight), n_tokens, k, d,
-      static_cast<T*>(out), static_cast<T*>(keep))));
+      ctx, static_cast<const T*>(ret), idx, static_cast<const T*>(weight), rank, dst_base,
+      capacity_rows, n_tokens, k, d, static_cast<T*>(out), static_cast<T*>(keep))));
   return cudaGetLastError();
 }
 

@@ -22,6 +22,18 @@ constexpr int kStatusPeerTimeout = 201;      // a peer's flag did not arrive in 
 constexpr int kStatusRecvOverflow = 202;     // more rows routed to a rank than its buffer holds
 constexpr int kStatusCapacityMismatch = 203; // the ranks of a group sized their receive buffers differently
 
+#ifdef __CUDACC__
+// A receive overflow is a report, not a failure: rows beyond the buffer are dropped, everything
+// else of the step is still exchanged and computed.  Every other code means that a wait gave up;
+// later waits on the same GPU then end at once instead of spending a full time-out each.
+__device__ __forceinline__ bool status_is_failure(int s) { return s != 0 && s != kStatusRecvOverflow; }
+// First failure wins; a failure replaces an overflow report.
+__device__ __forceinline__ void record_failure(int* status, int code) {
+  const int old = atomicCAS(status, 0, code);
+  if (old == kStatusRecvOverflow) atomicCAS(status, kStatusRecvOverflow, code);
+}
+#endif
+
 // Arrival of dispatched rows is tracked per block of this many rows of the receive buffer
 // (the M extent of a GEMM tile).
 constexpr int kRowBlock = 128;
@@ -98,9 +110,12 @@ cudaError_t launch_return_push(const ExchangeCtx& ctx, int dtype, const void* ro
                                int d, int capacity_rows, long ret_slots, cudaStream_t stream);
 
 // Waits for the return flags, then out[t] = sum_j w[t, j] * ret[t * k + j] over kept slots
-// (w = 1 when null) and, when `keep` is given, keep[s] = ret[s] for the backward pass.
+// (w = 1 when null) and, when `keep` is given, keep[s] = ret[s] for the backward pass.  With
+// `rank` / `dst_base` / `capacity_rows` a slot whose row dst_base[idx[s]] + rank[s] lies beyond
+// the owner's receive buffer (it was never sent) counts as zero.
 cudaError_t launch_wait_combine(const ExchangeCtx& ctx, int dtype, const void* ret,
-                                const int64_t* idx, const void* weight, int n_tokens, int k, int d,
+                                const int64_t* idx, const void* weight, const int* rank,
+                                const int* dst_base, int capacity_rows, int n_tokens, int k, int d,
                                 void* out, void* keep, cudaStream_t stream);
 
 // dscore[s] = <dout[s / k], y[s]>  (0 for dropped slots)

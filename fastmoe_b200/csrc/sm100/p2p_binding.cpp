@@ -152,12 +152,24 @@ class ExchangeContext {
   }
 
   void wait_combine(torch::Tensor ret, torch::Tensor idx, c10::optional<torch::Tensor> weight,
-                    int64_t k, torch::Tensor out, c10::optional<torch::Tensor> keep) {
+                    int64_t k, torch::Tensor out, c10::optional<torch::Tensor> keep,
+                    c10::optional<torch::Tensor> rank, c10::optional<torch::Tensor> dst_base,
+                    int64_t capacity_rows) {
     c10::cuda::CUDAGuard guard(out.device());
     const void* w = (weight.has_value() && weight->defined()) ? weight->data_ptr() : nullptr;
     void* kp = (keep.has_value() && keep->defined()) ? keep->data_ptr() : nullptr;
+    const int* rk = nullptr;
+    const int* db = nullptr;
+    if (rank.has_value() && rank->defined()) {
+      TORCH_CHECK(dst_base.has_value() && dst_base->defined() && rank->scalar_type() == torch::kInt &&
+                      dst_base->scalar_type() == torch::kInt && rank->numel() == idx.numel(),
+                  "wait_combine: int32 slot ranks (one per slot) and destination bases");
+      rk = rank->data_ptr<int>();
+      db = dst_base->data_ptr<int>();
+    }
     FMOE_P2P_CHECK(fmoe::launch_wait_combine(ctx_, dtype16(out), ret.data_ptr(),
-                                             idx.data_ptr<int64_t>(), w,
+                                             idx.data_ptr<int64_t>(), w, rk, db,
+                                             static_cast<int>(capacity_rows),
                                              static_cast<int>(out.size(0)), static_cast<int>(k),
                                              static_cast<int>(out.size(1)), out.data_ptr(), kp,
                                              stream()));
@@ -406,7 +418,10 @@ void bind_p2p(pybind11::module& m) {
       .def("wait_copy", &ExchangeContext::wait_copy)
       .def("wait_arrival", &ExchangeContext::wait_arrival)
       .def("return_push", &ExchangeContext::return_push)
-      .def("wait_combine", &ExchangeContext::wait_combine)
+      .def("wait_combine", &ExchangeContext::wait_combine, py::arg("ret"), py::arg("idx"),
+           py::arg("weight"), py::arg("k"), py::arg("out"), py::arg("keep"),
+           py::arg("rank") = py::none(), py::arg("dst_base") = py::none(),
+           py::arg("capacity_rows") = 0)
       .def("allgather", &ExchangeContext::allgather)
       .def("allreduce_multimem", &ExchangeContext::allreduce_multimem)
       .def("broadcast", &ExchangeContext::broadcast)

@@ -321,20 +321,22 @@ class _DispatchP2P(Function):
         ctx.k = k
         ctx.n_tok = x.shape[0]
         ctx.budget = budget
-        ctx.save_for_backward(idx, meta, tb.total)
+        ctx.capacity = capacity
+        ctx.save_for_backward(idx, meta, tb.total, rank, tb.dst_base)
         ctx.mark_non_differentiable(tb.expert_offs, meta, tb.total, tb.dst_base)
         return xs, tb.expert_offs, meta, tb.total, tb.dst_base
 
     @staticmethod
     def backward(ctx, dxs, _g1, _g2, _g3, _g4):
-        idx, meta, total = ctx.saved_tensors
+        idx, meta, total, rank, dst_base = ctx.saved_tensors
         ws = ctx.ws
         dxs = dxs.contiguous()
         d = dxs.shape[1]
         stage_ret, ret_ptrs = ws.buffer("ret", ctx.budget * ctx.k * d * dxs.element_size())
         ws.ctx.return_push(dxs, meta, total, ret_ptrs, ctx.budget * ctx.k)
         dx = torch.empty(ctx.n_tok, d, dtype=dxs.dtype, device=dxs.device)
-        ws.ctx.wait_combine(stage_ret, idx, None, ctx.k, dx, None)
+        ws.ctx.wait_combine(stage_ret, idx, None, ctx.k, dx, None, rank=rank, dst_base=dst_base,
+                            capacity_rows=ctx.capacity)
         return (dx,) + (None,) * 8
 
 
@@ -350,7 +352,8 @@ class _CombineP2P(Function):
         ws.ctx.return_push(ys, meta, total, ret_ptrs, budget * k)
         out = torch.empty(n_tok, d, dtype=ys.dtype, device=ys.device)
         y_slots = torch.empty(idx.numel(), d, dtype=ys.dtype, device=ys.device)
-        ws.ctx.wait_combine(stage_ret, idx, score, k, out, y_slots)
+        ws.ctx.wait_combine(stage_ret, idx, score, k, out, y_slots, rank=rank, dst_base=dst_base,
+                            capacity_rows=capacity)
         ctx.ws = ws
         ctx.args = n_expert, k, capacity
         ctx.save_for_backward(y_slots, score, idx, rank, dst_base, total)
@@ -424,12 +427,13 @@ class _FusedEPMLP(Function):
             n_tok = x.shape[0]
             out = torch.empty(n_tok, d, dtype=x.dtype, device=dev)
             y_slots = torch.empty(idx.numel(), d, dtype=x.dtype, device=dev)
-            ws.ctx.wait_combine(stage_ret, idx, score, k, out, y_slots)
+            ws.ctx.wait_combine(stage_ret, idx, score, k, out, y_slots, rank=rank,
+                                dst_base=tb.dst_base, capacity_rows=capacity)
 
         ctx.ws = ws
         ctx.args = n_expert, k, capacity, budget, act, n_tok
         ctx.lease = lease
-        ctx.save_for_backward(xs, pre, a, w1, w2, tb.buf, meta, idx, my_offs, pos, score, y_slots)
+        ctx.save_for_backward(xs, pre, a, w1, w2, tb.buf, meta, idx, my_offs, pos, score, y_slots, rank)
         ctx.tables = tb
         if not any(ctx.needs_input_grad):
             lease.release()  # nothing will run backward through this call
@@ -439,7 +443,7 @@ class _FusedEPMLP(Function):
     def backward(ctx, dout):
         from ..ops import grouped_gemm as gg
         nat = native.get()
-        (xs, pre, a, w1, w2, _tbuf, meta, idx, my_offs, pos, score, y_slots) = ctx.saved_tensors
+        (xs, pre, a, w1, w2, _tbuf, meta, idx, my_offs, pos, score, y_slots, rank) = ctx.saved_tensors
         n_expert, k, capacity, budget, act, n_tok = ctx.args
         tb = ctx.tables
         ws = ctx.ws
@@ -475,7 +479,8 @@ class _FusedEPMLP(Function):
             ws.ctx.gemm_ep(gg.MODE_NN, da, w1, tb.expert_offs, push_meta=meta, ret_ptrs=ret_ptrs,
                            push_slots=n_slots_cap)
             dx = torch.empty(n_tok, d, dtype=dout.dtype, device=dout.device)
-            ws.ctx.wait_combine(stage_ret, idx, None, k, dx, None)
+            ws.ctx.wait_combine(stage_ret, idx, None, k, dx, None, rank=rank, dst_base=tb.dst_base,
+                                capacity_rows=capacity)
         ctx.lease.release()
         return (dx, dscore, dw1, db1, dw2, db2) + (None,) * 11
 

@@ -321,8 +321,10 @@ def case_exchange_tables():
 
 def case_recv_overflow():
     r"""A bounded receive buffer (FMOE_RECV_CAPACITY_FACTOR) and a gate that sends everything to
-    rank 0: rows beyond the capacity are dropped, every rank finds STATUS_RECV_OVERFLOW in its
-    status word, and the next, balanced step works after the status is cleared."""
+    rank 0: rows beyond the capacity are dropped and count as zero, everything that fitted is
+    computed as usual (an overflow is a report, not a failure), every rank finds
+    STATUS_RECV_OVERFLOW in its status word, and the next, balanced step works after the status
+    is cleared."""
     from fastmoe_b200.utils import check_device_status
     nat = native.get()
     rank, world = dist.get_rank(), dist.get_world_size()
@@ -337,6 +339,18 @@ def case_recv_overflow():
     y = layer(x)
     torch.cuda.synchronize()
     assert torch.isfinite(y.float()).all()
+    if world == 2:
+        # every token picks experts 0 and 1 with score 1/2 each; expert 0's segment on rank 0
+        # is exactly the buffer (2 x 512 rows), expert 1's lies beyond it: y = expert0(x) / 2
+        ex = layer.experts
+        w1, b1 = ex.htoh4.weight.detach()[0].clone(), ex.htoh4.bias.detach()[0].clone()
+        w2, b2 = ex.h4toh.weight.detach()[0].clone(), ex.h4toh.bias.detach()[0].clone()
+        for t in (w1, b1, w2, b2):
+            dist.broadcast(t, 0)
+        hid = torch.nn.functional.gelu(x.float() @ w1.float().t() + b1.float())
+        want = 0.5 * (hid.to(x.dtype).float() @ w2.float().t() + b2.float())
+        err = float((y.detach().float() - want).abs().max())
+        assert err <= 3e-2 * float(want.abs().max()) + 1e-2, err
     try:
         check_device_status(_dev())
         raise AssertionError("overflow was not reported")
