@@ -199,6 +199,51 @@ class SymmWorkspace:
     def set_timeout_ms(self, ms):
         self.ctx.set_timeout_ms(float(ms))
 
+    def audit(self):
+        r"""Host-side audit of the signalling state between steps.  Synchronises the device; call
+        it where all ranks of the group are in step (after a barrier), with no layer call in
+        flight.  The reference has no counterpart (its exchanges are library collectives); here
+        every protocol word has an invariant that must hold again once a step is over:
+
+        * the status word is zero;
+        * the grid-completion counters (epoch words 1-5: dispatch, return, reduction, push,
+          broadcast) and the sender warps' per-block row counters are back at zero;
+        * no flag word — channel flags and the per-block arrival flags of the receive buffer —
+          carries an epoch ahead of this rank's own (a peer that ran ahead or a stale buffer);
+        * every receive-buffer lease has been handed back.
+
+        Returns a dict with the findings and ``ok``."""
+        nat = native.get()
+        torch.cuda.synchronize(self.device)
+        epoch = [int(v) for v in self.epoch.tolist()]
+        exchange_epoch, reduce_epoch = epoch[0], epoch[6]
+        signal = self.signal[:nat.P2P_NUM_CHANNELS * nat.P2P_MAX_PEERS * 4].view(torch.int32)
+        signal = signal.view(nat.P2P_NUM_CHANNELS, nat.P2P_MAX_PEERS)[:, :self.world]
+        ahead = 0
+        for chan in range(nat.P2P_NUM_CHANNELS):
+            # reduction kernels signal twice per launch: 2 * epoch ("ready") and 2 * epoch + 1 ("done")
+            limit = 2 * reduce_epoch + 1 if chan == nat.P2P_CHAN_REDUCE else exchange_epoch
+            ahead += int((signal[chan] - limit > 0).sum())
+        gate = self._buffers.get("gate")
+        if gate is not None:
+            flags = gate[0].view(torch.int32).view(-1, nat.P2P_MAX_PEERS)[:, :self.world]
+            ahead += int((flags - exchange_epoch > 0).sum())
+        counters = getattr(self, "_item_count", None)
+        busy_blocks = int((counters != 0).sum()) if counters is not None else 0
+        pooled = sum(len(v) for v in self._pool.values())
+        leased = len(getattr(self, "_leased_handles", [])) - pooled
+        report = {
+            "status": int(nat.read_status(self.device.index)),
+            "epoch": epoch,
+            "completion_counters": epoch[1:6],
+            "sender_block_counters_nonzero": busy_blocks,
+            "flags_ahead_of_epoch": ahead,
+            "leases_outstanding": leased,
+        }
+        report["ok"] = (report["status"] == 0 and not any(epoch[1:6]) and busy_blocks == 0
+                        and ahead == 0 and leased == 0)
+        return report
+
 
 class _Lease:
     r"""One pooled symmetric buffer in use; ``release()`` (or garbage collection) returns it."""

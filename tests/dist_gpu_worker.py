@@ -157,6 +157,13 @@ def case_oracle():
     assert 0 <= t["launch_skew_us"] <= t["kernel_us"], t
     assert t["sender_us"] <= t["kernel_us"] and t["first_rows_us"]["max"] <= t["kernel_us"], t
     assert 0 < t["first_unit_us"]["ids_loaded"] <= t["first_unit_us"]["counted"] <= t["kernel_us"], t
+    # the signalling state is back at rest: counters zero, no flag ahead of the epoch, leases back
+    del layer
+    import gc
+    gc.collect()
+    dist.barrier()
+    report = symm.get_workspace(dist.group.WORLD, _dev()).audit()
+    assert report["ok"], report
 
 
 def case_uneven_tokens():
