@@ -77,7 +77,7 @@ def _one_rank_group(port):
 def ep_layer_case(repeats=3, n_tok=4096, d=1024, h=4096, n_exp=2, k=2):
     r"""The fused expert-parallel layer in a one-rank process group: every row is "sent" to this
     GPU's own symmetric buffers, so the kernels run exactly the code of the multi-GPU path
-    (sender CTAs and arrival-gated tiles in the first GEMM launch, return push in the epilogue
+    (sender warps and arrival-gated tiles in the first GEMM launch, return push in the epilogue
     of the second, peer tables, flags, fences) without a second GPU.  Checked against the
     single-GPU fused path of the same layer."""
     import torch.distributed as dist

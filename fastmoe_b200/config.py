@@ -127,7 +127,7 @@ def recv_capacity_factor():
 
 def force_ep_path():
     r"""``FMOE_FORCE_EP=1``: layers with ``world_size == 1`` inside an initialised one-rank NCCL
-    group take the expert-parallel kernels (sender CTAs, arrival flags, return push) instead of
+    group take the expert-parallel kernels (sender warps, arrival flags, return push) instead of
     the single-GPU path.  Every peer table then points at the GPU itself; used to test and
     profile the multi-GPU code on one GPU."""
     return switch_from_env("FMOE_FORCE_EP", False)

@@ -670,7 +670,7 @@ __device__ __forceinline__ void epilogue_tile_rows(const RowTile& rt, Packed32& 
 
 
 // ------------------------------------------------------------------------------------------
-// Sender CTAs: the dispatch direction of the exchange inside a GEMM launch.
+// Sender warps: the dispatch direction of the exchange inside a GEMM launch.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ int ld_acquire_sys_i32(const int* p) {
   int v;

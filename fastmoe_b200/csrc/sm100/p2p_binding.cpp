@@ -258,7 +258,7 @@ class ExchangeContext {
   }
 
   // Row-mode grouped GEMM with the expert-parallel roles of the tcgen05 kernel:
-  //   * `send` (dict, optional): sender CTAs copy this rank's token rows `x` (scaled by
+  //   * `send` (dict, optional): sender warps copy this rank's token rows `x` (scaled by
   //     `scale` when given) into the peers' receive buffers in the order of `pos` and publish
   //     arrival flags — the dispatch direction of the exchange inside the GEMM launch;
   //   * `gate_flags` / `seg_off` (optional): the A operand is this rank's receive buffer and

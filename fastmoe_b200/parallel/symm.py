@@ -12,17 +12,19 @@ what the reference does with a private NCCL communicator obtained by subclassing
 One layer call is, per rank and without any host read:
 
     route → count_exchange (counts to all peers; offsets and block tables from the full matrix)
-          → grouped GEMM 1 launch.  Its first CTAs are *senders*: they copy this rank's token
-            rows (+ (source, slot) words) into the owners' receive buffers with bulk copies
-            and raise one arrival flag per (128-row block, source).  The other CTAs run the
-            GEMM (+ bias, activation) straight out of the receive buffer, every tile waiting
-            only for the flags of its own row block: dispatch and GEMM 1 overlap tile by tile
+          → grouped GEMM 1 launch.  Two warps of every CTA that are idle in the GEMM roles are
+            *senders*: they copy this rank's token rows (+ (source, slot) words) through
+            registers into the owners' receive buffers and raise one arrival flag per (128-row
+            block, source).  The GEMM roles of the same CTAs work (+ bias, activation) straight
+            out of the receive buffer, tiles walked in the arrival order of their row blocks and
+            every tile waiting only for the flags of its own block: dispatch and GEMM 1 overlap
+            tile by tile
           → grouped GEMM 2 whose epilogue stores every output row straight into its source
             rank's slot-indexed return buffer and raises the return flags
           → wait_combine  (arrival flags, gate-weighted sum over the k slots of a token)
 
 Backward runs the same two exchanges with gradient rows: the score-scaled output gradients
-are sent by the sender CTAs of the first input-gradient GEMM, the last input-gradient GEMM
+are sent by the sender warps of the first input-gradient GEMM, the last input-gradient GEMM
 pushes from its epilogue.  Layers whose activation the GEMM epilogue does not know use the
 stand-alone dispatch / return kernels around PyTorch ops.  The module also holds the other
 peer-to-peer collectives: gradient all-reduce (one- and two-shot), all-gather of slice
@@ -426,11 +428,11 @@ class _CombineP2P(Function):
 class _FusedEPMLP(Function):
     r"""The whole expert-parallel MLP as one autograd node (activations the GEMM epilogue knows).
 
-    Forward: count exchange → GEMM 1 launch (sender CTAs dispatch the rows, the other CTAs
+    Forward: count exchange → GEMM 1 launch (sender warps dispatch the rows, the GEMM warps
     compute tiles as their rows arrive; + bias, activation) → GEMM 2 whose epilogue stores every
     output row straight into the source rank's return buffer and raises the return flags →
     wait + gate-weighted combine.  Backward: ``d score`` locally; the first input-gradient GEMM
-    carries the sender CTAs for the score-scaled output gradients (and applies the activation
+    carries the sender warps for the score-scaled output gradients (and applies the activation
     derivative), then both weight gradients, and the last input-gradient GEMM again pushes its
     rows home, where the k copies of a token are summed.  GEMM 2's result and the expert input
     gradient never exist as local tensors; received rows are never copied out of the buffer

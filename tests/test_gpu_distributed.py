@@ -50,7 +50,7 @@ def test_many_ranks(case):
 
 @pytest.mark.parametrize("case", ["fused_vs_general", "oracle", "multi_layer", "graph_step"])
 def test_one_rank_group(case):
-    r"""The expert-parallel kernels (sender CTAs, arrival-gated tiles, return push, flags) in a
+    r"""The expert-parallel kernels (sender warps, arrival-gated tiles, return push, flags) in a
     one-rank process group: every peer table points at this GPU, so one GPU runs exactly the
     code of the multi-GPU path."""
     pytest.importorskip("torch")
