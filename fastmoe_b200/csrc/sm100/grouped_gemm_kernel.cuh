@@ -977,7 +977,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
       const int r0 = c.row_begin + c.m_tile * BM;
       const int r1 = min(r0 + BM, c.row_end);
       const int* so = p.gate.seg_off + c.group * (p.gate.world + 1) + lane;
-      if (!(so[0] < r1 && so[1] > r0)) return nullptr;
+      // a source without rows for this expert sends nothing and raises no flag: never wait
+      // for it, also when its (empty) range lies strictly inside the block
+      if (!(so[0] < so[1] && so[0] < r1 && so[1] > r0)) return nullptr;
       int src = p.gate.me - lane;
       if (src < 0) src += p.gate.world;
       const int blk = aux->tile_prefix[c.group] / n_tiles_n + c.m_tile;

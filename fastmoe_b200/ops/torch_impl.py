@@ -281,6 +281,33 @@ def send_item_prefix(count_matrix, me, n_expert, capacity_rows=None, block=128):
     return prefix
 
 
+def send_items(count_matrix, me, n_expert, capacity_rows=None, block=128):
+    r"""The sender warps' work list on rank ``me`` (``grouped_gemm_kernel.cuh::send_decode``): one
+    item per ``block``-row block of an owner's buffer that this rank's rows touch, in send
+    order.  Each item is ``(owner, flag block on the owner, first row, one past the last row)``
+    with rows counted from the start of the owner's buffer; the owner's arrival flag
+    ``(flag block, source = me)`` goes up when all rows of the item have been stored."""
+    mat = torch.as_tensor(count_matrix, dtype=torch.int64)
+    world = mat.shape[0]
+    cap = capacity_rows if capacity_rows is not None else int(mat.sum())
+    col = mat.sum(0)
+    items = []
+    for j in range(world):
+        owner = (me + j) % world
+        for e in range(n_expert):
+            g = owner * n_expert + e
+            seg = int(col[owner * n_expert:owner * n_expert + e].sum())
+            blk_base = sum((int(col[owner * n_expert + e2]) + block - 1) // block for e2 in range(e))
+            rel0 = sum(int(mat[(owner - i) % world, g]) for i in range((owner - me) % world))
+            n = int(mat[me, g])
+            end = min(rel0 + n, cap - seg)
+            if n == 0 or end <= rel0:
+                continue
+            for b in range(rel0 // block, (end - 1) // block + 1):
+                items.append((owner, blk_base + b, seg + max(rel0, b * block), seg + min(end, (b + 1) * block)))
+    return items
+
+
 def capacity_grants(count_matrix, capacities, n_expert):
     r"""What ``capacity_grant_kernel`` derives on every rank: ``grant[w, g]``, handed out in rank
     order from the capacity of ``g``'s owner (``capacities[owner, e]``)."""

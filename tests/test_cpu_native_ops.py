@@ -157,6 +157,39 @@ def test_exchange_offsets_tile_every_receive_buffer_exactly(world, n_expert, see
                 start, n = int(views[me][0][g]) - int(views[owner][1][e]), int(mat[me, g])
                 touched = len({r // block for r in range(start, start + n)})
                 assert prefix[j * n_expert + e + 1] - prefix[j * n_expert + e] == touched
+    # the senders' items against what the owners' tiles wait for: tile (expert e, block m) of
+    # owner p waits for the flag (blk_base + m, source w) of every source whose rows overlap the
+    # block; exactly those flags must be raised, each by one item that carries exactly the
+    # overlapping rows — also when the buffers are too small and rows are dropped
+    for cap in (None, max(1, int(mat.sum()) // (2 * world))):
+        raised = {}
+        for me in range(world):
+            items = torch_impl.send_items(mat, me, n_expert, cap, block=block)
+            prefix = torch_impl.send_item_prefix(mat, me, n_expert, cap, block=block)
+            assert len(items) == prefix[-1]
+            for owner, flag_blk, r0, r1 in items:
+                assert (owner, flag_blk, me) not in raised and r0 < r1
+                raised[(owner, flag_blk, me)] = (r0, r1)
+        waited = {}
+        for owner in range(world):
+            _b, offs, _t, _o = torch_impl.exchange_offsets(mat, owner, n_expert, cap)
+            limit = int(offs[-1])
+            blk0 = 0
+            for e in range(n_expert):
+                g = owner * n_expert + e
+                lo, hi = int(offs[e]), int(offs[e + 1])
+                for m in range((hi - lo + block - 1) // block):
+                    r0, r1 = lo + m * block, min(lo + (m + 1) * block, hi)
+                    for w in range(world):
+                        s0 = int(views[w][0][g])
+                        s1 = min(s0 + int(mat[w, g]), limit)
+                        # the producer's test (grouped_gemm_kernel.cuh, gate_flag): a source
+                        # with rows of its own that overlap the block
+                        if s0 < s1 and s0 < r1 and s1 > r0:
+                            waited[(owner, blk0 + m, w)] = (max(s0, r0), min(s1, r1))
+                # flag blocks are numbered over the unclamped segments (what the senders know)
+                blk0 += (int(mat[:, g].sum()) + block - 1) // block
+        assert raised == waited
     # a bounded receive buffer: totals are clamped and the overflow is flagged on every rank
     small = max(0, int(mat.sum()) // (2 * world))
     flags = [torch_impl.exchange_offsets(mat, me, n_expert, small)[3] for me in range(world)]
