@@ -238,7 +238,7 @@ count_exchange_kernel(const __grid_constant__ ExchangeCtx c, const int* __restri
     int t = 0;
     for (int e = 0; e < n_expert; ++e) t += col[p * n_expert + e];
     if (t > capacity_rows) atomicCAS(c.status, 0, kStatusRecvOverflow);
-    if (mat[p * width + tot] != capacity_rows) atomicCAS(c.status, 0, kStatusCapacityMismatch);
+    if (mat[p * width + tot] != capacity_rows) record_failure(c.status, kStatusCapacityMismatch);
   }
   if (threadIdx.x == 0) c.epoch[0] = epoch;
 }
