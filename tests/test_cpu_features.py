@@ -337,6 +337,66 @@ def test_ep_trace_summary_arithmetic(monkeypatch):
     assert config.ep_trace()
 
 
+def test_signal_audit_findings(monkeypatch):
+    r"""``SymmWorkspace.audit`` on a stand-in workspace (plain CPU tensors): a state at rest is
+    ``ok``; a flag ahead of the epoch, a completion counter or a sender block counter that is
+    not zero, a lease that was not handed back and a status code are each found."""
+    import types
+    from fastmoe_b200.ops import native
+    from fastmoe_b200.parallel import symm
+
+    class _Native:
+        P2P_NUM_CHANNELS, P2P_MAX_PEERS, P2P_CHAN_REDUCE = 4, 16, 3
+        status = 0
+
+        def read_status(self, _index):
+            return self.status
+
+    fake_native = _Native()
+    monkeypatch.setattr(native, "get", lambda: fake_native)
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+
+    def workspace():
+        ws = types.SimpleNamespace()
+        ws.device = types.SimpleNamespace(index=0)
+        ws.world = 2
+        ws.epoch = torch.tensor([7, 0, 0, 0, 0, 0, 3, 0], dtype=torch.int32)
+        signal = torch.zeros(4, 16, dtype=torch.int32)
+        signal[0:3, :2] = 7                 # counts / dispatch / return channels at the exchange epoch
+        signal[3, :2] = 2 * 3 + 1           # reduction channel: "done" of reduction 3
+        ws.signal = signal.view(torch.uint8).reshape(-1)
+        gate = torch.zeros(5, 16, dtype=torch.int32)
+        gate[:3, :2] = 7
+        gate[3, 0] = 6                      # a block that the last exchange did not touch
+        ws._buffers = {"gate": (gate.view(torch.uint8).reshape(-1), [], None)}
+        ws._item_count = torch.zeros(9, dtype=torch.int32)
+        ws._pool = {1 << 20: [("t", "p")]}
+        ws._leased_handles = ["h"]
+        return ws
+
+    audit = symm.SymmWorkspace.audit
+    rest = audit(workspace())
+    assert rest["ok"] and rest["flags_ahead_of_epoch"] == 0 and rest["leases_outstanding"] == 0
+
+    ws = workspace()
+    ws._buffers["gate"][0].view(torch.int32).view(5, 16)[4, 1] = 8
+    assert audit(ws)["flags_ahead_of_epoch"] == 1 and not audit(ws)["ok"]
+    ws = workspace()
+    ws.signal.view(torch.int32).view(4, 16)[3, 0] = 2 * 3 + 2
+    assert audit(ws)["flags_ahead_of_epoch"] == 1
+    ws = workspace()
+    ws.epoch[4] = 5
+    assert audit(ws)["completion_counters"] == [0, 0, 0, 5, 0] and not audit(ws)["ok"]
+    ws = workspace()
+    ws._item_count[2] = 40
+    assert audit(ws)["sender_block_counters_nonzero"] == 1 and not audit(ws)["ok"]
+    ws = workspace()
+    ws._pool = {1 << 20: []}
+    assert audit(ws)["leases_outstanding"] == 1 and not audit(ws)["ok"]
+    fake_native.status = 201
+    assert audit(workspace())["status"] == 201 and not audit(workspace())["ok"]
+
+
 def test_async_gradient_allreduce_handle_without_gpu():
     r"""``allreduce_gradients(async_op=True)`` returns a handle on every device; without CUDA the
     reduction has already happened when it returns."""
