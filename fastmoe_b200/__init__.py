@@ -10,5 +10,5 @@ from .linear import FMoELinear
 from .transformer import FMoETransformerMLP
 from .distributed import DistributedGroupedDataParallel
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 __all__ = ["FMoE", "FMoELinear", "FMoETransformerMLP", "DistributedGroupedDataParallel"]

@@ -21,7 +21,7 @@ class BuildWithNative(build_py):
 
 setup(
     name="fastmoe_b200",
-    version="0.1.0",
+    version="0.2.0",
     description="Mixture-of-Experts training system for NVIDIA B200 with the FastMoE API",
     packages=find_packages(include=["fastmoe_b200", "fastmoe_b200.*", "fmoe"]),
     py_modules=["fmoe_cuda"],
